@@ -1,0 +1,143 @@
+/*
+ * transducer_b200 -- C ABI of the sm_100a RNN-T loss / Viterbi library.
+ *
+ * Drop-in boundary for the CUDA path of awni/transducer.  The first three entry
+ * points take exactly the arguments of that project's transducer.h (minus the
+ * `useCuda` flag: this library has no CPU backend); the remaining ones replace the
+ * arithmetic its Python wrapper performs with torch ops around those calls.
+ *
+ * Conventions (identical to the reference, transducer/transducer_cpu.cpp:242-256):
+ *   emissions    float [B, maxT, V]      unnormalised scores per frame
+ *   predictions  float [B, maxU, V]      maxU = longest label sequence + 1
+ *   labels       int   [B, maxU-1]
+ *   inputLengths int   [B]               T_b  <= maxT
+ *   labelLengths int   [B]               U_b = labelLengths[b] + 1 <= maxU
+ *   lattices (logNorms, alphas, lngrads) float [B, maxT, maxU]
+ * The output distribution at node (t,u) is log_softmax(E[b,t,:] + P[b,u,:]).
+ *
+ * All pointers are DEVICE pointers on the current device unless stated otherwise.
+ * Calls are asynchronous on the stream chosen with tb200_set_stream (default: the
+ * legacy default stream, as the reference launches on, transducer_cuda.cu:295).
+ * Every function returns 0 on success, a TB200_ERR_* code otherwise; the message is
+ * available from tb200_last_error() on the calling thread.
+ */
+#ifndef TRANSDUCER_B200_H_
+#define TRANSDUCER_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB200_OK 0
+#define TB200_ERR_INVALID_ARGUMENT 1
+#define TB200_ERR_CUDA 2
+#define TB200_ERR_WORKSPACE 3
+#define TB200_ERR_UNSUPPORTED 4
+#define TB200_ERR_DEVICE_STATUS 5
+
+/* Library version (major*10000 + minor*100 + patch). */
+int tb200_version(void);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* tb200_last_error(void);
+
+/* Stream (a cudaStream_t) used by subsequent calls from this thread.  NULL selects
+ * the legacy default stream, which is what the reference's launches use
+ * (transducer/transducer_cuda.cu:295,333,372).  No counterpart in the reference. */
+int tb200_set_stream(void* stream);
+void* tb200_get_stream(void);
+
+/* Tuning / test switches.  Keys:
+ *   "lognorm_path"  0 auto, 1 exact SIMT logsumexp, 2 tensor-core factored GEMM
+ *   "grads_path"    0 auto, 1 SIMT, 2 tensor-core
+ *   "grad_passes"   1 or 3: TF32 products per gradient GEMM (3 = split, ~fp32 accuracy)
+ * Unknown keys return TB200_ERR_INVALID_ARGUMENT.  No counterpart in the reference. */
+int tb200_set_option(const char* key, int value);
+int tb200_get_option(const char* key, int* value);
+
+/* ---- the reference's three entry points ------------------------------------ */
+
+/* transducer/transducer.h:3-17 (`forward`, useCuda=true): alpha recursion.
+ * Writes costs[B] (+inf where T_b==0) and the valid region of alphas. */
+int tb200_forward(const float* emissions, const float* predictions, float* costs,
+                  float* alphas, const float* logNorms, const int* labels,
+                  const int* inputLengths, const int* labelLengths, int batchSize,
+                  int maxInputLength, int maxLabelLength, int alphabetSize, int blank);
+
+/* transducer/transducer.h:19-35 (`backward`): zero-fills egrads/pgrads/lngrads over
+ * their full padded extent, then writes the node occupancies to lngrads and
+ * subtracts the sparse blank/label terms from egrads/pgrads. */
+int tb200_backward(const float* emissions, const float* predictions, float* egrads,
+                   float* pgrads, float* lngrads, const float* alphas,
+                   const float* logNorms, const int* labels, const int* inputLengths,
+                   const int* labelLengths, int batchSize, int maxInputLength,
+                   int maxLabelLength, int alphabetSize, int blank);
+
+/* transducer/transducer.h:37-49 (`viterbi`): best alignment given the label
+ * lengths; writes the first labelLengths[b] entries of labels[b,:].  Like the
+ * reference (transducer_cuda.cu:364-369) it takes its temporaries from the
+ * stream-ordered allocator. */
+int tb200_viterbi(const float* emissions, const float* predictions,
+                  const float* logNorms, int* labels, const int* inputLengths,
+                  const int* labelLengths, int batchSize, int maxInputLength,
+                  int maxLabelLength, int alphabetSize, int blank);
+
+/* ---- the arithmetic the reference does in torch ops ------------------------- */
+
+/* transducer/torch_binding.py:35-40 and :162-167: logNorms[b,t,u] =
+ * logsumexp_v(E[b,t,v] + P[b,u,v]) for every valid node (padding is not written).
+ * Also returns the per-row shifts the factored gradient kernels reuse:
+ * rowRef [B,maxT] (a per-frame reference value <= max_v E, not necessarily the
+ * maximum) and maxP [B,maxU].  workspace: tb200_log_norms_workspace_bytes(). */
+size_t tb200_log_norms_workspace_bytes(int batchSize, int maxInputLength,
+                                       int maxLabelLength, int alphabetSize);
+int tb200_log_norms(const float* emissions, const float* predictions, float* logNorms,
+                    float* rowRef, float* maxP, const int* inputLengths,
+                    const int* labelLengths, int batchSize, int maxInputLength,
+                    int maxLabelLength, int alphabetSize, void* workspace,
+                    size_t workspaceBytes);
+
+/* transducer/torch_binding.py:25-58 (Transducer.forward): log-normalisers + alpha
+ * recursion.  Outputs costs[B], alphas, logNorms, rowRef, maxP (kept by the caller
+ * for the backward call).  If lossSum is not NULL it receives sum_b costs[b]
+ * (added in index order by the last CTA to finish). */
+size_t tb200_loss_forward_workspace_bytes(int batchSize, int maxInputLength,
+                                          int maxLabelLength, int alphabetSize);
+int tb200_loss_forward(const float* emissions, const float* predictions,
+                       const int* labels, const int* inputLengths,
+                       const int* labelLengths, float* costs, float* alphas,
+                       float* logNorms, float* rowRef, float* maxP, float* lossSum,
+                       int batchSize, int maxInputLength, int maxLabelLength,
+                       int alphabetSize, int blank, void* workspace,
+                       size_t workspaceBytes);
+
+/* transducer/torch_binding.py:60-90 (Transducer.backward): reverse sweep + dense
+ * gradient contractions + deltas scaling.  Every element of egrads [B,maxT,V] and
+ * pgrads [B,maxU,V] is written (zeros in the padding). */
+size_t tb200_loss_backward_workspace_bytes(int batchSize, int maxInputLength,
+                                           int maxLabelLength, int alphabetSize);
+int tb200_loss_backward(const float* emissions, const float* predictions,
+                        const int* labels, const int* inputLengths,
+                        const int* labelLengths, const float* alphas,
+                        const float* logNorms, const float* rowRef, const float* maxP,
+                        const float* deltas, float* egrads, float* pgrads,
+                        int batchSize, int maxInputLength, int maxLabelLength,
+                        int alphabetSize, int blank, void* workspace,
+                        size_t workspaceBytes);
+
+/* transducer/torch_binding.py:130-177 (TransducerLoss.viterbi): log-normalisers +
+ * best path, all temporaries in the caller's workspace. */
+size_t tb200_viterbi_decode_workspace_bytes(int batchSize, int maxInputLength,
+                                            int maxLabelLength, int alphabetSize);
+int tb200_viterbi_decode(const float* emissions, const float* predictions,
+                         const int* inputLengths, const int* labelLengths, int* labels,
+                         int batchSize, int maxInputLength, int maxLabelLength,
+                         int alphabetSize, int blank, void* workspace,
+                         size_t workspaceBytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRANSDUCER_B200_H_ */

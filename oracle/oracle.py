@@ -1,0 +1,315 @@
+"""CPU oracle for the additive-joiner RNN-T loss / Viterbi path (TEST INFRASTRUCTURE).
+
+Only tests/, the smoke check and bench.py's CPU legs import this module; the
+product package never does.
+
+Two backends sit behind the same functions:
+
+* ``impl="port"``      -> ``liboracle.so`` built from ``oracle.c`` (the plain-C
+  restatement of transducer/transducer_cpu.cpp);
+* ``impl="reference"`` -> ``_ref/libref_transducer.so``, the reference's own CPU
+  backend compiled unchanged from its sources by ``oracle/Makefile`` (its
+  ``forward``/``backward``/``viterbi`` have C++ linkage, transducer/transducer.h:3-49,
+  so they are bound by their mangled names).
+
+The arithmetic the reference does in torch ops around those three calls
+(transducer/torch_binding.py:35-40 for the log-normalisers, :85-89 for the dense
+part of the gradient, :162-167 for Viterbi) is restated here with the same torch
+CPU ops in the same order, so ``loss_and_grads`` / ``viterbi`` reproduce what
+``TransducerLoss`` returns on CPU.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PORT_SO = os.path.join(_HERE, "liboracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libref_transducer.so")
+
+_f = ctypes.POINTER(ctypes.c_float)
+_i = ctypes.POINTER(ctypes.c_int)
+_c = ctypes.c_int
+
+# mangled names of transducer.h's three functions (Itanium ABI)
+_REF_FORWARD = "_Z7forwardPKfS0_PfS1_S0_PKiS3_S3_iiiiib"
+_REF_BACKWARD = "_Z8backwardPKfS0_PfS1_S1_S0_S0_PKiS3_S3_iiiiib"
+_REF_VITERBI = "_Z7viterbiPKfS0_S0_PiPKiS3_iiiiib"
+
+_libs = {}
+
+
+def build(quiet=True):
+    """(Re)build liboracle.so and, where the reference sources exist, _ref/."""
+    subprocess.run(["make", "-C", _HERE], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def have_reference():
+    return os.path.exists(_REF_SO)
+
+
+def _port():
+    if "port" not in _libs:
+        if not os.path.exists(_PORT_SO):
+            build()
+        lib = ctypes.CDLL(_PORT_SO)
+        lib.oracle_log_norms_exact.argtypes = [_f, _f, _f, _i, _i, _c, _c, _c, _c]
+        lib.oracle_log_norms_factored.argtypes = [_f, _f, _f, _c, _c, _c, _c]
+        lib.oracle_forward.argtypes = [_f, _f, _f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c]
+        lib.oracle_backward.argtypes = [_f, _f, _f, _f, _f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c]
+        lib.oracle_accumulate_grads_exact.argtypes = [_f, _f, _f, _f, _f, _f, _i, _i, _c, _c, _c, _c]
+        lib.oracle_viterbi.argtypes = [_f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c]
+        for fn in ("oracle_log_norms_exact", "oracle_log_norms_factored", "oracle_forward",
+                   "oracle_backward", "oracle_accumulate_grads_exact", "oracle_viterbi"):
+            getattr(lib, fn).restype = None
+        _libs["port"] = lib
+    return _libs["port"]
+
+
+def _ref():
+    if "ref" not in _libs:
+        if not os.path.exists(_REF_SO):
+            raise RuntimeError("reference CPU backend not built: run `make -C oracle` "
+                               "where the reference sources are present")
+        lib = ctypes.CDLL(_REF_SO)
+        b = ctypes.c_bool
+        fw = getattr(lib, _REF_FORWARD)
+        fw.argtypes = [_f, _f, _f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c, b]
+        bw = getattr(lib, _REF_BACKWARD)
+        bw.argtypes = [_f, _f, _f, _f, _f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c, b]
+        vt = getattr(lib, _REF_VITERBI)
+        vt.argtypes = [_f, _f, _f, _i, _i, _i, _c, _c, _c, _c, _c, b]
+        for fn in (fw, bw, vt):
+            fn.restype = None
+        _libs["ref"] = (fw, bw, vt)
+    return _libs["ref"]
+
+
+def _fp(a):
+    return a.ctypes.data_as(_f) if a is not None and a.size else ctypes.cast(None, _f)
+
+
+def _ip(a):
+    return a.ctypes.data_as(_i) if a is not None and a.size else ctypes.cast(None, _i)
+
+
+def _f32(a):
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def _i32(a):
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int32))
+
+
+# ----------------------------------------------------------------------------
+# the three transducer.h calls
+# ----------------------------------------------------------------------------
+
+def forward(E, P, LN, labels, in_lens, lab_lens, blank=0, impl="port"):
+    """transducer.h:3-17 on host buffers -> (costs[B], alphas[B,T,U'])."""
+    E, P, LN = _f32(E), _f32(P), _f32(LN)
+    labels, in_lens, lab_lens = _i32(labels), _i32(in_lens), _i32(lab_lens)
+    B, T, V = E.shape
+    U = P.shape[1]
+    costs = np.zeros(B, np.float32)
+    alphas = np.zeros((B, T, U), np.float32)
+    args = (_fp(E), _fp(P), _fp(costs), _fp(alphas), _fp(LN), _ip(labels), _ip(in_lens),
+            _ip(lab_lens), B, T, U, V, blank)
+    if impl == "reference":
+        _ref()[0](*args, False)
+    else:
+        _port().oracle_forward(*args)
+    return costs, alphas
+
+
+def backward(E, P, alphas, LN, labels, in_lens, lab_lens, blank=0, impl="port"):
+    """transducer.h:19-35 -> (egrads, pgrads, lngrads): zero-filled, sparse part only."""
+    E, P, LN, alphas = _f32(E), _f32(P), _f32(LN), _f32(alphas)
+    labels, in_lens, lab_lens = _i32(labels), _i32(in_lens), _i32(lab_lens)
+    B, T, V = E.shape
+    U = P.shape[1]
+    eg = np.empty_like(E)
+    pg = np.empty_like(P)
+    lg = np.empty((B, T, U), np.float32)
+    args = (_fp(E), _fp(P), _fp(eg), _fp(pg), _fp(lg), _fp(alphas), _fp(LN), _ip(labels),
+            _ip(in_lens), _ip(lab_lens), B, T, U, V, blank)
+    if impl == "reference":
+        _ref()[1](*args, False)
+    else:
+        _port().oracle_backward(*args)
+    return eg, pg, lg
+
+
+def viterbi_abi(E, P, LN, in_lens, lab_lens, blank=0, impl="port", fill=-1):
+    """transducer.h:37-49 -> labels[B,U'-1]; entries past label_lengths[b] keep `fill`."""
+    E, P, LN = _f32(E), _f32(P), _f32(LN)
+    in_lens, lab_lens = _i32(in_lens), _i32(lab_lens)
+    B, T, V = E.shape
+    U = P.shape[1]
+    out = np.full((B, max(U - 1, 0)), fill, np.int32)
+    args = (_fp(E), _fp(P), _fp(LN), _ip(out), _ip(in_lens), _ip(lab_lens), B, T, U, V, blank)
+    if impl == "reference":
+        _ref()[2](*args, False)
+    else:
+        _port().oracle_viterbi(*args)
+    return out
+
+
+# ----------------------------------------------------------------------------
+# log-normalisers
+# ----------------------------------------------------------------------------
+
+def log_norms_exact(E, P, in_lens, lab_lens):
+    """transducer/test.h:51-80: exact logsumexp per valid (t,u); padding is 0."""
+    E, P = _f32(E), _f32(P)
+    in_lens, lab_lens = _i32(in_lens), _i32(lab_lens)
+    B, T, V = E.shape
+    U = P.shape[1]
+    LN = np.zeros((B, T, U), np.float32)
+    _port().oracle_log_norms_exact(_fp(E), _fp(P), _fp(LN), _ip(in_lens), _ip(lab_lens), B, T, U, V)
+    return LN
+
+
+def log_norms_factored_c(E, P):
+    """torch_binding.py:35-40 in plain C (index-order fp32 inner products)."""
+    E, P = _f32(E), _f32(P)
+    B, T, V = E.shape
+    U = P.shape[1]
+    LN = np.zeros((B, T, U), np.float32)
+    _port().oracle_log_norms_factored(_fp(E), _fp(P), _fp(LN), B, T, U, V)
+    return LN
+
+
+def log_norms_torch(E, P):
+    """torch_binding.py:35-40 with the same torch CPU ops; returns the pieces
+    the reference keeps for its backward pass."""
+    E = torch.as_tensor(np.asarray(E, np.float32))
+    P = torch.as_tensor(np.asarray(P, np.float32))
+    max_e = E.max(dim=2, keepdim=True)[0]
+    max_p = P.max(dim=2, keepdim=True)[0]
+    exp_e = torch.exp(E - max_e)
+    exp_p = torch.exp(P - max_p)
+    exp_ln = torch.bmm(exp_e, exp_p.transpose(1, 2))
+    ln = torch.log(exp_ln) + max_e + max_p.transpose(1, 2)
+    return ln, exp_e, exp_p, exp_ln
+
+
+# ----------------------------------------------------------------------------
+# the whole path, as TransducerLoss runs it on CPU
+# ----------------------------------------------------------------------------
+
+def loss_and_grads(E, P, labels, in_lens, lab_lens, blank=0, deltas=None, impl="port",
+                   want_grads=True):
+    """What ``TransducerLoss(blank)(E,P,labels,in_lens,lab_lens)`` followed by
+    ``(deltas*costs).sum().backward()`` yields on CPU (torch_binding.py:25-90).
+
+    Returns a dict with costs, alphas, log_norms and, if asked, egrads, pgrads,
+    lngrads (the node occupancies)."""
+    E, P = _f32(E), _f32(P)
+    B = E.shape[0]
+    ln_t, exp_e, exp_p, exp_ln = log_norms_torch(E, P)
+    LN = ln_t.contiguous().numpy()
+    costs, alphas = forward(E, P, LN, labels, in_lens, lab_lens, blank, impl)
+    out = {"costs": costs, "alphas": alphas, "log_norms": LN}
+    if not want_grads:
+        return out
+    eg, pg, lg = backward(E, P, alphas, LN, labels, in_lens, lab_lens, blank, impl)
+    out["lngrads"] = lg.copy()
+    d = torch.ones(B) if deltas is None else torch.as_tensor(np.asarray(deltas, np.float32))
+    eg_t, pg_t = torch.from_numpy(eg), torch.from_numpy(pg)
+    w = torch.from_numpy(lg) * exp_ln.reciprocal()
+    eg_t += exp_e * torch.bmm(w, exp_p)
+    pg_t += exp_p * torch.bmm(w.transpose(1, 2), exp_e)
+    out["egrads"] = (d[:, None, None] * eg_t).numpy()
+    out["pgrads"] = (d[:, None, None] * pg_t).numpy()
+    return out
+
+
+def viterbi(E, P, in_lens, lab_lens, blank=0, impl="port", fill=-1):
+    """``TransducerLoss(blank).viterbi`` on CPU (torch_binding.py:130-177)."""
+    ln_t = log_norms_torch(E, P)[0]
+    return viterbi_abi(E, P, ln_t.contiguous().numpy(), in_lens, lab_lens, blank, impl, fill)
+
+
+def accumulate_grads_exact(E, P, egrads, pgrads, lngrads, LN, in_lens, lab_lens):
+    """transducer/test.h:82-113, in place on egrads/pgrads (small cases)."""
+    E, P, LN, lngrads = _f32(E), _f32(P), _f32(LN), _f32(lngrads)
+    in_lens, lab_lens = _i32(in_lens), _i32(lab_lens)
+    B, T, V = E.shape
+    U = P.shape[1]
+    assert egrads.dtype == np.float32 and egrads.flags.c_contiguous
+    assert pgrads.dtype == np.float32 and pgrads.flags.c_contiguous
+    _port().oracle_accumulate_grads_exact(_fp(E), _fp(P), _fp(egrads), _fp(pgrads), _fp(lngrads),
+                                          _fp(LN), _ip(in_lens), _ip(lab_lens), B, T, U, V)
+
+
+# ----------------------------------------------------------------------------
+# float64 "truth": the same loss by an alpha/beta recursion in double precision.
+# Used only to attribute differences between two fp32 implementations to the
+# fp32 noise floor of the recursion (alphas reach ~1e4 at T=2000, ulp ~1e-3).
+# ----------------------------------------------------------------------------
+
+def truth64(E, P, labels, in_lens, lab_lens, blank=0):
+    E = torch.as_tensor(np.asarray(E, np.float64))
+    P = torch.as_tensor(np.asarray(P, np.float64))
+    labels = np.asarray(labels)
+    B, Tm, V = E.shape
+    Um = P.shape[1]
+    me = E.max(dim=2, keepdim=True)[0]
+    mp = P.max(dim=2, keepdim=True)[0]
+    xe, xp = torch.exp(E - me), torch.exp(P - mp)
+    s = torch.bmm(xe, xp.transpose(1, 2))
+    LN = (torch.log(s) + me + mp.transpose(1, 2)).numpy()
+    En, Pn = E.numpy(), P.numpy()
+    costs = np.full(B, np.inf)
+    eg = np.zeros((B, Tm, V))
+    pg = np.zeros((B, Um, V))
+    for b in range(B):
+        T, U = int(in_lens[b]), int(lab_lens[b]) + 1
+        if T == 0 or U == 0:
+            continue
+        lab = labels[b, :U - 1].astype(np.int64)
+        ln = LN[b, :T, :U]
+        stay = En[b, :T, blank][:, None] + Pn[b, :U, blank][None, :] - ln          # [T,U]
+        step = np.full((T, U), -np.inf)
+        if U > 1:
+            step[:, :U - 1] = En[b, :T][:, lab] + Pn[b, np.arange(U - 1), lab][None, :] - ln[:, :U - 1]
+        al = np.full((T, U), -np.inf)
+        be = np.full((T, U), -np.inf)
+        al[0, 0] = 0.0
+        for t in range(T):
+            for u in range(U):
+                if t == 0 and u == 0:
+                    continue
+                a = al[t - 1, u] + stay[t - 1, u] if t > 0 else -np.inf
+                c = al[t, u - 1] + step[t, u - 1] if u > 0 else -np.inf
+                al[t, u] = np.logaddexp(a, c)
+        be[T - 1, U - 1] = stay[T - 1, U - 1]
+        for t in range(T - 1, -1, -1):
+            for u in range(U - 1, -1, -1):
+                if t == T - 1 and u == U - 1:
+                    continue
+                a = be[t + 1, u] + stay[t, u] if t < T - 1 else -np.inf
+                c = be[t, u + 1] + step[t, u] if u < U - 1 else -np.inf
+                be[t, u] = np.logaddexp(a, c)
+        ll = be[0, 0]
+        costs[b] = -ll
+        g = np.exp(al + be - ll)                                   # node occupancy
+        occ_stay = np.zeros((T, U))
+        occ_stay[:T - 1] = np.exp(al[:T - 1] + stay[:T - 1] + be[1:] - ll)
+        occ_stay[T - 1, U - 1] = 1.0
+        occ_step = np.zeros((T, U))
+        if U > 1:
+            occ_step[:, :U - 1] = np.exp(al[:, :U - 1] + step[:, :U - 1] + be[:, 1:] - ll)
+        w = torch.from_numpy(g / s[b, :T, :U].numpy())
+        eg[b, :T] = (xe[b, :T] * (w @ xp[b, :U])).numpy()
+        pg[b, :U] = (xp[b, :U] * (w.T @ xe[b, :T])).numpy()
+        eg[b, :T, blank] -= occ_stay.sum(1)
+        pg[b, :U, blank] -= occ_stay.sum(0)
+        for u in range(U - 1):
+            eg[b, :T, lab[u]] -= occ_step[:, u]
+            pg[b, u, lab[u]] -= occ_step[:, u].sum()
+    return {"costs": costs, "egrads": eg, "pgrads": pg, "log_norms": LN}

@@ -1,0 +1,59 @@
+"""ctypes view of the C ABI declared in include/transducer_b200.h.
+
+The product path never falls back to anything else: if the shared library has not
+been built, importing this module raises."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtransducer_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "transducer_b200: native library missing (%s). Build it with "
+        "`python -m transducer_b200.build`; there is no CPU or PyTorch fallback." % LIB_PATH)
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_p = ctypes.c_void_p
+_i = ctypes.c_int
+_z = ctypes.c_size_t
+
+# name -> (restype, argtypes); one entry per declaration in transducer_b200.h
+SIGNATURES = {
+    "tb200_version": (_i, []),
+    "tb200_last_error": (ctypes.c_char_p, []),
+    "tb200_set_stream": (_i, [_p]),
+    "tb200_get_stream": (_p, []),
+    "tb200_set_option": (_i, [ctypes.c_char_p, _i]),
+    "tb200_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
+    "tb200_forward": (_i, [_p] * 8 + [_i] * 5),
+    "tb200_backward": (_i, [_p] * 10 + [_i] * 5),
+    "tb200_viterbi": (_i, [_p] * 6 + [_i] * 5),
+    "tb200_log_norms_workspace_bytes": (_z, [_i] * 4),
+    "tb200_log_norms": (_i, [_p] * 7 + [_i] * 4 + [_p, _z]),
+    "tb200_loss_forward_workspace_bytes": (_z, [_i] * 4),
+    "tb200_loss_forward": (_i, [_p] * 11 + [_i] * 5 + [_p, _z]),
+    "tb200_loss_backward_workspace_bytes": (_z, [_i] * 4),
+    "tb200_loss_backward": (_i, [_p] * 12 + [_i] * 5 + [_p, _z]),
+    "tb200_viterbi_decode_workspace_bytes": (_z, [_i] * 4),
+    "tb200_viterbi_decode": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class Tb200Error(RuntimeError):
+    pass
+
+
+def check(rc):
+    """Raise with the library's message when a C-ABI call did not return 0."""
+    if rc != 0:
+        msg = lib.tb200_last_error().decode()
+        if rc in (1, 3):
+            raise ValueError(msg)
+        raise Tb200Error("tb200 error %d: %s" % (rc, msg))

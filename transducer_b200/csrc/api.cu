@@ -1,0 +1,346 @@
+// C ABI (include/transducer_b200.h) and the reference-compatible C++-linkage entry
+// points (include/transducer.h) on top of the kernel launchers.
+#include <cstring>
+#include <string>
+
+#include "../../include/transducer.h"
+#include "../../include/transducer_b200.h"
+#include "kernels.h"
+
+namespace tb200 {
+namespace {
+
+thread_local cudaStream_t g_stream = nullptr;
+thread_local std::string g_error;
+
+struct Options {
+  int lognorm_path = 0;
+  int grads_path = 0;
+  int grad_passes = 3;
+};
+Options g_opt;
+
+int fail(int code, const std::string& msg) {
+  g_error = msg;
+  return code;
+}
+
+// Runs `body`, mapping exceptions to status codes.
+template <typename F>
+int guarded(F&& body) {
+  try {
+    body();
+    return kOk;
+  } catch (const CudaError& e) {
+    return fail(kErrCuda, e.what());
+  } catch (const std::invalid_argument& e) {
+    return fail(kErrInvalidArgument, e.what());
+  } catch (const std::exception& e) {
+    return fail(kErrCuda, e.what());
+  }
+}
+
+void check_dims(const Dims& d) {
+  if (d.B < 0 || d.maxT < 0 || d.maxU < 0 || d.V <= 0)
+    throw std::invalid_argument("negative batch/length or non-positive alphabet size");
+  if (d.blank < 0 || d.blank >= d.V) throw std::invalid_argument("blank outside [0, alphabetSize)");
+}
+
+// Bump allocator over the caller's workspace; every block is 256-byte aligned.
+struct Carver {
+  char* base;
+  size_t used = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  template <typename T>
+  T* take(size_t n) {
+    used = (used + 255) & ~size_t(255);
+    T* p = base ? reinterpret_cast<T*>(base + used) : nullptr;
+    used += n * sizeof(T);
+    return p;
+  }
+  size_t total() const { return (used + 255) & ~size_t(255); }
+};
+
+int ld_w(const Dims& d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
+
+struct LogNormWs {
+  unsigned* ticket;
+  LogNormWs(Carver& c, const Dims&) { ticket = c.take<unsigned>(64); }
+};
+
+struct BackwardWs {
+  float *expP, *W, *em, *eBlank, *pBlank, *pLabel, *maxPScratch;
+  BackwardWs(Carver& c, const Dims& d) {
+    const size_t B = d.B, T = d.maxT, U = d.maxU, V = d.V;
+    expP = c.take<float>(B * U * V);
+    W = c.take<float>(B * T * ld_w(d));
+    em = c.take<float>(B * T * U);
+    eBlank = c.take<float>(B * T);
+    pBlank = c.take<float>(B * U);
+    pLabel = c.take<float>(B * U);
+    maxPScratch = c.take<float>(B * U);
+  }
+};
+
+struct ViterbiWs {
+  float *LN, *rowRef, *maxP, *best;
+  uint32_t* decBits;
+  ViterbiWs(Carver& c, const Dims& d) {
+    const size_t B = d.B, T = d.maxT, U = d.maxU;
+    LN = c.take<float>(B * T * U);
+    rowRef = c.take<float>(B * T);
+    maxP = c.take<float>(B * U);
+    best = c.take<float>(B * T * U);
+    decBits = c.take<uint32_t>(viterbi_decbits_words(d));
+  }
+};
+
+void need(size_t have, size_t want, const void* ws) {
+  if (want > 0 && (ws == nullptr || have < want))
+    throw std::invalid_argument("workspace too small: need " + std::to_string(want) +
+                                " bytes, got " + std::to_string(have));
+}
+
+// Log-normalisers plus the row shifts.  With the exact path rowRef is the true row
+// maximum of E.
+void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+                    const int* inLens, const int* labLens, const Dims& d, LogNormWs&) {
+  launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
+  if (rowRef) launch_row_max(E, rowRef, inLens, 0, d.B, d.maxT, d.V, g_stream);
+  if (maxP) launch_row_max(P, maxP, labLens, 1, d.B, d.maxU, d.V, g_stream);
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" {
+
+int tb200_version(void) { return 100; }
+
+const char* tb200_last_error(void) { return g_error.c_str(); }
+
+int tb200_set_stream(void* stream) {
+  g_stream = static_cast<cudaStream_t>(stream);
+  return kOk;
+}
+void* tb200_get_stream(void) { return g_stream; }
+
+int tb200_set_option(const char* key, int value) {
+  if (!key) return fail(kErrInvalidArgument, "null option key");
+  if (!strcmp(key, "lognorm_path") && value >= 0 && value <= 2) g_opt.lognorm_path = value;
+  else if (!strcmp(key, "grads_path") && value >= 0 && value <= 2) g_opt.grads_path = value;
+  else if (!strcmp(key, "grad_passes") && (value == 1 || value == 3)) g_opt.grad_passes = value;
+  else return fail(kErrInvalidArgument, std::string("unknown option or bad value: ") + key);
+  return kOk;
+}
+
+int tb200_get_option(const char* key, int* value) {
+  if (!key || !value) return fail(kErrInvalidArgument, "null argument");
+  if (!strcmp(key, "lognorm_path")) *value = g_opt.lognorm_path;
+  else if (!strcmp(key, "grads_path")) *value = g_opt.grads_path;
+  else if (!strcmp(key, "grad_passes")) *value = g_opt.grad_passes;
+  else return fail(kErrInvalidArgument, std::string("unknown option: ") + key);
+  return kOk;
+}
+
+int tb200_forward(const float* E, const float* P, float* costs, float* alphas,
+                  const float* LN, const int* labels, const int* inLens,
+                  const int* labLens, int B, int maxT, int maxU, int V, int blank) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    launch_alpha(E, P, costs, alphas, LN, labels, inLens, labLens, d, nullptr, nullptr,
+                 g_stream);
+  });
+}
+
+int tb200_backward(const float* E, const float* P, float* egrads, float* pgrads,
+                   float* lngrads, const float* alphas, const float* LN,
+                   const int* labels, const int* inLens, const int* labLens, int B,
+                   int maxT, int maxU, int V, int blank) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    const size_t b = B, t = maxT, u = maxU, v = V;
+    if (b * t * v) TB200_CUDA_CHECK(cudaMemsetAsync(egrads, 0, sizeof(float) * b * t * v, g_stream));
+    if (b * u * v) TB200_CUDA_CHECK(cudaMemsetAsync(pgrads, 0, sizeof(float) * b * u * v, g_stream));
+    if (b * t * u) TB200_CUDA_CHECK(cudaMemsetAsync(lngrads, 0, sizeof(float) * b * t * u, g_stream));
+    launch_gamma_abi(E, P, egrads, pgrads, lngrads, alphas, LN, labels, inLens, labLens, d,
+                     g_stream);
+  });
+}
+
+int tb200_viterbi(const float* E, const float* P, const float* LN, int* labels,
+                  const int* inLens, const int* labLens, int B, int maxT, int maxU, int V,
+                  int blank) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    if (B == 0 || maxT == 0 || maxU == 0) return;
+    const size_t cells = (size_t)B * maxT * maxU;
+    float* best = nullptr;
+    uint32_t* dec = nullptr;
+    TB200_CUDA_CHECK(cudaMallocAsync((void**)&best, sizeof(float) * cells, g_stream));
+    TB200_CUDA_CHECK(cudaMallocAsync((void**)&dec, sizeof(uint32_t) * viterbi_decbits_words(d),
+                                     g_stream));
+    try {
+      launch_maxplus(E, P, best, inLens, labLens, d, g_stream);
+      launch_viterbi_lattice(E, P, LN, best, dec, labels, inLens, labLens, d, g_stream);
+    } catch (...) {
+      cudaFreeAsync(best, g_stream);
+      cudaFreeAsync(dec, g_stream);
+      throw;
+    }
+    TB200_CUDA_CHECK(cudaFreeAsync(best, g_stream));
+    TB200_CUDA_CHECK(cudaFreeAsync(dec, g_stream));
+  });
+}
+
+size_t tb200_log_norms_workspace_bytes(int B, int maxT, int maxU, int V) {
+  Dims d{B, maxT, maxU, V, 0};
+  Carver c(nullptr);
+  LogNormWs ws(c, d);
+  return c.total();
+}
+
+int tb200_log_norms(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+                    const int* inLens, const int* labLens, int B, int maxT, int maxU, int V,
+                    void* workspace, size_t workspaceBytes) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, 0};
+    check_dims(d);
+    need(workspaceBytes, tb200_log_norms_workspace_bytes(B, maxT, maxU, V), workspace);
+    Carver c(workspace);
+    LogNormWs ws(c, d);
+    log_norms_impl(E, P, LN, rowRef, maxP, inLens, labLens, d, ws);
+  });
+}
+
+size_t tb200_loss_forward_workspace_bytes(int B, int maxT, int maxU, int V) {
+  return tb200_log_norms_workspace_bytes(B, maxT, maxU, V);
+}
+
+int tb200_loss_forward(const float* E, const float* P, const int* labels, const int* inLens,
+                       const int* labLens, float* costs, float* alphas, float* LN,
+                       float* rowRef, float* maxP, float* lossSum, int B, int maxT, int maxU,
+                       int V, int blank, void* workspace, size_t workspaceBytes) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    need(workspaceBytes, tb200_loss_forward_workspace_bytes(B, maxT, maxU, V), workspace);
+    Carver c(workspace);
+    LogNormWs ws(c, d);
+    log_norms_impl(E, P, LN, rowRef, maxP, inLens, labLens, d, ws);
+    if (lossSum) {
+      TB200_CUDA_CHECK(cudaMemsetAsync(ws.ticket, 0, sizeof(unsigned), g_stream));
+      if (B == 0) TB200_CUDA_CHECK(cudaMemsetAsync(lossSum, 0, sizeof(float), g_stream));
+    }
+    launch_alpha(E, P, costs, alphas, LN, labels, inLens, labLens, d, lossSum,
+                 lossSum ? ws.ticket : nullptr, g_stream);
+  });
+}
+
+size_t tb200_loss_backward_workspace_bytes(int B, int maxT, int maxU, int V) {
+  Dims d{B, maxT, maxU, V, 0};
+  Carver c(nullptr);
+  BackwardWs ws(c, d);
+  return c.total();
+}
+
+int tb200_loss_backward(const float* E, const float* P, const int* labels, const int* inLens,
+                        const int* labLens, const float* alphas, const float* LN,
+                        const float* rowRef, const float* maxP, const float* deltas,
+                        float* egrads, float* pgrads, int B, int maxT, int maxU, int V,
+                        int blank, void* workspace, size_t workspaceBytes) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    need(workspaceBytes, tb200_loss_backward_workspace_bytes(B, maxT, maxU, V), workspace);
+    if (B == 0) return;
+    Carver c(workspace);
+    BackwardWs ws(c, d);
+    const int ldW = ld_w(d);
+    if (maxT > 0)
+      TB200_CUDA_CHECK(cudaMemsetAsync(ws.W, 0, sizeof(float) * (size_t)B * maxT * ldW, g_stream));
+    launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
+    launch_gamma_fused(E, P, alphas, LN, rowRef, maxP, labels, inLens, labLens, ws.W, ldW,
+                       ws.em, ws.eBlank, ws.pBlank, ws.pLabel, d, g_stream);
+    launch_egrad_simt(E, rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
+                      egrads, inLens, labLens, d, g_stream);
+    launch_pgrad_simt(E, rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,
+                      pgrads, inLens, labLens, d, g_stream);
+  });
+}
+
+size_t tb200_viterbi_decode_workspace_bytes(int B, int maxT, int maxU, int V) {
+  Dims d{B, maxT, maxU, V, 0};
+  Carver c(nullptr);
+  ViterbiWs ws(c, d);
+  LogNormWs lw(c, d);
+  return c.total();
+}
+
+int tb200_viterbi_decode(const float* E, const float* P, const int* inLens,
+                         const int* labLens, int* labels, int B, int maxT, int maxU, int V,
+                         int blank, void* workspace, size_t workspaceBytes) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    need(workspaceBytes, tb200_viterbi_decode_workspace_bytes(B, maxT, maxU, V), workspace);
+    if (B == 0 || maxT == 0 || maxU == 0) return;
+    Carver c(workspace);
+    ViterbiWs ws(c, d);
+    LogNormWs lw(c, d);
+    log_norms_impl(E, P, ws.LN, nullptr, nullptr, inLens, labLens, d, lw);
+    launch_maxplus(E, P, ws.best, inLens, labLens, d, g_stream);
+    launch_viterbi_lattice(E, P, ws.LN, ws.best, ws.decBits, labels, inLens, labLens, d,
+                           g_stream);
+  });
+}
+
+}  // extern "C"
+
+// ---- transducer.h-compatible C++ entry points --------------------------------
+
+namespace {
+void rethrow(int rc) {
+  if (rc == kOk) return;
+  if (rc == kErrInvalidArgument) throw std::invalid_argument(tb200_last_error());
+  throw std::runtime_error(tb200_last_error());
+}
+void require_cuda(bool useCuda) {
+  if (!useCuda) throw std::invalid_argument("Transducer not built with a CPU backend.");
+}
+}  // namespace
+
+void forward(const float* emissions, const float* predictions, float* costs, float* alphas,
+             const float* logNorms, const int* labels, const int* inputLengths,
+             const int* labelLengths, int batchSize, int maxInputLength, int maxLabelLength,
+             int alphabetSize, int blank, bool useCuda) {
+  require_cuda(useCuda);
+  rethrow(tb200_forward(emissions, predictions, costs, alphas, logNorms, labels, inputLengths,
+                        labelLengths, batchSize, maxInputLength, maxLabelLength, alphabetSize,
+                        blank));
+}
+
+void backward(const float* emissions, const float* predictions, float* egrads, float* pgrads,
+              float* lngrads, const float* alphas, const float* logNorms, const int* labels,
+              const int* inputLengths, const int* labelLengths, int batchSize,
+              int maxInputLength, int maxLabelLength, int alphabetSize, int blank,
+              bool useCuda) {
+  require_cuda(useCuda);
+  rethrow(tb200_backward(emissions, predictions, egrads, pgrads, lngrads, alphas, logNorms,
+                         labels, inputLengths, labelLengths, batchSize, maxInputLength,
+                         maxLabelLength, alphabetSize, blank));
+}
+
+void viterbi(const float* emissions, const float* predictions, const float* logNorms,
+             int* labels, const int* inputLengths, const int* labelLengths, int batchSize,
+             int maxInputLength, int maxLabelLength, int alphabetSize, int blank,
+             bool useCuda) {
+  require_cuda(useCuda);
+  rethrow(tb200_viterbi(emissions, predictions, logNorms, labels, inputLengths, labelLengths,
+                        batchSize, maxInputLength, maxLabelLength, alphabetSize, blank));
+}
