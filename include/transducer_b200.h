@@ -57,6 +57,17 @@ void* tb200_get_stream(void);
 int tb200_set_option(const char* key, int value);
 int tb200_get_option(const char* key, int* value);
 
+/* Launch accounting.  tb200_launch_count: kernels launched by this library since
+ * load.  With profiling enabled every launch is bracketed by CUDA events on its
+ * stream; tb200_profile_report synchronises them and writes one
+ * "kernel_name launches total_ms" line per kernel into buf (truncated to bufBytes,
+ * NUL-terminated) and returns the untruncated length.  No counterpart in the
+ * reference (it has wall-clock helpers only, transducer/benchmark_cuda.cu:59-74). */
+long long tb200_launch_count(void);
+int tb200_profile_enable(int on);
+int tb200_profile_reset(void);
+size_t tb200_profile_report(char* buf, size_t bufBytes);
+
 /* ---- the reference's three entry points ------------------------------------ */
 
 /* transducer/transducer.h:3-17 (`forward`, useCuda=true): alpha recursion.

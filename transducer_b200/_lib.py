@@ -27,6 +27,10 @@ SIGNATURES = {
     "tb200_get_stream": (_p, []),
     "tb200_set_option": (_i, [ctypes.c_char_p, _i]),
     "tb200_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
+    "tb200_launch_count": (ctypes.c_longlong, []),
+    "tb200_profile_enable": (_i, [_i]),
+    "tb200_profile_reset": (_i, []),
+    "tb200_profile_report": (_z, [ctypes.c_char_p, _z]),
     "tb200_forward": (_i, [_p] * 8 + [_i] * 5),
     "tb200_backward": (_i, [_p] * 10 + [_i] * 5),
     "tb200_viterbi": (_i, [_p] * 6 + [_i] * 5),
@@ -57,3 +61,14 @@ def check(rc):
         if rc in (1, 3):
             raise ValueError(msg)
         raise Tb200Error("tb200 error %d: %s" % (rc, msg))
+
+
+def profile_report():
+    """Per-kernel device time recorded since the last reset: {name: (launches, total_ms)}."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.tb200_profile_report(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        out[name] = (int(n), float(ms))
+    return out

@@ -6,6 +6,7 @@
 #include "../../include/transducer.h"
 #include "../../include/transducer_b200.h"
 #include "kernels.h"
+#include "profile.h"
 
 namespace tb200 {
 namespace {
@@ -143,6 +144,25 @@ int tb200_get_option(const char* key, int* value) {
   else if (!strcmp(key, "grad_passes")) *value = g_opt.grad_passes;
   else return fail(kErrInvalidArgument, std::string("unknown option: ") + key);
   return kOk;
+}
+
+long long tb200_launch_count(void) { return launch_count(); }
+int tb200_profile_enable(int on) {
+  profile_enable(on != 0);
+  return kOk;
+}
+int tb200_profile_reset(void) {
+  profile_reset();
+  return kOk;
+}
+size_t tb200_profile_report(char* buf, size_t bufBytes) {
+  const std::string s = profile_report();
+  if (buf && bufBytes > 0) {
+    const size_t n = s.size() < bufBytes - 1 ? s.size() : bufBytes - 1;
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return s.size();
 }
 
 int tb200_forward(const float* E, const float* P, float* costs, float* alphas,

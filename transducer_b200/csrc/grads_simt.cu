@@ -11,6 +11,7 @@
 // These fp32 FMA kernels take any vocabulary size and alignment; the tensor-core
 // kernels replace them for shapes TMA can address.
 #include "kernels.h"
+#include "profile.h"
 
 namespace tb200 {
 namespace {
@@ -189,11 +190,15 @@ void launch_egrad_simt(const float* E, const float* rowRef, const float* W, int 
                        cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.V <= 0) return;
   dim3 grid(div_up(d.V, BN), div_up(d.maxT, BM), d.B);
+  {
+  ScopedKernel sk("egrad_simt", stream);
   egrad_simt_kernel<<<grid, 256, 0, stream>>>(E, rowRef, W, ldW, expP, eBlank, deltas,
                                               egrads, inLens, labLens, d.maxT, d.maxU, d.V,
                                               d.blank);
+  }
   TB200_CHECK_LAUNCH();
   if (d.maxU > 1) {
+    ScopedKernel sk("egrad_label_scatter", stream);
     dim3 g2(div_up(d.maxT, 128), d.B);
     egrad_label_scatter_kernel<<<g2, 128, 0, stream>>>(em, labels, deltas, egrads, inLens,
                                                        labLens, d.maxT, d.maxU, d.V);
@@ -208,6 +213,7 @@ void launch_pgrad_simt(const float* E, const float* rowRef, const float* W, int 
                        cudaStream_t stream) {
   if (d.B <= 0 || d.maxU <= 0 || d.V <= 0) return;
   dim3 grid(div_up(d.V, BN), div_up(d.maxU, BM), d.B);
+  ScopedKernel sk("pgrad_simt", stream);
   pgrad_simt_kernel<<<grid, 256, 0, stream>>>(E, rowRef, W, ldW, expP, pBlank, pLabel,
                                               labels, deltas, pgrads, inLens, labLens,
                                               d.maxT, d.maxU, d.V, d.blank);

@@ -14,6 +14,7 @@
 //   reverse transducer/transducer_cpu.cpp:81-143  (transducer_cuda.cu:99-176)
 //   viterbi transducer/transducer_cpu.cpp:145-222 (transducer_cuda.cu:178-267)
 #include "kernels.h"
+#include "profile.h"
 
 namespace tb200 {
 namespace {
@@ -464,6 +465,7 @@ void launch_alpha(const float* E, const float* P, float* costs, float* alphas,
                   cudaStream_t stream) {
   if (d.B <= 0) return;
   const StripCfg cfg = pick_strips(d.maxU);
+  ScopedKernel sk("alpha_wavefront", stream);
 #define CALL(R, PF, NT)                                                              \
   alpha_kernel<R, PF, NT><<<d.B, cfg.threads, 0, stream>>>(                          \
       E, P, costs, alphas, LN, labels, inLens, labLens, d.B, d.maxT, d.maxU, d.V,   \
@@ -492,6 +494,7 @@ void launch_gamma_abi(const float* E, const float* P, float* egrads, float* pgra
   const StripCfg cfg = pick_strips(d.maxU);
   const size_t smem = sizeof(float) * (size_t)(d.maxT > 0 ? d.maxT : 1);
   if (smem > kMaxDynSmem) throw std::invalid_argument("input length above 51200 frames is not supported");
+  ScopedKernel sk("gamma_wavefront_abi", stream);
 #define CALL(R, PF, NT)                                                               \
   allow_smem(gamma_kernel<R, PF, NT, true>, smem);                                    \
   gamma_kernel<R, PF, NT, true><<<d.B, cfg.threads, smem, stream>>>(                  \
@@ -512,6 +515,7 @@ void launch_gamma_fused(const float* E, const float* P, const float* alphas,
   const StripCfg cfg = pick_strips(d.maxU);
   const size_t smem = sizeof(float) * (size_t)(d.maxT > 0 ? d.maxT : 1);
   if (smem > kMaxDynSmem) throw std::invalid_argument("input length above 51200 frames is not supported");
+  ScopedKernel sk("gamma_wavefront", stream);
 #define CALL(R, PF, NT)                                                               \
   allow_smem(gamma_kernel<R, PF, NT, false>, smem);                                   \
   gamma_kernel<R, PF, NT, false><<<d.B, cfg.threads, smem, stream>>>(                 \
@@ -533,6 +537,7 @@ void launch_viterbi_lattice(const float* E, const float* P, const float* LN,
   if (d.B <= 0 || d.maxT <= 0) return;
   const StripCfg cfg = pick_strips(d.maxU);
   const size_t smem = sizeof(int) * (size_t)d.maxU;
+  ScopedKernel sk("viterbi_wavefront", stream);
 #define CALL(R, PF, NT)                                                               \
   viterbi_kernel<R, PF, NT><<<d.B, cfg.threads, smem, stream>>>(                      \
       E, P, LN, best, decBits, labels, inLens, labLens, d.maxT, d.maxU, d.V, d.blank)

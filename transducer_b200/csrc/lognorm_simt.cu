@@ -8,6 +8,7 @@
 // for shapes the TMA-fed tensor-core kernel cannot take (vocabulary not a multiple
 // of 4 floats, unaligned base pointers).
 #include "kernels.h"
+#include "profile.h"
 
 namespace tb200 {
 namespace {
@@ -112,6 +113,7 @@ void launch_lognorm_exact(const float* E, const float* P, float* LN, const int* 
   if (d.maxT > 65535 || d.B > 65535)
     throw std::invalid_argument("exact log-normaliser: batch or frame count above 65535");
   dim3 grid(div_up(d.maxU, kWarpsPerCta), d.maxT, d.B);
+  ScopedKernel sk("lognorm_exact", stream);
   lognorm_exact_kernel<<<grid, kWarpsPerCta * 32, 0, stream>>>(E, P, LN, inLens, labLens,
                                                                d.maxT, d.maxU, d.V);
   TB200_CHECK_LAUNCH();
@@ -122,6 +124,7 @@ void launch_lognorm_exact_list(const float* E, const float* P, float* LN,
                                Dims d, cudaStream_t stream) {
   if (maxCount <= 0) return;
   const int ctas = 148 * 4;
+  ScopedKernel sk("lognorm_exact_list", stream);
   lognorm_exact_list_kernel<<<ctas, kWarpsPerCta * 32, 0, stream>>>(
       E, P, LN, cells, count, maxCount, d.maxT, d.maxU, d.V);
   TB200_CHECK_LAUNCH();
@@ -131,6 +134,7 @@ void launch_row_max(const float* X, float* rowMax, const int* lens, int lenOffse
                     int maxRows, int V, cudaStream_t stream) {
   if (B <= 0 || maxRows <= 0) return;
   dim3 grid(div_up(maxRows, 8), B);
+  ScopedKernel sk("row_max", stream);
   row_max_kernel<<<grid, 256, 0, stream>>>(X, rowMax, lens, lenOffset, maxRows, V);
   TB200_CHECK_LAUNCH();
 }
@@ -139,6 +143,7 @@ void launch_exp_rows(const float* P, float* expP, float* maxP, const int* labLen
                      int maxU, int V, cudaStream_t stream) {
   if (B <= 0 || maxU <= 0) return;
   dim3 grid(maxU, B);
+  ScopedKernel sk("exp_rows", stream);
   exp_rows_kernel<<<grid, 256, 0, stream>>>(P, expP, maxP, labLens, maxU, V);
   TB200_CHECK_LAUNCH();
 }

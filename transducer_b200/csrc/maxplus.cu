@@ -8,6 +8,7 @@
 // (max,+) has no tensor-core form; this is a register-tiled SIMT kernel: 2 issue
 // slots (FADD, FMNMX) per (t,u,v).
 #include "kernels.h"
+#include "profile.h"
 
 namespace tb200 {
 namespace {
@@ -75,6 +76,7 @@ void launch_maxplus(const float* E, const float* P, float* best, const int* inLe
                     const int* labLens, Dims d, cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 1) return;
   dim3 grid(div_up(d.maxU - 1, TN), div_up(d.maxT, TM), d.B);
+  ScopedKernel sk("maxplus", stream);
   maxplus_kernel<<<grid, 256, 0, stream>>>(E, P, best, inLens, labLens, d.maxT, d.maxU, d.V,
                                            d.blank);
   TB200_CHECK_LAUNCH();
