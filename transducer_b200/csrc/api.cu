@@ -65,8 +65,16 @@ struct Carver {
 int ld_w(const Dims& d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
 
 struct LogNormWs {
-  unsigned* ticket;
-  LogNormWs(Carver& c, const Dims&) { ticket = c.take<unsigned>(64); }
+  unsigned* ticket;  // alpha kernel's completion counter
+  int* status;       // [0] device error code, [1] nodes recomputed exactly
+  float* split;      // exp(P) hi/lo operand of the tensor-core path
+  float* maxPScratch;
+  LogNormWs(Carver& c, const Dims& d) {
+    ticket = c.take<unsigned>(16);
+    status = c.take<int>(16);
+    maxPScratch = c.take<float>((size_t)d.B * d.maxU);
+    split = c.take<float>(lognorm_umma_workspace_floats(d));
+  }
 };
 
 struct BackwardWs {
@@ -105,7 +113,21 @@ void need(size_t have, size_t want, const void* ws) {
 // Log-normalisers plus the row shifts.  With the exact path rowRef is the true row
 // maximum of E.
 void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
-                    const int* inLens, const int* labLens, const Dims& d, LogNormWs&) {
+                    const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
+  const bool can = lognorm_umma_supported(E, P, d);
+  if (g_opt.lognorm_path == 2 && !can)
+    throw std::invalid_argument(
+        "tensor-core log-normaliser needs alphabetSize % 4 == 0, alphabetSize >= 32, "
+        "maxLabelLength <= 256 and 16-byte aligned emissions");
+  if (can && g_opt.lognorm_path != 1) {
+    // the kernel needs somewhere to put the row shifts even if the caller does not want them
+    float* mp = maxP ? maxP : ws.maxPScratch;
+    if (!rowRef) throw std::invalid_argument("rowRef must not be null");
+    launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split, ws.status, g_stream);
+    return;
+  }
   launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
   if (rowRef) launch_row_max(E, rowRef, inLens, 0, d.B, d.maxT, d.V, g_stream);
   if (maxP) launch_row_max(P, maxP, labLens, 1, d.B, d.maxU, d.V, g_stream);
@@ -313,7 +335,7 @@ int tb200_viterbi_decode(const float* E, const float* P, const int* inLens,
     Carver c(workspace);
     ViterbiWs ws(c, d);
     LogNormWs lw(c, d);
-    log_norms_impl(E, P, ws.LN, nullptr, nullptr, inLens, labLens, d, lw);
+    log_norms_impl(E, P, ws.LN, ws.rowRef, ws.maxP, inLens, labLens, d, lw);
     launch_maxplus(E, P, ws.best, inLens, labLens, d, g_stream);
     launch_viterbi_lattice(E, P, ws.LN, ws.best, ws.decBits, labels, inLens, labLens, d,
                            g_stream);

@@ -69,6 +69,16 @@ void launch_row_max(const float* X, float* rowMax, const int* lens, int lenOffse
 void launch_exp_rows(const float* P, float* expP, float* maxP, const int* labLens,
                      int B, int maxU, int V, cudaStream_t stream);
 
+// ---- lognorm_umma.cu ----------------------------------------------------------
+// Tensor-core log-normalisers (one pass over E).  Usable when lognorm_umma_supported();
+// splitWs holds lognorm_umma_workspace_floats(d) floats, status two ints (zeroed by the
+// caller): [0] first device-side error code (0 = none), [1] nodes recomputed exactly.
+bool lognorm_umma_supported(const float* E, const float* P, Dims d);
+size_t lognorm_umma_workspace_floats(Dims d);
+void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+                         const int* inLens, const int* labLens, Dims d, float* splitWs,
+                         int* status, cudaStream_t stream);
+
 // ---- maxplus.cu --------------------------------------------------------------
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,
                     const int* labLens, Dims d, cudaStream_t stream);

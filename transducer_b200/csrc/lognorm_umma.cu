@@ -1,0 +1,437 @@
+// Log-normalisers as an exp-factored tensor-core contraction (tcgen05 / TMEM / TMA).
+//
+//   LN[b,t,u] = log( sum_v exp(E[b,t,v]-ref[b,t]) * exp(P[b,u,v]-maxP[b,u]) ) + ref[b,t] + maxP[b,u]
+//
+// which is what the reference computes with torch ops (transducer/torch_binding.py:35-40:
+// row maxima, exp, bmm, log) -- here in ONE pass over E and without storing exp(E).
+//
+// Tile: 128 frames of one utterance (UMMA M=128) x all label positions (N = maxU rounded
+// up to 16, <= 256) x the whole vocabulary in K-chunks of 32 floats.
+//
+// Roles inside a CTA (192 threads):
+//   warps 0-3  operand transform, later epilogue.  Thread r owns frame r of the tile
+//              (= TMEM lane r): reads its 128-byte row of the raw E chunk from shared
+//              memory, computes x = exp(E - ref), splits x = hi + lo with hi exactly
+//              representable in TF32, and stores hi/lo straight into TENSOR MEMORY
+//              (the A operand of the MMA is read from TMEM, so the transformed tile
+//              never goes back through shared memory).
+//   warp 4     TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage.
+//   warp 5     MMA issuer: per 8-wide k-step three kind::tf32 MMAs
+//              hi*Bhi + lo*Bhi + hi*Blo into one fp32 accumulator in TMEM (the 3xTF32
+//              split reproduces fp32 products to ~2^-21 relative).
+//
+// ref[b,t] is NOT the row maximum (that would cost a second pass over E): it is the
+// maximum of the first 32 entries of the row.  Any reference gives the same LN as long
+// as the factored sum neither overflows nor underflows in fp32; nodes where it does
+// (sum not in [1e-30, 1e30], or non-finite) are marked and recomputed by the exact fp32
+// SIMT logsumexp in lognorm_fixup_kernel.
+#include <cuda.h>
+
+#include "kernels.h"
+#include "profile.h"
+#include "sm100.cuh"
+
+namespace tb200 {
+
+namespace sm100 {
+
+CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    TB200_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn)
+      throw CudaError("cuTensorMapEncodeTiled is not available from this driver");
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1Bytes, stride2Bytes};
+  const cuuint32_t box[3] = {32, box1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult rc = encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    throw CudaError("cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+  return m;
+}
+
+}  // namespace sm100
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileM = 128;
+constexpr int kChunkK = 32;                       // floats per K-chunk = one 128-byte swizzle row
+constexpr int kRawBytes = kTileM * kChunkK * 4;   // 16 KB
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kSumLo = 1e-30f, kSumHi = 1e30f;
+
+// ---------------------------------------------------------------------------------
+// exp(P - maxP) split into TF32 hi/lo, zero-padded to [B][nPad][kPad]
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) expp_split_kernel(
+    const float* __restrict__ P, float* __restrict__ bHi, float* __restrict__ bLo,
+    float* __restrict__ maxP, const int* __restrict__ labLens, int maxU, int V, int nPad,
+    int kPad) {
+  __shared__ float red[8];
+  const int b = blockIdx.y, u = blockIdx.x;
+  const int U = min(labLens[b] + 1, maxU);
+  float* hi = bHi + ((i64)b * nPad + u) * kPad;
+  float* lo = bLo + ((i64)b * nPad + u) * kPad;
+  if (u >= U) {
+    for (int v = threadIdx.x; v < kPad; v += blockDim.x) { hi[v] = 0.0f; lo[v] = 0.0f; }
+    if (u < maxU && threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = 0.0f;
+    return;
+  }
+  const float* p = P + ((i64)b * maxU + u) * V;
+  float m = neg_inf();
+  for (int v = threadIdx.x; v < V; v += blockDim.x) m = fmaxf(m, p[v]);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = fmaxf(m, red[k]);
+  for (int v = threadIdx.x; v < kPad; v += blockDim.x) {
+    float h = 0.0f, l = 0.0f;
+    if (v < V) {
+      const float x = expf(p[v] - m);
+      h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+      l = tf32_round(x - h);
+    }
+    hi[v] = h;
+    lo[v] = l;
+  }
+  if (threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = m;
+}
+
+// ---------------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------------
+struct LnParams {
+  float* LN;
+  float* rowRef;
+  const float* maxP;
+  const int* inLens;
+  const int* labLens;
+  int* status;       // [0] first error code, [1] number of nodes handed to the fix-up
+  int maxT, maxU, V, nPad, stages, tmemCols, accCols;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
+    const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
+    const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
+  const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
+  const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
+  if (t0 >= T || U <= 0) return;  // before any allocation or barrier
+
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
+                                             ~uintptr_t(1023));
+  const int S = p.stages;
+  const int bBytes = p.nPad * kChunkK * 4;
+  const int stageBytes = kRawBytes + 2 * bBytes;
+  __shared__ uint64_t barFull[4], barReady[4], barDone[4], barAcc;
+  __shared__ uint32_t tmemBase;
+  __shared__ int abortFlag;
+  __shared__ float sMaxP[256];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nChunks = (p.V + kChunkK - 1) / kChunkK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&barFull[s], 1);
+      mbar_init(&barReady[s], 4);
+      mbar_init(&barDone[s], 1);
+    }
+    mbar_init(&barAcc, 1);
+    abortFlag = 0;
+    fence_mbar_init();
+  }
+  for (int u = threadIdx.x; u < p.nPad; u += kThreads)
+    sMaxP[u] = (u < U) ? p.maxP[(i64)b * p.maxU + u] : 0.0f;
+  if (warp == 5) {
+    tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tBase = tmemBase;
+  const uint32_t tA = tBase + (uint32_t)p.accCols;  // operand stages: [hi 32 | lo 32] columns each
+  volatile int* abortp = &abortFlag;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmE);
+      tma_prefetch_desc(&tmHi);
+      tma_prefetch_desc(&tmLo);
+      int issued = 0;
+      for (int c = 0; c < nChunks; ++c) {
+        const int s = c % S;
+        if (c >= S && !mbar_wait(&barDone[s], ((c / S) - 1) & 1, abortp, p.status,
+                                 kStatusTimeoutStageFree))
+          break;
+        uint8_t* st = smem + (size_t)s * stageBytes;
+        mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
+        tma_load_3d(st, &tmE, &barFull[s], c * kChunkK, t0, b);
+        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], c * kChunkK, 0, b);
+        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], c * kChunkK, 0, b);
+        issued = c + 1;
+      }
+      if (*abortp) {
+        // after an abort: give the copies still in flight a bounded time to land
+        // before the CTA's shared memory is released
+        for (int c = max(0, issued - S); c < issued; ++c) {
+          const unsigned long long t1 = global_timer_ns();
+          while (!mbar_try_wait(&barFull[c % S], (c / S) & 1) &&
+                 global_timer_ns() - t1 < 50000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
+      bool ok = true;
+      for (int c = 0; c < nChunks && ok; ++c) {
+        const int s = c % S;
+        const uint32_t ph = (c / S) & 1;
+        ok = mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma) &&
+             mbar_wait(&barReady[s], ph, abortp, p.status, kStatusTimeoutOperand);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t bHi = smem_u32(smem + (size_t)s * stageBytes + kRawBytes);
+        const uint32_t bLo = bHi + (uint32_t)bBytes;
+        const uint32_t aHi = tA + (uint32_t)(s * 64), aLo = aHi + 32;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t dHi = smem_desc_sw128(bHi + k * 32, 16, 1024);
+          const uint64_t dLo = smem_desc_sw128(bLo + k * 32, 16, 1024);
+          mma_tf32_ts(tBase, aHi + k * 8, dHi, idesc, (c | k) ? 1u : 0u);
+          mma_tf32_ts(tBase, aLo + k * 8, dHi, idesc, 1u);
+          mma_tf32_ts(tBase, aHi + k * 8, dLo, idesc, 1u);
+        }
+        mma_commit(&barDone[s]);
+      }
+      if (ok) mma_commit(&barAcc);
+    }
+  } else {
+    // ---------------- operand transform (thread = frame = TMEM lane) ----------------
+    const int r = threadIdx.x;  // 0..127
+    const uint32_t laneAddr = (uint32_t)(warp * 32) << 16;
+    float ref = 0.0f;
+    bool ok = true;
+    for (int c = 0; c < nChunks && ok; ++c) {
+      const int s = c % S;
+      ok = mbar_wait(&barFull[s], (c / S) & 1, abortp, p.status, kStatusTimeoutTma);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
+      if (!ok) break;
+      const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
+      float x[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 q = *reinterpret_cast<const float4*>(row + ((j ^ (r & 7)) << 4));
+        x[4 * j] = q.x; x[4 * j + 1] = q.y; x[4 * j + 2] = q.z; x[4 * j + 3] = q.w;
+      }
+      const int kLeft = p.V - c * kChunkK;  // valid columns in this chunk
+      if (c == 0) {
+        float m = neg_inf();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < kLeft) m = fmaxf(m, x[j]);
+        // a -inf/NaN prefix would poison every term; fall back to 0 and let the
+        // range check route the row to the exact path if needed
+        ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
+      }
+      const float nref = -ref * kLog2e;
+      uint32_t hi[32], lo[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float e = exp2f(fmaf(x[j], kLog2e, nref));
+        if (j >= kLeft) e = 0.0f;
+        const uint32_t h = __float_as_uint(e) & 0xffffe000u;
+        hi[j] = h;
+        lo[j] = __float_as_uint(e - __uint_as_float(h));
+      }
+      const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
+      tmem_st16(dst, reinterpret_cast<const uint32_t(&)[16]>(hi[0]));
+      tmem_st16(dst + 16, reinterpret_cast<const uint32_t(&)[16]>(hi[16]));
+      tmem_st16(dst + 32, reinterpret_cast<const uint32_t(&)[16]>(lo[0]));
+      tmem_st16(dst + 48, reinterpret_cast<const uint32_t(&)[16]>(lo[16]));
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&barReady[s]);
+    }
+    // ---------------- epilogue ----------------
+    if (ok) ok = mbar_wait(&barAcc, 0, abortp, p.status, kStatusTimeoutMma);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int t = t0 + r;
+      float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
+      int flagged = 0;
+      for (int u0 = 0; u0 < p.nPad; u0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tBase + laneAddr + (uint32_t)u0, v);
+        tmem_wait_ld();
+        if (t < T) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int u = u0 + j;
+            if (u < U) {
+              const float acc = __uint_as_float(v[j]);
+              float ln = (logf(acc) + ref) + sMaxP[u];
+              if (!(acc >= kSumLo && acc <= kSumHi)) {
+                ln = __int_as_float(0x7fc00000);  // marker: recompute exactly
+                ++flagged;
+              }
+              out[u] = ln;
+            }
+          }
+        }
+      }
+      if (t < T) p.rowRef[(i64)b * p.maxT + t] = ref;
+      if (flagged) atomicAdd(&p.status[1], flagged);
+    }
+  }
+
+  // ---------------- teardown (all roles, also after an abort) ----------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 5) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
+}
+
+// Recomputes marked nodes (NaN in LN) with the exact fp32 logsumexp.  Each warp scans
+// 32 consecutive nodes per iteration; marked ones are evaluated by the whole warp.
+__global__ void __launch_bounds__(256) lognorm_fixup_kernel(
+    const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ LN,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int B, int maxT, int maxU,
+    int V) {
+  const int lane = threadIdx.x & 31;
+  const i64 warpsTotal = (i64)gridDim.x * (blockDim.x >> 5);
+  const i64 cells = (i64)B * maxT * maxU;
+  for (i64 base = ((i64)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; base < cells;
+       base += warpsTotal * 32) {
+    const i64 idx = base + lane;
+    bool marked = false;
+    if (idx < cells) {
+      const int u = (int)(idx % maxU);
+      const int t = (int)((idx / maxU) % maxT);
+      const int b = (int)(idx / ((i64)maxU * maxT));
+      if (t < min(inLens[b], maxT) && u < min(labLens[b] + 1, maxU)) {
+        const float v = LN[idx];
+        marked = (v != v);
+      }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, marked);
+    while (todo) {
+      const int src = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const i64 k = base + src;
+      const int u = (int)(k % maxU);
+      const int t = (int)((k / maxU) % maxT);
+      const int b = (int)(k / ((i64)maxU * maxT));
+      const float* er = E + ((i64)b * maxT + t) * V;
+      const float* pr = P + ((i64)b * maxU + u) * V;
+      float m = neg_inf();
+      for (int v = lane; v < V; v += 32) m = fmaxf(m, er[v] + pr[v]);
+      m = warp_max(m);
+      float s = 0.0f;
+      if (m != neg_inf() && m != pos_inf())
+        for (int v = lane; v < V; v += 32) s += expf((er[v] + pr[v]) - m);
+      s = warp_sum(s);
+      if (lane == 0) LN[k] = logf(s) + m;
+    }
+  }
+}
+
+int pow2_at_least(int x) {
+  int p = 32;
+  while (p < x) p <<= 1;
+  return p;
+}
+
+}  // namespace
+
+bool lognorm_umma_supported(const float* E, const float* P, Dims d) {
+  (void)P;
+  return d.V % 4 == 0 && d.V >= 32 && d.maxU >= 1 && d.maxU <= 256 &&
+         (reinterpret_cast<uintptr_t>(E) & 15) == 0 && d.B <= 65535;
+}
+
+size_t lognorm_umma_workspace_floats(Dims d) {
+  const size_t nPad = (size_t)round_up64(d.maxU > 0 ? d.maxU : 1, 16);
+  const size_t kPad = (size_t)round_up64(d.V, kChunkK);
+  return 2 * (size_t)d.B * nPad * kPad;
+}
+
+void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+                         const int* inLens, const int* labLens, Dims d, float* splitWs,
+                         int* status, cudaStream_t stream) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  const int nPad = (int)round_up64(d.maxU, 16);
+  const int kPad = (int)round_up64(d.V, kChunkK);
+  float* bHi = splitWs;
+  float* bLo = splitWs + (size_t)d.B * nPad * kPad;
+  {
+    ScopedKernel sk("expp_split", stream);
+    expp_split_kernel<<<dim3(nPad, d.B), 256, 0, stream>>>(P, bHi, bLo, maxP, labLens, d.maxU,
+                                                           d.V, nPad, kPad);
+  }
+  TB200_CHECK_LAUNCH();
+
+  const CUtensorMap tmE = make_tmap_f32_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B,
+                                           (uint64_t)d.V * 4, (uint64_t)d.maxT * d.V * 4, kTileM);
+  const CUtensorMap tmHi = make_tmap_f32_3d(bHi, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
+                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPad);
+  const CUtensorMap tmLo = make_tmap_f32_3d(bLo, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
+                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPad);
+
+  LnParams p;
+  p.LN = LN; p.rowRef = rowRef; p.maxP = maxP; p.inLens = inLens; p.labLens = labLens;
+  p.status = status;
+  p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.nPad = nPad;
+  const int stageBytes = kRawBytes + 2 * nPad * kChunkK * 4;
+  // two stages let two CTAs share an SM (their prologues/epilogues overlap) when the
+  // label axis is short; a third stage when only one CTA fits anyway
+  int stages = 2;
+  const bool twoPerSm = (2 * (2 * stageBytes + 2048) <= 220 * 1024) && (nPad + 2 * 64 <= 256);
+  if (!twoPerSm && 3 * stageBytes + 2048 <= 220 * 1024 && nPad + 3 * 64 <= 512) stages = 3;
+  p.stages = stages;
+  p.accCols = nPad;
+  p.tmemCols = pow2_at_least(nPad + stages * 64);
+  size_t smem = (size_t)stages * stageBytes + 1024;
+  if (!twoPerSm && smem < 120 * 1024) smem = 120 * 1024;  // keep a 512-column CTA alone on its SM
+  TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(div_up(d.maxT, kTileM), d.B);
+  {
+    ScopedKernel sk("lognorm_umma", stream);
+    lognorm_umma_kernel<<<grid, kThreads, smem, stream>>>(tmE, tmHi, tmLo, p);
+  }
+  TB200_CHECK_LAUNCH();
+  {
+    ScopedKernel sk("lognorm_fixup", stream);
+    lognorm_fixup_kernel<<<148 * 2, 256, 0, stream>>>(E, P, LN, inLens, labLens, d.B, d.maxT,
+                                                      d.maxU, d.V);
+  }
+  TB200_CHECK_LAUNCH();
+}
+
+}  // namespace tb200
