@@ -8,17 +8,21 @@
 // Tile: 128 frames of one utterance (UMMA M=128) x all label positions (N = maxU rounded
 // up to 16, <= 256) x the whole vocabulary in K-chunks of 32 floats.
 //
-// Roles inside a CTA (192 threads):
-//   warps 0-3  operand transform, later epilogue.  Thread r owns frame r of the tile
-//              (= TMEM lane r): reads its 128-byte row of the raw E chunk from shared
-//              memory, computes x = exp(E - ref), splits x = hi + lo with hi exactly
-//              representable in TF32, and stores hi/lo straight into TENSOR MEMORY
-//              (the A operand of the MMA is read from TMEM, so the transformed tile
-//              never goes back through shared memory).
-//   warp 4     TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage.
-//   warp 5     MMA issuer: per 8-wide k-step three kind::tf32 MMAs
-//              hi*Bhi + lo*Bhi + hi*Blo into one fp32 accumulator in TMEM (the 3xTF32
-//              split reproduces fp32 products to ~2^-21 relative).
+// Roles inside a CTA (one CTA per SM, 10 or 14 warps):
+//   warps 0-3   operand transform.  Thread r owns frame r of the tile (= TMEM lane r):
+//               reads its 128-byte row of the raw E chunk from shared memory, computes
+//               x = exp(E - ref), splits x = hi + lo with hi exactly representable in
+//               TF32, and stores hi/lo straight into TENSOR MEMORY (the A operand of the
+//               MMA is read from TMEM, so the transformed tile never goes back through
+//               shared memory).
+//   warps 4-7   (and 8-11 when the label axis exceeds 128) accumulator drain + epilogue:
+//               after every kGroup chunks they add the TMEM accumulator into fp32
+//               registers (round-to-nearest) and hand the accumulator back, so the tensor
+//               core's truncating accumulation never runs over more than 24 steps.
+//   next warp   TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage.
+//   last warp   MMA issuer: per 8-wide k-step three kind::tf32 MMAs
+//               hi*Bhi + lo*Bhi + hi*Blo into the current accumulator (the 3xTF32 split
+//               reproduces fp32 products to ~2^-21 relative).
 //
 // ref[b,t] is NOT the row maximum (that would cost a second pass over E): it is the
 // maximum of the first 32 entries of the row.  Any reference gives the same LN as long
@@ -26,6 +30,8 @@
 // (sum not in [1e-30, 1e30], or non-finite) are marked and recomputed by the exact fp32
 // SIMT logsumexp in lognorm_fixup_kernel.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "kernels.h"
 #include "profile.h"
@@ -73,7 +79,6 @@ using namespace sm100;
 constexpr int kTileM = 128;
 constexpr int kChunkK = 32;                       // floats per K-chunk = one 128-byte swizzle row
 constexpr int kRawBytes = kTileM * kChunkK * 4;   // 16 KB
-constexpr int kThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kSumLo = 1e-30f, kSumHi = 1e30f;
 
@@ -126,12 +131,23 @@ struct LnParams {
   const int* inLens;
   const int* labLens;
   int* status;       // [0] first error code, [1] number of nodes handed to the fix-up
-  int maxT, maxU, V, nPad, stages, tmemCols, accCols;
+  int maxT, maxU, V, nPad, stages, nAcc, tmemCols;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
+// Chunks per accumulation group.  The tensor core adds into its fp32 accumulator with
+// truncation: measured on B200, every tcgen05.mma step loses ~2^-24 of the running sum
+// (always downward), i.e. -2e-4 on LN after the 3750 steps of a 10000-word vocabulary.
+// So an accumulator only ever sees kGroup chunks (12*kGroup steps); the drain warps then
+// add it, round-to-nearest, into fp32 registers and the MMA starts a fresh accumulator.
+constexpr int kGroup = 2;
+constexpr int kDrainCols = 128;  // accumulator columns owned by one drain warpgroup
+
+template <int NDRAIN>
+__global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
     const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
+  constexpr int kProducerWarp = 4 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
+  constexpr int kThreads = (6 + 4 * NDRAIN) * 32;
   const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
   if (t0 >= T || U <= 0) return;  // before any allocation or barrier
@@ -139,16 +155,18 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
                                              ~uintptr_t(1023));
-  const int S = p.stages;
+  const int S = p.stages, nAcc = p.nAcc;
   const int bBytes = p.nPad * kChunkK * 4;
   const int stageBytes = kRawBytes + 2 * bBytes;
-  __shared__ uint64_t barFull[4], barReady[4], barDone[4], barAcc;
+  __shared__ uint64_t barFull[4], barReady[4], barDone[4], barAccFull[2], barAccEmpty[2], barRef;
   __shared__ uint32_t tmemBase;
   __shared__ int abortFlag;
   __shared__ float sMaxP[256];
+  __shared__ float sRef[kTileM];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nChunks = (p.V + kChunkK - 1) / kChunkK;
+  const int nGroups = (nChunks + kGroup - 1) / kGroup;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -156,24 +174,28 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
       mbar_init(&barReady[s], 4);
       mbar_init(&barDone[s], 1);
     }
-    mbar_init(&barAcc, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&barAccFull[a], 1);
+      mbar_init(&barAccEmpty[a], 4 * NDRAIN);
+    }
+    mbar_init(&barRef, 4);
     abortFlag = 0;
     fence_mbar_init();
   }
   for (int u = threadIdx.x; u < p.nPad; u += kThreads)
     sMaxP[u] = (u < U) ? p.maxP[(i64)b * p.maxU + u] : 0.0f;
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tBase = tmemBase;
-  const uint32_t tA = tBase + (uint32_t)p.accCols;  // operand stages: [hi 32 | lo 32] columns each
+  const uint32_t tBase = tmemBase;                          // accumulators: nAcc x nPad columns
+  const uint32_t tA = tBase + (uint32_t)(nAcc * p.nPad);    // operand stages: [hi 32 | lo 32] each
   volatile int* abortp = &abortFlag;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmE);
@@ -203,34 +225,38 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
       bool ok = true;
       for (int c = 0; c < nChunks && ok; ++c) {
-        const int s = c % S;
+        const int s = c % S, g = c / kGroup, a = g % nAcc;
         const uint32_t ph = (c / S) & 1;
-        ok = mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma) &&
+        if (c % kGroup == 0 && g >= nAcc)
+          ok = mbar_wait(&barAccEmpty[a], ((g / nAcc) - 1) & 1, abortp, p.status,
+                         kStatusTimeoutStageFree);
+        ok = ok && mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma) &&
              mbar_wait(&barReady[s], ph, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
         const uint32_t bHi = smem_u32(smem + (size_t)s * stageBytes + kRawBytes);
         const uint32_t bLo = bHi + (uint32_t)bBytes;
         const uint32_t aHi = tA + (uint32_t)(s * 64), aLo = aHi + 32;
+        const uint32_t dAcc = tBase + (uint32_t)(a * p.nPad);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint64_t dHi = smem_desc_sw128(bHi + k * 32, 16, 1024);
           const uint64_t dLo = smem_desc_sw128(bLo + k * 32, 16, 1024);
-          mma_tf32_ts(tBase, aHi + k * 8, dHi, idesc, (c | k) ? 1u : 0u);
-          mma_tf32_ts(tBase, aLo + k * 8, dHi, idesc, 1u);
-          mma_tf32_ts(tBase, aHi + k * 8, dLo, idesc, 1u);
+          mma_tf32_ts(dAcc, aHi + k * 8, dHi, idesc, ((c % kGroup) | k) ? 1u : 0u);
+          mma_tf32_ts(dAcc, aLo + k * 8, dHi, idesc, 1u);
+          mma_tf32_ts(dAcc, aHi + k * 8, dLo, idesc, 1u);
         }
         mma_commit(&barDone[s]);
+        if (c % kGroup == kGroup - 1 || c == nChunks - 1) mma_commit(&barAccFull[a]);
       }
-      if (ok) mma_commit(&barAcc);
     }
-  } else {
+  } else if (warp < 4) {
     // ---------------- operand transform (thread = frame = TMEM lane) ----------------
     const int r = threadIdx.x;  // 0..127
     const uint32_t laneAddr = (uint32_t)(warp * 32) << 16;
@@ -256,6 +282,8 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
         // a -inf/NaN prefix would poison every term; fall back to 0 and let the
         // range check route the row to the exact path if needed
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
+        sRef[r] = ref;
+        if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
       }
       const float nref = -ref * kLog2e;
       uint32_t hi[32], lo[32];
@@ -275,37 +303,65 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&barReady[s]);
+      if (lane == 0) {
+        mbar_arrive(&barReady[s]);
+        if (c == 0) mbar_arrive(&barRef);
+      }
     }
-    // ---------------- epilogue ----------------
-    if (ok) ok = mbar_wait(&barAcc, 0, abortp, p.status, kStatusTimeoutMma);
+  } else {
+    // ---------------- accumulator drain + epilogue ----------------
+    const int h = (warp - 4) >> 2;               // which 128-column slice
+    const int q = warp & 3;                      // TMEM lane quarter this warp may touch
+    const int r = q * 32 + lane;
+    const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
+    const int c0 = h * kDrainCols, c1 = min(p.nPad, c0 + kDrainCols);
+    float sum[kDrainCols];
+#pragma unroll
+    for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
+    bool ok = true;
+    for (int g = 0; g < nGroups && ok; ++g) {
+      const int a = g % nAcc;
+      ok = mbar_wait(&barAccFull[a], (g / nAcc) & 1, abortp, p.status, kStatusTimeoutMma);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t src = tBase + laneAddr + (uint32_t)(a * p.nPad + c0);
+#pragma unroll
+      for (int i = 0; i < kDrainCols / 16; ++i) {
+        if (c0 + i * 16 < c1) {
+          uint32_t v[16];
+          tmem_ld16(src + i * 16, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[i * 16 + j] += __uint_as_float(v[j]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&barAccEmpty[a]);
+    }
+    if (ok) ok = mbar_wait(&barRef, 0, abortp, p.status, kStatusTimeoutOperand);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
-      tc_fence_after();
       const int t = t0 + r;
-      float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
+      const float ref = sRef[r];
       int flagged = 0;
-      for (int u0 = 0; u0 < p.nPad; u0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(tBase + laneAddr + (uint32_t)u0, v);
-        tmem_wait_ld();
-        if (t < T) {
+      if (t < T) {
+        float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int u = u0 + j;
-            if (u < U) {
-              const float acc = __uint_as_float(v[j]);
-              float ln = (logf(acc) + ref) + sMaxP[u];
-              if (!(acc >= kSumLo && acc <= kSumHi)) {
-                ln = __int_as_float(0x7fc00000);  // marker: recompute exactly
-                ++flagged;
-              }
-              out[u] = ln;
+        for (int j = 0; j < kDrainCols; ++j) {
+          const int u = c0 + j;
+          if (u < U) {
+            const float acc = sum[j];
+            float ln = (logf(acc) + ref) + sMaxP[u];
+            if (!(acc >= kSumLo && acc <= kSumHi)) {
+              ln = __int_as_float(0x7fc00000);  // marker: recompute exactly
+              ++flagged;
             }
+            out[u] = ln;
           }
         }
       }
-      if (t < T) p.rowRef[(i64)b * p.maxT + t] = ref;
       if (flagged) atomicAdd(&p.status[1], flagged);
     }
   }
@@ -314,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) lognorm_umma_kernel(
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
 }
 
 // Recomputes marked nodes (NaN in LN) with the exact fp32 logsumexp.  Each warp scans
@@ -408,22 +464,34 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   p.status = status;
   p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.nPad = nPad;
   const int stageBytes = kRawBytes + 2 * nPad * kChunkK * 4;
-  // two stages let two CTAs share an SM (their prologues/epilogues overlap) when the
-  // label axis is short; a third stage when only one CTA fits anyway
-  int stages = 2;
-  const bool twoPerSm = (2 * (2 * stageBytes + 2048) <= 220 * 1024) && (nPad + 2 * 64 <= 256);
-  if (!twoPerSm && 3 * stageBytes + 2048 <= 220 * 1024 && nPad + 3 * 64 <= 512) stages = 3;
+  // Tensor memory (512 columns): accumulators first, then the operand stages (64 columns
+  // each).  Two accumulators let the MMA run while the previous group is drained; a wide
+  // label axis leaves room for only one.  One CTA per SM (the kernel asks for > 114 KB).
+  const int maxStagesSmem = (int)((220 * 1024 - 2048) / stageBytes);
+  int nAcc = 2;
+  int stages = std::min(4, std::min(maxStagesSmem, (512 - 2 * nPad) / 64));
+  if (stages < 2) {
+    nAcc = 1;
+    stages = std::min(4, std::min(maxStagesSmem, (512 - nPad) / 64));
+  }
+  if (stages < 1) throw std::invalid_argument("label axis too long for the tensor-core log-normaliser");
   p.stages = stages;
-  p.accCols = nPad;
-  p.tmemCols = pow2_at_least(nPad + stages * 64);
+  p.nAcc = nAcc;
+  p.tmemCols = pow2_at_least(nAcc * nPad + stages * 64);
   size_t smem = (size_t)stages * stageBytes + 1024;
-  if (!twoPerSm && smem < 120 * 1024) smem = 120 * 1024;  // keep a 512-column CTA alone on its SM
-  TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (smem < 120 * 1024) smem = 120 * 1024;
   dim3 grid(div_up(d.maxT, kTileM), d.B);
   {
     ScopedKernel sk("lognorm_umma", stream);
-    lognorm_umma_kernel<<<grid, kThreads, smem, stream>>>(tmE, tmHi, tmLo, p);
+    if (nPad <= kDrainCols) {
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel<1>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      lognorm_umma_kernel<1><<<grid, 10 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+    } else {
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel<2>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      lognorm_umma_kernel<2><<<grid, 14 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+    }
   }
   TB200_CHECK_LAUNCH();
   {
