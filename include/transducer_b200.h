@@ -111,28 +111,31 @@ int tb200_log_norms(const float* emissions, const float* predictions, float* log
                     size_t workspaceBytes);
 
 /* transducer/torch_binding.py:25-58 (Transducer.forward): log-normalisers + alpha
- * recursion.  Outputs costs[B], alphas, logNorms, rowRef, maxP (kept by the caller
- * for the backward call).  If lossSum is not NULL it receives sum_b costs[b]
- * (added in index order by the last CTA to finish). */
+ * recursion.  Writes costs[B]; if lossSum is not NULL it receives sum_b costs[b]
+ * (added in index order by the last CTA to finish).  What the reference keeps for
+ * its backward pass as autograd-saved tensors (alphas, log_norms, expEs, ...,
+ * torch_binding.py:52-55) is kept here in `saved`, an opaque device buffer of
+ * tb200_loss_saved_bytes() owned by the caller; exp(E) is not among it. */
+size_t tb200_loss_saved_bytes(int batchSize, int maxInputLength, int maxLabelLength,
+                              int alphabetSize);
 size_t tb200_loss_forward_workspace_bytes(int batchSize, int maxInputLength,
                                           int maxLabelLength, int alphabetSize);
 int tb200_loss_forward(const float* emissions, const float* predictions,
                        const int* labels, const int* inputLengths,
-                       const int* labelLengths, float* costs, float* alphas,
-                       float* logNorms, float* rowRef, float* maxP, float* lossSum,
-                       int batchSize, int maxInputLength, int maxLabelLength,
-                       int alphabetSize, int blank, void* workspace,
-                       size_t workspaceBytes);
+                       const int* labelLengths, float* costs, float* lossSum,
+                       void* saved, size_t savedBytes, int batchSize,
+                       int maxInputLength, int maxLabelLength, int alphabetSize,
+                       int blank, void* workspace, size_t workspaceBytes);
 
 /* transducer/torch_binding.py:60-90 (Transducer.backward): reverse sweep + dense
- * gradient contractions + deltas scaling.  Every element of egrads [B,maxT,V] and
- * pgrads [B,maxU,V] is written (zeros in the padding). */
+ * gradient contractions + deltas scaling, from the same inputs and the `saved`
+ * buffer of the forward call.  Every element of egrads [B,maxT,V] and pgrads
+ * [B,maxU,V] is written (zeros in the padding). */
 size_t tb200_loss_backward_workspace_bytes(int batchSize, int maxInputLength,
                                            int maxLabelLength, int alphabetSize);
 int tb200_loss_backward(const float* emissions, const float* predictions,
                         const int* labels, const int* inputLengths,
-                        const int* labelLengths, const float* alphas,
-                        const float* logNorms, const float* rowRef, const float* maxP,
+                        const int* labelLengths, const void* saved, size_t savedBytes,
                         const float* deltas, float* egrads, float* pgrads,
                         int batchSize, int maxInputLength, int maxLabelLength,
                         int alphabetSize, int blank, void* workspace,

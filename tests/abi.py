@@ -81,16 +81,16 @@ def viterbi(E, P, LN, il, ll, blank=0, fill=-1):
 
 
 def loss_forward(E, P, labels, il, ll, blank=0):
+    """tb200_loss_forward -> dict(costs, loss_sum, saved)."""
     B, T, U, V = shapes(E, P)
-    z = lambda *s: torch.zeros(s, device="cuda")
-    out = dict(costs=z(B), alphas=z(B, T, U), log_norms=z(B, T, U), row_ref=z(B, T), max_p=z(B, U),
-               loss_sum=z(1))
+    out = dict(costs=torch.zeros((B,), device="cuda"), loss_sum=torch.zeros((1,), device="cuda"))
+    ns = lib.tb200_loss_saved_bytes(B, T, U, V)
+    out["saved"] = workspace(ns)
     n = lib.tb200_loss_forward_workspace_bytes(B, T, U, V)
     ws = workspace(n)
     use_torch_stream()
     check(lib.tb200_loss_forward(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(out["costs"]),
-                                 ptr(out["alphas"]), ptr(out["log_norms"]), ptr(out["row_ref"]),
-                                 ptr(out["max_p"]), ptr(out["loss_sum"]), B, T, U, V, blank,
+                                 ptr(out["loss_sum"]), ptr(out["saved"]), ns, B, T, U, V, blank,
                                  ptr(ws), n))
     return out
 
@@ -104,9 +104,9 @@ def loss_backward(E, P, labels, il, ll, fwd, deltas=None, blank=0):
     n = lib.tb200_loss_backward_workspace_bytes(B, T, U, V)
     ws = workspace(n)
     use_torch_stream()
-    check(lib.tb200_loss_backward(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(fwd["alphas"]),
-                                  ptr(fwd["log_norms"]), ptr(fwd["row_ref"]), ptr(fwd["max_p"]),
-                                  ptr(deltas), ptr(eg), ptr(pg), B, T, U, V, blank, ptr(ws), n))
+    check(lib.tb200_loss_backward(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(fwd["saved"]),
+                                  fwd["saved"].numel(), ptr(deltas), ptr(eg), ptr(pg), B, T, U, V,
+                                  blank, ptr(ws), n))
     return eg, pg
 
 

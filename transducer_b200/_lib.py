@@ -37,9 +37,10 @@ SIGNATURES = {
     "tb200_log_norms_workspace_bytes": (_z, [_i] * 4),
     "tb200_log_norms": (_i, [_p] * 7 + [_i] * 4 + [_p, _z]),
     "tb200_loss_forward_workspace_bytes": (_z, [_i] * 4),
-    "tb200_loss_forward": (_i, [_p] * 11 + [_i] * 5 + [_p, _z]),
+    "tb200_loss_saved_bytes": (_z, [_i] * 4),
+    "tb200_loss_forward": (_i, [_p] * 8 + [_z] + [_i] * 5 + [_p, _z]),
     "tb200_loss_backward_workspace_bytes": (_z, [_i] * 4),
-    "tb200_loss_backward": (_i, [_p] * 12 + [_i] * 5 + [_p, _z]),
+    "tb200_loss_backward": (_i, [_p] * 6 + [_z] + [_p] * 3 + [_i] * 5 + [_p, _z]),
     "tb200_viterbi_decode_workspace_bytes": (_z, [_i] * 4),
     "tb200_viterbi_decode": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
 }

@@ -93,37 +93,36 @@ PYBIND11_MODULE(_transducer, m) {
         "input_lengths"_a, "label_lengths"_a, "batch_size"_a, "max_input_length"_a,
         "max_label_length"_a, "alphabet_size"_a, "workspace"_a, "workspace_bytes"_a);
 
+  m.def("loss_saved_bytes", &tb200_loss_saved_bytes);
+
   m.def("loss_forward",
-        [](addr e, addr p, addr labels, addr ilen, addr llen, addr costs, addr alphas, addr ln,
-           addr rowref, addr maxp, addr loss_sum, int B, int T, int U, int V, int blank, addr ws,
+        [](addr e, addr p, addr labels, addr ilen, addr llen, addr costs, addr loss_sum,
+           addr saved, size_t savedBytes, int B, int T, int U, int V, int blank, addr ws,
            size_t wsBytes) {
           check(tb200_loss_forward(at<const float>(e), at<const float>(p), at<const int>(labels),
                                    at<const int>(ilen), at<const int>(llen), at<float>(costs),
-                                   at<float>(alphas), at<float>(ln), at<float>(rowref),
-                                   at<float>(maxp), at<float>(loss_sum), B, T, U, V, blank,
-                                   at<void>(ws), wsBytes));
+                                   at<float>(loss_sum), at<void>(saved), savedBytes, B, T, U, V,
+                                   blank, at<void>(ws), wsBytes));
         },
         "emissions"_a, "predictions"_a, "labels"_a, "input_lengths"_a, "label_lengths"_a,
-        "costs"_a, "alphas"_a, "log_norms"_a, "row_ref"_a, "max_p"_a, "loss_sum"_a,
-        "batch_size"_a, "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a,
-        "blank"_a, "workspace"_a, "workspace_bytes"_a);
+        "costs"_a, "loss_sum"_a, "saved"_a, "saved_bytes"_a, "batch_size"_a,
+        "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a, "blank"_a, "workspace"_a,
+        "workspace_bytes"_a);
 
   m.def("loss_backward",
-        [](addr e, addr p, addr labels, addr ilen, addr llen, addr alphas, addr ln, addr rowref,
-           addr maxp, addr deltas, addr eg, addr pg, int B, int T, int U, int V, int blank,
-           addr ws, size_t wsBytes) {
+        [](addr e, addr p, addr labels, addr ilen, addr llen, addr saved, size_t savedBytes,
+           addr deltas, addr eg, addr pg, int B, int T, int U, int V, int blank, addr ws,
+           size_t wsBytes) {
           check(tb200_loss_backward(at<const float>(e), at<const float>(p),
                                     at<const int>(labels), at<const int>(ilen),
-                                    at<const int>(llen), at<const float>(alphas),
-                                    at<const float>(ln), at<const float>(rowref),
-                                    at<const float>(maxp), at<const float>(deltas),
-                                    at<float>(eg), at<float>(pg), B, T, U, V, blank,
-                                    at<void>(ws), wsBytes));
+                                    at<const int>(llen), at<const void>(saved), savedBytes,
+                                    at<const float>(deltas), at<float>(eg), at<float>(pg), B, T,
+                                    U, V, blank, at<void>(ws), wsBytes));
         },
         "emissions"_a, "predictions"_a, "labels"_a, "input_lengths"_a, "label_lengths"_a,
-        "alphas"_a, "log_norms"_a, "row_ref"_a, "max_p"_a, "deltas"_a, "egrads"_a, "pgrads"_a,
-        "batch_size"_a, "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a,
-        "blank"_a, "workspace"_a, "workspace_bytes"_a);
+        "saved"_a, "saved_bytes"_a, "deltas"_a, "egrads"_a, "pgrads"_a, "batch_size"_a,
+        "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a, "blank"_a, "workspace"_a,
+        "workspace_bytes"_a);
 
   m.def("viterbi_decode",
         [](addr e, addr p, addr ilen, addr llen, addr labels, int B, int T, int U, int V,

@@ -77,11 +77,34 @@ struct LogNormWs {
   }
 };
 
+// What the forward call leaves for the backward call (opaque to the caller).
+struct SavedState {
+  float *alphasS, *LNs, *ELs, *ebl, *rowRef, *maxP;
+  SavedState(Carver& c, const Dims& d) {
+    const SkewGeom g = skew_geom(d);
+    const size_t B = d.B;
+    alphasS = c.take<float>(B * g.stride);
+    LNs = c.take<float>(B * g.stride);
+    ELs = c.take<float>(B * g.stride);
+    ebl = c.take<float>(B * d.maxT);
+    rowRef = c.take<float>(B * d.maxT);
+    maxP = c.take<float>(B * d.maxU);
+  }
+};
+
+struct ForwardWs {
+  float* LN;  // row-major log-normalisers before the re-layout
+  ForwardWs(Carver& c, const Dims& d) { LN = c.take<float>((size_t)d.B * d.maxT * d.maxU); }
+};
+
 struct BackwardWs {
-  float *expP, *W, *em, *eBlank, *pBlank, *pLabel, *maxPScratch;
+  float *expP, *Ws, *EMs, *W, *em, *eBlank, *pBlank, *pLabel, *maxPScratch;
   BackwardWs(Carver& c, const Dims& d) {
+    const SkewGeom g = skew_geom(d);
     const size_t B = d.B, T = d.maxT, U = d.maxU, V = d.V;
     expP = c.take<float>(B * U * V);
+    Ws = c.take<float>(B * g.stride);
+    EMs = c.take<float>(B * g.stride);
     W = c.take<float>(B * T * ld_w(d));
     em = c.take<float>(B * T * U);
     eBlank = c.take<float>(B * T);
@@ -260,27 +283,44 @@ int tb200_log_norms(const float* E, const float* P, float* LN, float* rowRef, fl
   });
 }
 
+size_t tb200_loss_saved_bytes(int B, int maxT, int maxU, int V) {
+  Dims d{B, maxT, maxU, V, 0};
+  Carver c(nullptr);
+  SavedState s(c, d);
+  return c.total();
+}
+
 size_t tb200_loss_forward_workspace_bytes(int B, int maxT, int maxU, int V) {
-  return tb200_log_norms_workspace_bytes(B, maxT, maxU, V);
+  Dims d{B, maxT, maxU, V, 0};
+  Carver c(nullptr);
+  ForwardWs f(c, d);
+  LogNormWs l(c, d);
+  return c.total();
 }
 
 int tb200_loss_forward(const float* E, const float* P, const int* labels, const int* inLens,
-                       const int* labLens, float* costs, float* alphas, float* LN,
-                       float* rowRef, float* maxP, float* lossSum, int B, int maxT, int maxU,
-                       int V, int blank, void* workspace, size_t workspaceBytes) {
+                       const int* labLens, float* costs, float* lossSum, void* saved,
+                       size_t savedBytes, int B, int maxT, int maxU, int V, int blank,
+                       void* workspace, size_t workspaceBytes) {
   return guarded([&] {
     Dims d{B, maxT, maxU, V, blank};
     check_dims(d);
     need(workspaceBytes, tb200_loss_forward_workspace_bytes(B, maxT, maxU, V), workspace);
+    need(savedBytes, tb200_loss_saved_bytes(B, maxT, maxU, V), saved);
+    Carver cs(saved);
+    SavedState st(cs, d);
     Carver c(workspace);
+    ForwardWs fw(c, d);
     LogNormWs ws(c, d);
-    log_norms_impl(E, P, LN, rowRef, maxP, inLens, labLens, d, ws);
+    const SkewGeom g = skew_geom(d);
+    log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws);
+    launch_lattice_prep(E, fw.LN, st.LNs, st.ELs, st.ebl, labels, inLens, labLens, g, d, g_stream);
     if (lossSum) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.ticket, 0, sizeof(unsigned), g_stream));
       if (B == 0) TB200_CUDA_CHECK(cudaMemsetAsync(lossSum, 0, sizeof(float), g_stream));
     }
-    launch_alpha(E, P, costs, alphas, LN, labels, inLens, labLens, d, lossSum,
-                 lossSum ? ws.ticket : nullptr, g_stream);
+    launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
+                      d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
   });
 }
 
@@ -292,26 +332,29 @@ size_t tb200_loss_backward_workspace_bytes(int B, int maxT, int maxU, int V) {
 }
 
 int tb200_loss_backward(const float* E, const float* P, const int* labels, const int* inLens,
-                        const int* labLens, const float* alphas, const float* LN,
-                        const float* rowRef, const float* maxP, const float* deltas,
-                        float* egrads, float* pgrads, int B, int maxT, int maxU, int V,
-                        int blank, void* workspace, size_t workspaceBytes) {
+                        const int* labLens, const void* saved, size_t savedBytes,
+                        const float* deltas, float* egrads, float* pgrads, int B, int maxT,
+                        int maxU, int V, int blank, void* workspace, size_t workspaceBytes) {
   return guarded([&] {
     Dims d{B, maxT, maxU, V, blank};
     check_dims(d);
     need(workspaceBytes, tb200_loss_backward_workspace_bytes(B, maxT, maxU, V), workspace);
+    need(savedBytes, tb200_loss_saved_bytes(B, maxT, maxU, V), saved);
     if (B == 0) return;
+    Carver cs(const_cast<void*>(saved));
+    SavedState st(cs, d);
     Carver c(workspace);
     BackwardWs ws(c, d);
+    const SkewGeom g = skew_geom(d);
     const int ldW = ld_w(d);
-    if (maxT > 0)
-      TB200_CUDA_CHECK(cudaMemsetAsync(ws.W, 0, sizeof(float) * (size_t)B * maxT * ldW, g_stream));
     launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
-    launch_gamma_fused(E, P, alphas, LN, rowRef, maxP, labels, inLens, labLens, ws.W, ldW,
-                       ws.em, ws.eBlank, ws.pBlank, ws.pLabel, d, g_stream);
-    launch_egrad_simt(E, rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
+    launch_gamma_skew(P, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
+                      inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
+                      g_stream);
+    launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
+    launch_egrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
                       egrads, inLens, labLens, d, g_stream);
-    launch_pgrad_simt(E, rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,
+    launch_pgrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,
                       pgrads, inLens, labLens, d, g_stream);
   });
 }

@@ -20,28 +20,52 @@ struct Dims {
 constexpr int kMaxLatticeU = 8192;  // widest label axis the wavefront kernels take
 
 // ---- lattice.cu ------------------------------------------------------------
+// transducer.h `forward`: row-major lattices, emission terms gathered from E.
 void launch_alpha(const float* E, const float* P, float* costs, float* alphas,
                   const float* LN, const int* labels, const int* inLens,
                   const int* labLens, Dims d, float* lossSum, unsigned* ticket,
                   cudaStream_t stream);
 
-// Reverse sweep.  abi=true reproduces transducer.h's backward contract: the three
-// outputs must already be zero-filled; lngrads receives the node occupancies and
-// the sparse blank/label terms are subtracted in place from egrads/pgrads.
+// transducer.h `backward`: the three outputs must already be zero-filled; lngrads
+// receives the node occupancies and the sparse blank/label terms are subtracted in
+// place from egrads/pgrads.
 void launch_gamma_abi(const float* E, const float* P, float* egrads, float* pgrads,
                       float* lngrads, const float* alphas, const float* LN,
                       const int* labels, const int* inLens, const int* labLens,
                       Dims d, cudaStream_t stream);
 
-// Fused-path reverse sweep: writes W[t,u] = occupancy * exp(rowRef[t] + maxP[u] - LN[t,u])
-// (row stride ldW >= maxU, rows/cols outside the valid lattice are NOT touched: the
-// caller zero-fills W), the label-arc occupancies `em` [B,maxT,maxU], and the summed
+// Skewed lattice storage used by the fused path: node (t,u) of utterance b lives at
+// b*stride + (t+u)*ld + u, so one wavefront step reads and writes one contiguous row.
+struct SkewGeom {
+  int ld;       // floats per anti-diagonal row (maxU rounded up to 32)
+  int nDiag;    // rows per utterance
+  i64 stride;   // floats per utterance
+};
+SkewGeom skew_geom(Dims d);
+
+// LN (row-major) -> LNs (skewed); ELs[t,u] = E[t,label_u] (skewed); ebl[b,t] = E[t,blank].
+void launch_lattice_prep(const float* E, const float* LN, float* LNs, float* ELs, float* ebl,
+                         const int* labels, const int* inLens, const int* labLens, SkewGeom g,
+                         Dims d, cudaStream_t stream);
+
+void launch_alpha_skew(const float* P, float* costs, float* alphasS, const float* LNs,
+                       const float* ELs, const float* ebl, SkewGeom g, const int* labels,
+                       const int* inLens, const int* labLens, Dims d, float* lossSum,
+                       unsigned* ticket, cudaStream_t stream);
+
+// Fused-path reverse sweep on skewed lattices.  Writes (skewed) Ws[t,u] = occupancy *
+// exp(rowRef[t] + maxP[u] - LN[t,u]) and the label-arc occupancies EMs, plus the summed
 // sparse terms eBlank [B,maxT], pBlank [B,maxU], pLabel [B,maxU].
-void launch_gamma_fused(const float* E, const float* P, const float* alphas,
-                        const float* LN, const float* rowRef, const float* maxP,
-                        const int* labels, const int* inLens, const int* labLens,
-                        float* W, int ldW, float* em, float* eBlank, float* pBlank,
-                        float* pLabel, Dims d, cudaStream_t stream);
+void launch_gamma_skew(const float* P, const float* alphasS, const float* LNs,
+                       const float* ELs, const float* ebl, SkewGeom g, const float* rowRef,
+                       const float* maxP, const int* labels, const int* inLens,
+                       const int* labLens, float* Ws, float* EMs, float* eBlank,
+                       float* pBlank, float* pLabel, Dims d, cudaStream_t stream);
+
+// Ws/EMs (skewed) -> W [B,maxT,ldW] (zero outside the valid lattice) and em [B,maxT,maxU].
+void launch_lattice_unskew(const float* Ws, const float* EMs, float* W, int ldW, float* em,
+                           const int* inLens, const int* labLens, SkewGeom g, Dims d,
+                           cudaStream_t stream);
 
 // Max-plus wavefront + bounded on-device backtrack + label argmax on the path.
 // best [B,maxT,maxU] holds max_{v != blank}(E[t,v]+P[u,v]); decBits is scratch of

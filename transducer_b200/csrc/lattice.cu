@@ -26,7 +26,7 @@ namespace {
 // The last CTA to finish adds the per-utterance costs in index order into
 // *lossSum (deterministic), so a data-parallel caller can hand that scalar
 // straight to its all-reduce without another kernel.
-__device__ void finish_cost(float* costs, int b, float cost, int B, float* lossSum,
+__device__ __forceinline__ void finish_cost(float* costs, int b, float cost, int B, float* lossSum,
                             unsigned* ticket) {
   costs[b] = cost;
   if (lossSum == nullptr) return;
@@ -41,10 +41,34 @@ __device__ void finish_cost(float* costs, int b, float cost, int B, float* lossS
   }
 }
 
-template <int R, int PF, int MAXNT>
+// Lattice addressing.  Row-major: node (t,u) at t*ld + u (the reference's layout).
+// Skewed: node (t,u) at (t+u)*ld + u, i.e. one anti-diagonal per row, so that the
+// threads of a wavefront step touch consecutive addresses.
+// Offsets within one utterance fit 32 bits (checked by the launchers).
+template <bool SKEW>
+__device__ __forceinline__ int node(int t, int u, int ld) {
+  return SKEW ? (t + u) * ld + u : t * ld + u;
+}
+
+// log(exp(a)+exp(b)) for the alpha recursion.  Same -inf handling and operation order
+// as the reference's logSumExp; the correction term log1p(exp(-|a-b|)) <= ln 2 is
+// evaluated with the hardware ex2/lg2 units (absolute error ~2e-7, far below one ulp of
+// the alphas it is added to once they exceed a few units in magnitude).
+__device__ __forceinline__ float lse2_fast(float a, float b) {
+  if (a == neg_inf()) return b;
+  if (b == neg_inf()) return a;
+  return fmaxf(a, b) + __logf(1.0f + __expf(-fabsf(a - b)));
+}
+
+// SKEW=false: LN/alphas row-major [B,maxT,maxU], emission terms gathered from E.
+// SKEW=true : LN/alphas/ELs skewed [B,nDiag,ld]; ELs[t,u] = E[t,label_u] and
+//             ebl[b,t] = E[t,blank] were gathered by lattice_prep_kernel, so the
+//             sweep itself issues only coalesced loads and stores.
+template <int R, int PF, int MAXNT, bool SKEW>
 __global__ void __launch_bounds__(MAXNT) alpha_kernel(
     const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ costs,
     float* __restrict__ alphas, const float* __restrict__ LN,
+    const float* __restrict__ ELs, const float* __restrict__ ebl, int ld, i64 latStride,
     const int* __restrict__ labels, const int* __restrict__ inLens,
     const int* __restrict__ labLens, int B, int maxT, int maxU, int V, int blank,
     float* lossSum, unsigned* ticket) {
@@ -57,8 +81,10 @@ __global__ void __launch_bounds__(MAXNT) alpha_kernel(
   }
   const float* e = E + (i64)b * maxT * V;
   const float* p = P + (i64)b * maxU * V;
-  const float* ln = LN + (i64)b * maxT * maxU;
-  float* al = alphas + (i64)b * maxT * maxU;
+  const float* ln = LN + (i64)b * latStride;
+  const float* el = SKEW ? ELs + (i64)b * latStride : nullptr;
+  const float* eb = SKEW ? ebl + (i64)b * maxT : nullptr;
+  float* al = alphas + (i64)b * latStride;
   const int* lab_g = labels + (i64)b * (maxU - 1);
 
   const int nStrips = (U + R - 1) / R;
@@ -83,19 +109,20 @@ __global__ void __launch_bounds__(MAXNT) alpha_kernel(
     }
   }
 
+  float cost = 0.0f;
+  bool owner = false;
   float q_ln[PF][R], q_el[PF][R], q_eb[PF];
+  // Operand prefetch for step s into ring slot k.  The loads are UNCONDITIONAL, with
+  // the node clamped into the lattice: predicated loads were scheduled next to their
+  // use by the compiler, which put the whole memory latency on the recursion.
   auto issue = [&](int s, int k) {
-    const int t = s - i;
-    if (mine && t >= 0 && t < T) {
-      q_eb[k] = e[(i64)t * V + blank];
+    const int t = min(max(s - i, 0), T - 1);
+    q_eb[k] = SKEW ? eb[t] : e[(i64)t * V + blank];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int u = i * R + r;
-        if (u < U) {
-          q_ln[k][r] = ln[(i64)t * maxU + u];
-          q_el[k][r] = e[(i64)t * V + lab[r]];
-        }
-      }
+    for (int r = 0; r < R; ++r) {
+      const int u = min(i * R + r, U - 1);
+      q_ln[k][r] = ln[node<SKEW>(t, u, ld)];
+      q_el[k][r] = SKEW ? el[node<SKEW>(t, u, ld)] : e[(i64)t * V + lab[r]];
     }
   };
 #pragma unroll
@@ -104,8 +131,9 @@ __global__ void __launch_bounds__(MAXNT) alpha_kernel(
   for (int s0 = 0; s0 < S; s0 += PF) {
 #pragma unroll
     for (int k = 0; k < PF; ++k) {
+      // no early exit: a `break` here keeps the compiler from unrolling, which sends the
+      // prefetch ring to local memory; steps past the end are simply empty
       const int s = s0 + k;
-      if (s >= S) break;  // uniform across the block
       const int t = s - i;
       if (mine && t >= 0 && t < T) {
         float step_in = (i == 0) ? neg_inf() : xch[(s + 1) & 1][i];
@@ -113,13 +141,15 @@ __global__ void __launch_bounds__(MAXNT) alpha_kernel(
         for (int r = 0; r < R; ++r) {
           const int u = i * R + r;
           if (u < U) {
-            const float a = (s == 0 && u == 0) ? 0.0f : lse2(step_in, stay[r]);
-            al[(i64)t * maxU + u] = a;
+            const float a = (s == 0 && u == 0) ? 0.0f : (SKEW ? lse2_fast(step_in, stay[r]) : lse2(step_in, stay[r]));
+            al[node<SKEW>(t, u, ld)] = a;
             const float lnv = q_ln[k][r];
             stay[r] = ((a + q_eb[k]) + pbl[r]) - lnv;
             step_in = ((a + q_el[k][r]) + plab[r]) - lnv;
-            if (t == T - 1 && u == U - 1)
-              finish_cost(costs, b, -stay[r], B, lossSum, ticket);
+            if (t == T - 1 && u == U - 1) {
+              cost = -stay[r];
+              owner = true;
+            }
           }
         }
         xch[s & 1][i + 1] = step_in;
@@ -128,16 +158,22 @@ __global__ void __launch_bounds__(MAXNT) alpha_kernel(
       __syncthreads();
     }
   }
+  if (owner) finish_cost(costs, b, cost, B, lossSum, ticket);
 }
 
 // ---------------------------------------------------------------------------
 // reverse occupancy sweep
 // ---------------------------------------------------------------------------
 
-template <int R, int PF, int MAXNT, bool ABI>
+// ABI=true : the transducer.h contract (row-major lattices, read-modify-write of the
+//            zero-filled egrads/pgrads, occupancies to lngrads).
+// ABI=false: fused path.  With SKEW the lattices (alphas, LN, ELs in; W, em out) are
+//            skewed with row length ld; without it they are row-major (W with ldW).
+template <int R, int PF, int MAXNT, bool ABI, bool SKEW>
 __global__ void __launch_bounds__(MAXNT) gamma_kernel(
     const float* __restrict__ E, const float* __restrict__ P,
     const float* __restrict__ alphas, const float* __restrict__ LN,
+    const float* __restrict__ ELs, const float* __restrict__ ebl, int ld, i64 latStride,
     const float* __restrict__ rowRef, const float* __restrict__ maxP,
     const int* __restrict__ labels, const int* __restrict__ inLens,
     const int* __restrict__ labLens,
@@ -163,8 +199,10 @@ __global__ void __launch_bounds__(MAXNT) gamma_kernel(
 
   const float* e = E + (i64)b * maxT * V;
   const float* p = P + (i64)b * maxU * V;
-  const float* al = alphas + (i64)b * maxT * maxU;
-  const float* ln = LN + (i64)b * maxT * maxU;
+  const float* al = alphas + (i64)b * latStride;
+  const float* ln = LN + (i64)b * latStride;
+  const float* el = SKEW ? ELs + (i64)b * latStride : nullptr;
+  const float* eb = SKEW ? ebl + (i64)b * maxT : nullptr;
   const int* lab_g = labels + (i64)b * (maxU - 1);
 
   for (int t = i; t < T; t += NT) sEB[t] = (t == T - 1) ? 1.0f : 0.0f;
@@ -195,20 +233,16 @@ __global__ void __launch_bounds__(MAXNT) gamma_kernel(
   }
 
   float q_a[PF][R], q_ln[PF][R], q_el[PF][R], q_eb[PF], q_ref[PF];
-  auto issue = [&](int s, int k) {
-    const int t = T - 1 - (s - ir);
-    if (mine && t >= 0 && t < T) {
-      q_eb[k] = e[(i64)t * V + blank];
-      if (!ABI) q_ref[k] = rowRef[(i64)b * maxT + t];
+  auto issue = [&](int s, int k) {  // unconditional, clamped: see alpha_kernel
+    const int t = min(max(T - 1 - (s - ir), 0), T - 1);
+    q_eb[k] = SKEW ? eb[t] : e[(i64)t * V + blank];
+    if (!ABI) q_ref[k] = rowRef[(i64)b * maxT + t];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int u = i * R + r;
-        if (u < U) {
-          q_a[k][r] = al[(i64)t * maxU + u];
-          q_ln[k][r] = ln[(i64)t * maxU + u];
-          q_el[k][r] = e[(i64)t * V + lab[r]];
-        }
-      }
+    for (int r = 0; r < R; ++r) {
+      const int u = min(i * R + r, U - 1);
+      q_a[k][r] = al[node<SKEW>(t, u, ld)];
+      q_ln[k][r] = ln[node<SKEW>(t, u, ld)];
+      q_el[k][r] = SKEW ? el[node<SKEW>(t, u, ld)] : e[(i64)t * V + lab[r]];
     }
   };
 #pragma unroll
@@ -219,7 +253,6 @@ __global__ void __launch_bounds__(MAXNT) gamma_kernel(
 #pragma unroll
     for (int k = 0; k < PF; ++k) {
       const int s = s0 + k;
-      if (s >= S) break;
       const int t = T - 1 - (s - ir);
       if (mine && t >= 0 && t < T) {
         float g_rt = 0.0f, a_rt = 0.0f;
@@ -255,8 +288,13 @@ __global__ void __launch_bounds__(MAXNT) gamma_kernel(
             } else {
               // exponent clamp keeps W finite where the factored sum had underflowed
               const float sh = fminf((q_ref[k] + mp[r]) - lnv, 80.0f);
-              W[(i64)b * maxT * ldW + (i64)t * ldW + u] = g * expf(sh);
-              em[(i64)b * maxT * maxU + (i64)t * maxU + u] = step;
+              if (SKEW) {
+                W[(i64)b * latStride + node<true>(t, u, ld)] = g * expf(sh);
+                em[(i64)b * latStride + node<true>(t, u, ld)] = step;
+              } else {
+                W[(i64)b * maxT * ldW + (i64)t * ldW + u] = g * expf(sh);
+                em[(i64)b * maxT * maxU + (i64)t * maxU + u] = step;
+              }
             }
             g_dn[r] = g;
             a_dn[r] = a;
@@ -339,18 +377,14 @@ __global__ void __launch_bounds__(MAXNT) viterbi_kernel(
   for (int u = i; u < U; u += NT) sFrame[u] = -1;
 
   float q_ln[PF][R], q_bs[PF][R], q_eb[PF];
-  auto issue = [&](int s, int k) {
-    const int t = s - i;
-    if (mine && t >= 0 && t < T) {
-      q_eb[k] = e[(i64)t * V + blank];
+  auto issue = [&](int s, int k) {  // unconditional, clamped: see alpha_kernel
+    const int t = min(max(s - i, 0), T - 1);
+    q_eb[k] = e[(i64)t * V + blank];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int u = i * R + r;
-        if (u < U) {
-          q_ln[k][r] = ln[(i64)t * maxU + u];
-          q_bs[k][r] = (u < U - 1) ? bs[(i64)t * maxU + u] : 0.0f;
-        }
-      }
+    for (int r = 0; r < R; ++r) {
+      const int u = min(i * R + r, U - 1);
+      q_ln[k][r] = ln[(i64)t * maxU + u];
+      q_bs[k][r] = bs[(i64)t * maxU + min(u, max(U - 2, 0))];
     }
   };
 #pragma unroll
@@ -360,7 +394,6 @@ __global__ void __launch_bounds__(MAXNT) viterbi_kernel(
 #pragma unroll
     for (int k = 0; k < PF; ++k) {
       const int s = s0 + k;
-      if (s >= S) break;
       const int t = s - i;
       if (mine && t >= 0 && t < T) {
         float step_in = (i == 0) ? neg_inf() : xch[(s + 1) & 1][i];
@@ -448,6 +481,11 @@ StripCfg pick_strips(int maxU) {
   return {R, threads};
 }
 
+void check_lattice_fits_int(Dims d) {
+  if ((i64)(d.maxT + d.maxU) * round_up64(d.maxU > 0 ? d.maxU : 1, 32) >= 2147483647LL)
+    throw std::invalid_argument("lattice of one utterance exceeds 2^31 nodes");
+}
+
 }  // namespace
 
 #define TB200_DISPATCH_STRIPS(cfg, CALL)                  \
@@ -464,12 +502,38 @@ void launch_alpha(const float* E, const float* P, float* costs, float* alphas,
                   const int* labLens, Dims d, float* lossSum, unsigned* ticket,
                   cudaStream_t stream) {
   if (d.B <= 0) return;
+  check_lattice_fits_int(d);
+  const StripCfg cfg = pick_strips(d.maxU);
+  ScopedKernel sk("alpha_wavefront_abi", stream);
+#define CALL(R, PF, NT)                                                              \
+  alpha_kernel<R, PF, NT, false><<<d.B, cfg.threads, 0, stream>>>(                   \
+      E, P, costs, alphas, LN, nullptr, nullptr, d.maxU, (i64)d.maxT * d.maxU, labels, \
+      inLens, labLens, d.B, d.maxT, d.maxU, d.V, d.blank, lossSum, ticket)
+  TB200_DISPATCH_STRIPS(cfg, CALL);
+#undef CALL
+  TB200_CHECK_LAUNCH();
+}
+
+SkewGeom skew_geom(Dims d) {
+  SkewGeom g;
+  g.ld = (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32);
+  g.nDiag = d.maxT + d.maxU;  // one spare row
+  g.stride = (i64)g.ld * g.nDiag;
+  return g;
+}
+
+void launch_alpha_skew(const float* P, float* costs, float* alphasS, const float* LNs,
+                       const float* ELs, const float* ebl, SkewGeom g, const int* labels,
+                       const int* inLens, const int* labLens, Dims d, float* lossSum,
+                       unsigned* ticket, cudaStream_t stream) {
+  if (d.B <= 0) return;
+  check_lattice_fits_int(d);
   const StripCfg cfg = pick_strips(d.maxU);
   ScopedKernel sk("alpha_wavefront", stream);
 #define CALL(R, PF, NT)                                                              \
-  alpha_kernel<R, PF, NT><<<d.B, cfg.threads, 0, stream>>>(                          \
-      E, P, costs, alphas, LN, labels, inLens, labLens, d.B, d.maxT, d.maxU, d.V,   \
-      d.blank, lossSum, ticket)
+  alpha_kernel<R, PF, NT, true><<<d.B, cfg.threads, 0, stream>>>(                    \
+      nullptr, P, costs, alphasS, LNs, ELs, ebl, g.ld, g.stride, labels, inLens,    \
+      labLens, d.B, d.maxT, d.maxU, d.V, d.blank, lossSum, ticket)
   TB200_DISPATCH_STRIPS(cfg, CALL);
 #undef CALL
   TB200_CHECK_LAUNCH();
@@ -491,38 +555,150 @@ void launch_gamma_abi(const float* E, const float* P, float* egrads, float* pgra
                       const int* labels, const int* inLens, const int* labLens,
                       Dims d, cudaStream_t stream) {
   if (d.B <= 0) return;
+  check_lattice_fits_int(d);
   const StripCfg cfg = pick_strips(d.maxU);
   const size_t smem = sizeof(float) * (size_t)(d.maxT > 0 ? d.maxT : 1);
   if (smem > kMaxDynSmem) throw std::invalid_argument("input length above 51200 frames is not supported");
   ScopedKernel sk("gamma_wavefront_abi", stream);
 #define CALL(R, PF, NT)                                                               \
-  allow_smem(gamma_kernel<R, PF, NT, true>, smem);                                    \
-  gamma_kernel<R, PF, NT, true><<<d.B, cfg.threads, smem, stream>>>(                  \
-      E, P, alphas, LN, nullptr, nullptr, labels, inLens, labLens, egrads, pgrads,    \
-      lngrads, nullptr, 0, nullptr, nullptr, nullptr, nullptr, d.maxT, d.maxU, d.V,   \
-      d.blank)
+  allow_smem(gamma_kernel<R, PF, NT, true, false>, smem);                             \
+  gamma_kernel<R, PF, NT, true, false><<<d.B, cfg.threads, smem, stream>>>(           \
+      E, P, alphas, LN, nullptr, nullptr, d.maxU, (i64)d.maxT * d.maxU, nullptr,      \
+      nullptr, labels, inLens, labLens, egrads, pgrads, lngrads, nullptr, 0, nullptr, \
+      nullptr, nullptr, nullptr, d.maxT, d.maxU, d.V, d.blank)
   TB200_DISPATCH_STRIPS(cfg, CALL);
 #undef CALL
   TB200_CHECK_LAUNCH();
 }
 
-void launch_gamma_fused(const float* E, const float* P, const float* alphas,
-                        const float* LN, const float* rowRef, const float* maxP,
-                        const int* labels, const int* inLens, const int* labLens,
-                        float* W, int ldW, float* em, float* eBlank, float* pBlank,
-                        float* pLabel, Dims d, cudaStream_t stream) {
+void launch_gamma_skew(const float* P, const float* alphasS, const float* LNs,
+                       const float* ELs, const float* ebl, SkewGeom g, const float* rowRef,
+                       const float* maxP, const int* labels, const int* inLens,
+                       const int* labLens, float* Ws, float* EMs, float* eBlank,
+                       float* pBlank, float* pLabel, Dims d, cudaStream_t stream) {
   if (d.B <= 0) return;
+  check_lattice_fits_int(d);
   const StripCfg cfg = pick_strips(d.maxU);
   const size_t smem = sizeof(float) * (size_t)(d.maxT > 0 ? d.maxT : 1);
   if (smem > kMaxDynSmem) throw std::invalid_argument("input length above 51200 frames is not supported");
   ScopedKernel sk("gamma_wavefront", stream);
 #define CALL(R, PF, NT)                                                               \
-  allow_smem(gamma_kernel<R, PF, NT, false>, smem);                                   \
-  gamma_kernel<R, PF, NT, false><<<d.B, cfg.threads, smem, stream>>>(                 \
-      E, P, alphas, LN, rowRef, maxP, labels, inLens, labLens, nullptr, nullptr,      \
-      nullptr, W, ldW, em, eBlank, pBlank, pLabel, d.maxT, d.maxU, d.V, d.blank)
+  allow_smem(gamma_kernel<R, PF, NT, false, true>, smem);                             \
+  gamma_kernel<R, PF, NT, false, true><<<d.B, cfg.threads, smem, stream>>>(           \
+      nullptr, P, alphasS, LNs, ELs, ebl, g.ld, g.stride, rowRef, maxP, labels,       \
+      inLens, labLens, nullptr, nullptr, nullptr, Ws, g.ld, EMs, eBlank, pBlank,      \
+      pLabel, d.maxT, d.maxU, d.V, d.blank)
   TB200_DISPATCH_STRIPS(cfg, CALL);
 #undef CALL
+  TB200_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------------------
+// layout changes between row-major and skewed lattices
+// ---------------------------------------------------------------------------
+namespace {
+
+// One CTA per 32x32 (t,u) tile.  Reads LN row-major and gathers E[t,label_u]; writes
+// both skewed.  Column tile 0 also writes ebl[t] = E[t,blank].
+__global__ void __launch_bounds__(256) lattice_prep_kernel(
+    const float* __restrict__ E, const float* __restrict__ LN, float* __restrict__ LNs,
+    float* __restrict__ ELs, float* __restrict__ ebl, const int* __restrict__ labels,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
+    int blank, int ld, i64 latStride) {
+  __shared__ float tLn[32][33], tEl[32][33];
+  const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
+  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  if (t0 >= T || u0 >= U) return;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const float* e = E + (i64)b * maxT * V;
+  const float* ln = LN + (i64)b * maxT * maxU;
+  const int* lab = labels + (i64)b * (maxU - 1);
+  const int u = u0 + lane;
+  const int myLab = (u < U - 1) ? lab[u] : blank;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int tt = w * 4 + k, t = t0 + tt;
+    float a = 0.0f, c = 0.0f;
+    if (t < T && u < U) {
+      a = ln[(i64)t * maxU + u];
+      c = e[(i64)t * V + myLab];
+    }
+    tLn[tt][lane] = a;
+    tEl[tt][lane] = c;
+  }
+  if (u0 == 0 && threadIdx.x < 32 && t0 + lane < T)
+    ebl[(i64)b * maxT + t0 + lane] = e[(i64)(t0 + lane) * V + blank];
+  __syncthreads();
+  // diagonal s = t + u of this tile: s - (t0+u0) in [0, 62]; lane <-> u
+  for (int ds = w; ds < 63; ds += 8) {
+    const int tt = ds - lane;
+    if (tt >= 0 && tt < 32 && t0 + tt < T && u < U) {
+      const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
+      LNs[o] = tLn[tt][lane];
+      ELs[o] = tEl[tt][lane];
+    }
+  }
+}
+
+// Skewed -> row-major for two arrays at once (W with row length ldW, em with maxU);
+// everything outside the valid lattice of W is written as zero so the matrix can be
+// used as a GEMM operand without a separate fill.
+__global__ void __launch_bounds__(256) lattice_unskew_kernel(
+    const float* __restrict__ Ws, const float* __restrict__ EMs, float* __restrict__ W,
+    float* __restrict__ em, const int* __restrict__ inLens, const int* __restrict__ labLens,
+    int maxT, int maxU, int ld, i64 latStride, int ldW) {
+  __shared__ float tW[32][33], tE[32][33];
+  const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
+  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int u = u0 + lane;
+  const bool live = t0 < T && u0 < U;
+  if (live) {
+    for (int ds = w; ds < 63; ds += 8) {
+      const int tt = ds - lane;
+      if (tt >= 0 && tt < 32) {
+        float a = 0.0f, c = 0.0f;
+        if (t0 + tt < T && u < U) {
+          const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
+          a = Ws[o];
+          c = EMs[o];
+        }
+        tW[tt][lane] = a;
+        tE[tt][lane] = c;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int tt = w * 4 + k, t = t0 + tt;
+    if (t >= maxT) continue;
+    if (u < ldW) W[((i64)b * maxT + t) * ldW + u] = live ? tW[tt][lane] : 0.0f;
+    if (u < maxU) em[((i64)b * maxT + t) * maxU + u] = live ? tE[tt][lane] : 0.0f;
+  }
+}
+
+}  // namespace
+
+void launch_lattice_prep(const float* E, const float* LN, float* LNs, float* ELs, float* ebl,
+                         const int* labels, const int* inLens, const int* labLens, SkewGeom g,
+                         Dims d, cudaStream_t stream) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  dim3 grid(div_up(d.maxU, 32), div_up(d.maxT, 32), d.B);
+  ScopedKernel sk("lattice_prep", stream);
+  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, LN, LNs, ELs, ebl, labels, inLens, labLens,
+                                                d.maxT, d.maxU, d.V, d.blank, g.ld, g.stride);
+  TB200_CHECK_LAUNCH();
+}
+
+void launch_lattice_unskew(const float* Ws, const float* EMs, float* W, int ldW, float* em,
+                           const int* inLens, const int* labLens, SkewGeom g, Dims d,
+                           cudaStream_t stream) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  dim3 grid(div_up(ldW, 32), div_up(d.maxT, 32), d.B);
+  ScopedKernel sk("lattice_unskew", stream);
+  lattice_unskew_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, W, em, inLens, labLens, d.maxT,
+                                                  d.maxU, g.ld, g.stride, ldW);
   TB200_CHECK_LAUNCH();
 }
 

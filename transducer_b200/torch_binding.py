@@ -45,29 +45,28 @@ class Transducer(torch.autograd.Function):
         U = predictions.shape[1]
         f32 = dict(device=device, dtype=torch.float32)
         costs = torch.empty((B,), **f32)
-        alphas = torch.empty((B, T, U), **f32)
-        log_norms = torch.empty((B, T, U), **f32)
-        row_ref = torch.empty((B, T), **f32)
-        max_p = torch.empty((B, U), **f32)
         loss_sum = torch.empty((1,), **f32)
         with DeviceManager(device):
+            saved_bytes = _transducer.loss_saved_bytes(B, T, U, V)
+            saved = _workspace(saved_bytes, device)
             nbytes = _transducer.loss_forward_workspace_bytes(B, T, U, V)
             ws = _workspace(nbytes, device)
             _transducer.loss_forward(
                 emissions.data_ptr(), predictions.data_ptr(), labels.data_ptr(),
                 input_lengths.data_ptr(), label_lengths.data_ptr(), costs.data_ptr(),
-                alphas.data_ptr(), log_norms.data_ptr(), row_ref.data_ptr(), max_p.data_ptr(),
-                loss_sum.data_ptr(), B, T, U, V, blank, ws.data_ptr(), nbytes)
-        ctx.save_for_backward(emissions, predictions, alphas, log_norms, row_ref, max_p,
-                              labels, input_lengths, label_lengths)
+                loss_sum.data_ptr(), saved.data_ptr(), saved_bytes, B, T, U, V, blank,
+                ws.data_ptr(), nbytes)
+        # `saved` replaces the reference's saved alphas/log_norms/expEs/expPs/expLNs
+        # (torch_binding.py:52-55); exp(emissions) is recomputed, never stored
+        ctx.save_for_backward(emissions, predictions, saved, labels, input_lengths,
+                              label_lengths)
         ctx.blank = blank
         ctx.mark_non_differentiable(loss_sum)
         return costs, loss_sum
 
     @staticmethod
     def backward(ctx, deltas, _unused=None):
-        (emissions, predictions, alphas, log_norms, row_ref, max_p, labels, input_lengths,
-         label_lengths) = ctx.saved_tensors
+        emissions, predictions, saved, labels, input_lengths, label_lengths = ctx.saved_tensors
         device = emissions.device
         B, T, V = emissions.shape
         U = predictions.shape[1]
@@ -79,10 +78,9 @@ class Transducer(torch.autograd.Function):
             ws = _workspace(nbytes, device)
             _transducer.loss_backward(
                 emissions.data_ptr(), predictions.data_ptr(), labels.data_ptr(),
-                input_lengths.data_ptr(), label_lengths.data_ptr(), alphas.data_ptr(),
-                log_norms.data_ptr(), row_ref.data_ptr(), max_p.data_ptr(), deltas.data_ptr(),
-                egrads.data_ptr(), pgrads.data_ptr(), B, T, U, V, ctx.blank, ws.data_ptr(),
-                nbytes)
+                input_lengths.data_ptr(), label_lengths.data_ptr(), saved.data_ptr(),
+                saved.numel(), deltas.data_ptr(), egrads.data_ptr(), pgrads.data_ptr(),
+                B, T, U, V, ctx.blank, ws.data_ptr(), nbytes)
         return egrads, pgrads, None, None, None, None
 
 
