@@ -52,7 +52,9 @@ void* tb200_get_stream(void);
 /* Tuning / test switches.  Keys:
  *   "lognorm_path"  0 auto, 1 exact SIMT logsumexp, 2 tensor-core factored GEMM
  *   "grads_path"    0 auto, 1 SIMT, 2 tensor-core
- *   "grad_passes"   1 or 3: TF32 products per gradient GEMM (3 = split, ~fp32 accuracy)
+ *   "grad_passes"   1 or 2: TF32 products per gradient GEMM step.  2 (default): the
+ *                   exp(E)/exp(P) operands are split hi+lo, the lattice weights rounded
+ *                   once (error ~1e-4 of the gradient maximum); 1: everything rounded once
  * Unknown keys return TB200_ERR_INVALID_ARGUMENT.  No counterpart in the reference. */
 int tb200_set_option(const char* key, int value);
 int tb200_get_option(const char* key, int* value);

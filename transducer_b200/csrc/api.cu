@@ -17,7 +17,7 @@ thread_local std::string g_error;
 struct Options {
   int lognorm_path = 0;
   int grads_path = 0;
-  int grad_passes = 3;
+  int grad_passes = 2;
 };
 Options g_opt;
 
@@ -99,10 +99,12 @@ struct ForwardWs {
 
 struct BackwardWs {
   float *expP, *Ws, *EMs, *W, *em, *eBlank, *pBlank, *pLabel, *maxPScratch;
+  int* status;
   BackwardWs(Carver& c, const Dims& d) {
     const SkewGeom g = skew_geom(d);
     const size_t B = d.B, T = d.maxT, U = d.maxU, V = d.V;
-    expP = c.take<float>(B * U * V);
+    status = c.take<int>(16);
+    expP = c.take<float>(B * U * V);  // SIMT path only
     Ws = c.take<float>(B * g.stride);
     EMs = c.take<float>(B * g.stride);
     W = c.take<float>(B * T * ld_w(d));
@@ -177,7 +179,7 @@ int tb200_set_option(const char* key, int value) {
   if (!key) return fail(kErrInvalidArgument, "null option key");
   if (!strcmp(key, "lognorm_path") && value >= 0 && value <= 2) g_opt.lognorm_path = value;
   else if (!strcmp(key, "grads_path") && value >= 0 && value <= 2) g_opt.grads_path = value;
-  else if (!strcmp(key, "grad_passes") && (value == 1 || value == 3)) g_opt.grad_passes = value;
+  else if (!strcmp(key, "grad_passes") && (value == 1 || value == 2)) g_opt.grad_passes = value;
   else return fail(kErrInvalidArgument, std::string("unknown option or bad value: ") + key);
   return kOk;
 }
@@ -347,10 +349,24 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
     BackwardWs ws(c, d);
     const SkewGeom g = skew_geom(d);
     const int ldW = ld_w(d);
-    launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
     launch_gamma_skew(P, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
                       inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
                       g_stream);
+    const int passes = g_opt.grad_passes;
+    const bool can = grads_umma_supported(E, d, passes);
+    if (g_opt.grads_path == 2 && !can)
+      throw std::invalid_argument(
+          "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
+          "maxLabelLength <= 128 and 16-byte aligned emissions");
+    if (can && g_opt.grads_path != 1) {
+      TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
+      launch_unskew_round(ws.Ws, ws.EMs, ws.W, ws.em, inLens, labLens, g, d, g_stream);
+      launch_grads_umma(E, P, st.rowRef, st.maxP, ws.W, ws.em, ws.eBlank, ws.pBlank,
+                        ws.pLabel, labels, deltas, egrads, pgrads, inLens, labLens, d, passes,
+                        ws.status, g_stream);
+      return;
+    }
+    launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
     launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
     launch_egrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
                       egrads, inLens, labLens, d, g_stream);

@@ -103,6 +103,23 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
                          int* status, cudaStream_t stream);
 
+// ---- grads_umma.cu --------------------------------------------------------------
+// Tensor-core gradients: one pass over E produces egrads and pgrads.  Usable when
+// grads_umma_supported(); passes = 2 (E-sized operands split hi/lo, W rounded once) or 1.
+int grads_umma_ld_w(Dims d);
+bool grads_umma_supported(const float* E, Dims d, int passes);
+// Ws/EMs (skewed) -> W [B,maxT,ldW] rounded to TF32, zero outside the valid lattice, and
+// em [B,maxT,maxU].
+void launch_unskew_round(const float* Ws, const float* EMs, float* W, float* em,
+                         const int* inLens, const int* labLens, SkewGeom g, Dims d,
+                         cudaStream_t stream);
+void launch_grads_umma(const float* E, const float* P, const float* rowRef, const float* maxP,
+                       const float* W, const float* em, const float* eBlank,
+                       const float* pBlank, const float* pLabel, const int* labels,
+                       const float* deltas, float* egrads, float* pgrads, const int* inLens,
+                       const int* labLens, Dims d, int passes, int* status,
+                       cudaStream_t stream);
+
 // ---- maxplus.cu --------------------------------------------------------------
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,
                     const int* labLens, Dims d, cudaStream_t stream);

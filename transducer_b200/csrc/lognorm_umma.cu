@@ -42,7 +42,8 @@ namespace tb200 {
 namespace sm100 {
 
 CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1) {
+                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
+                             bool atom32) {
   typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -63,7 +64,8 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult rc = encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS)
     throw CudaError("cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));

@@ -173,6 +173,21 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smemAddr, uint32_t 
   return d;
 }
 
+// The same for the 128-byte swizzle with 32-byte atoms (rows of 128 bytes, 32-byte chunks
+// XORed with row % 4; what a TMA box written with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B holds):
+// the only layout an MN-major TF32 operand may use.  Atoms are 32 MN-elements x 4 K-rows;
+// lboBytes = distance between atoms along MN, sboBytes = distance between 4-row groups.
+__device__ __forceinline__ uint64_t smem_desc_sw128_base32(uint32_t smemAddr, uint32_t lboBytes,
+                                                           uint32_t sboBytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smemAddr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lboBytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sboBytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;  // SWIZZLE_128B_BASE32B
+  return d;
+}
+
 // Instruction descriptor, kind::tf32, fp32 accumulate, M x N tile.
 // aMajorMN / bMajorMN: 0 = K-major operand, 1 = MN-major operand.
 __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int aMajorMN, int bMajorMN) {
@@ -220,8 +235,10 @@ __device__ __forceinline__ float tf32_round(float x) {
 // ---- host: tensor maps ------------------------------------------------------------
 // fp32 tensor [d2][d1][d0] (d0 innermost, contiguous), box [1][box1][32] with the
 // 128-byte swizzle; out-of-range elements read as zero.
+// atom32 selects the 128-byte swizzle with 32-byte atoms instead of the plain one.
 CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1);
+                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
+                             bool atom32 = false);
 
 }  // namespace sm100
 }  // namespace tb200
