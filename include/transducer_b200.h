@@ -52,9 +52,10 @@ void* tb200_get_stream(void);
 /* Tuning / test switches.  Keys:
  *   "lognorm_path"  0 auto, 1 exact SIMT logsumexp, 2 tensor-core factored GEMM
  *   "grads_path"    0 auto, 1 SIMT, 2 tensor-core
- *   "grad_passes"   1 or 2: TF32 products per gradient GEMM step.  2 (default): the
- *                   exp(E)/exp(P) operands are split hi+lo, the lattice weights rounded
- *                   once (error ~1e-4 of the gradient maximum); 1: everything rounded once
+ *   "grad_passes"   operand precision of the tensor-core gradient kernel.  The lattice
+ *                   weights are always rounded once to TF32.  1: exp(E), exp(P) rounded
+ *                   once too; 2 (default): exp(E) split hi+lo (exact products for
+ *                   pgrads); 3: exp(P) split as well (smaller tiles, slower)
  * Unknown keys return TB200_ERR_INVALID_ARGUMENT.  No counterpart in the reference. */
 int tb200_set_option(const char* key, int value);
 int tb200_get_option(const char* key, int* value);

@@ -40,7 +40,7 @@ def test_reference_cpp_symbols_exported():
 def test_version_and_options_roundtrip():
     assert _lib.lib.tb200_version() >= 100
     v = ctypes.c_int(-1)
-    assert _lib.lib.tb200_get_option(b"grad_passes", ctypes.byref(v)) == 0 and v.value in (1, 2)
+    assert _lib.lib.tb200_get_option(b"grad_passes", ctypes.byref(v)) == 0 and v.value in (1, 2, 3)
     assert _lib.lib.tb200_set_option(b"no_such_key", 1) == 1
     assert b"no_such_key" in _lib.lib.tb200_last_error()
 

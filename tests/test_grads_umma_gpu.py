@@ -46,14 +46,14 @@ SHAPES = [
 
 
 @pytest.mark.parametrize("shape", SHAPES)
-@pytest.mark.parametrize("passes", [2, 1])
+@pytest.mark.parametrize("passes", [3, 2, 1])
 def test_matches_simt_kernels(shape, passes):
     B, T, U, V, std = shape
     case = make(B, T, U, V, std, seed=B + T + U + V)
     _, eg_s, pg_s = grads(*case, path=1)
     _, eg_t, pg_t = grads(*case, path=2, passes=passes)
     assert not torch.isnan(eg_t).any() and not torch.isnan(pg_t).any()
-    tol = 3e-4 if passes == 2 else 2e-3
+    tol = {3: 3e-4, 2: 1e-3, 1: 2e-3}[passes]
     e_err = (eg_t - eg_s).abs().max().item() / eg_s.abs().max().item()
     p_err = (pg_t - pg_s).abs().max().item() / pg_s.abs().max().item()
     assert e_err <= tol and p_err <= tol, (shape, passes, e_err, p_err)

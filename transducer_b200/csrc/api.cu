@@ -179,7 +179,7 @@ int tb200_set_option(const char* key, int value) {
   if (!key) return fail(kErrInvalidArgument, "null option key");
   if (!strcmp(key, "lognorm_path") && value >= 0 && value <= 2) g_opt.lognorm_path = value;
   else if (!strcmp(key, "grads_path") && value >= 0 && value <= 2) g_opt.grads_path = value;
-  else if (!strcmp(key, "grad_passes") && (value == 1 || value == 2)) g_opt.grad_passes = value;
+  else if (!strcmp(key, "grad_passes") && value >= 1 && value <= 3) g_opt.grad_passes = value;
   else return fail(kErrInvalidArgument, std::string("unknown option or bad value: ") + key);
   return kOk;
 }

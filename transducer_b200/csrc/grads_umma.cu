@@ -25,10 +25,12 @@
 // writes 32 consecutive columns of one frame, i.e. coalesced 128-byte stores.  D2 stays in
 // TMEM across all tiles and becomes pgrads[:, v-block] at the end.
 //
-// PASSES = 2: the E-sized operands are split x = hi + lo (hi exactly representable in TF32)
-//             and both halves are multiplied with W rounded once to TF32: the only operand
-//             error left is W's (2^-12 relative, unbiased), ~1e-4 of the gradient's maximum.
-// PASSES = 1: every operand rounded to TF32 once.
+// Operand precision (`passes`): the lattice weights W are always rounded once to TF32
+// (round-to-nearest, 2^-12 relative, unbiased).  passes = 1: exp(E) and exp(P) likewise.
+// passes = 2 (default): exp(E) is split hi + lo with hi exactly representable in TF32, two
+// MMAs per k-step of GEMM2, so pgrads carry only W's rounding.  passes = 3: exp(P) split
+// as well (GEMM1), at the price of a smaller frame tile because both halves of exp(P)^T
+// must stay resident in tensor memory.
 #include <cuda.h>
 
 #include <algorithm>
@@ -73,10 +75,18 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
-template <int TB, int PASSES>
-__global__ void __launch_bounds__(192, 1) grads_umma_kernel(
+constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
+constexpr int kOwnerWarps = 8;
+constexpr int kGradThreads = (kOwnerWarps + 2) * 32;
+
+// ESPLIT / PSPLIT: split exp(E) / exp(P) into TF32 hi + lo (two MMAs per k-step) instead
+// of rounding once.
+template <int TB, bool ESPLIT, bool PSPLIT>
+__global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmWk,
     const __grid_constant__ CUtensorMap tmWmn, const GradParams p) {
+  constexpr int TBH = TB / 2;  // frames per owner half
+  static_assert(TBH % 8 == 0, "tile halves move through TMEM in 8-column pieces");
   const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,7 +108,7 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
                                              ~uintptr_t(1023));
   const int S = p.stages;
   const int nUB = p.ldW / 32;
-  constexpr int kEBoxBytes = TB * 128;             // one 32-column box of the E tile
+  constexpr int kEBoxBytes = TB * 128;  // one 32-column box of the E tile
   constexpr int kEBytes = 4 * kEBoxBytes;
   const int wBoxBytes = TB * 128;
   const int wBytes = nUB * wBoxBytes;
@@ -108,66 +118,109 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
       barD2Done;
   __shared__ uint32_t tmemBase;
   __shared__ int abortFlag;
-  __shared__ int sListN;
+  __shared__ int sWarpCnt[4];
   __shared__ short sListU[128], sListV[128];
+  __shared__ int sLab[128];
+  __shared__ float sPb[128], sPl[128];
+  __shared__ float sNref[3][TB];  // per stage: -rowRef[t] * log2(e) for the tile's frames
+  __shared__ float sEbl[3][TB];   // per stage: blank-arc sums of the tile's frames
+  __shared__ float sEm[3][kMaxStagedLabels][TB];  // per stage: label-arc occupancies
 
   const int nTiles = (T + TB - 1) / TB;
+  const bool blankHere = p.blank >= v0 && p.blank < v0 + kVBlock;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&barFull[s], 1);
-      mbar_init(&barFree[s], 5);  // 4 owner warps done reading E + 1 MMA commit done reading W
+      mbar_init(&barFree[s], kOwnerWarps + 1);  // owner warps done + MMA commit done reading W
     }
-    mbar_init(&barPReady, 4);
-    mbar_init(&barEReady, 4);
+    mbar_init(&barPReady, kOwnerWarps);
+    mbar_init(&barEReady, kOwnerWarps);
     mbar_init(&barE2Free, 1);
     mbar_init(&barD1Full, 1);
-    mbar_init(&barD1Free, 4);
+    mbar_init(&barD1Free, kOwnerWarps);
     mbar_init(&barD2Done, 1);
     abortFlag = 0;
-    // labels that fall into this column block, in label-position order
-    const int* lab = p.labels + (i64)b * (p.maxU - 1);
-    int n = 0;
-    for (int u = 0; u < U - 1 && n < 128; ++u) {
-      const int l = lab[u];
-      if (l >= v0 && l < v0 + kVBlock) {
-        sListU[n] = (short)u;
-        sListV[n] = (short)(l - v0);
-        ++n;
-      }
-    }
-    sListN = n;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  // Per-position data of this utterance and the labels that fall into this column block
+  // (kept in label-position order so repeated labels are combined deterministically).
+  bool inBlock = false;
+  int myLab = -1;
+  if (threadIdx.x < 128) {
+    const int u = threadIdx.x;
+    if (u < U) {
+      sPb[u] = p.pBlank[(i64)b * p.maxU + u];
+      sPl[u] = p.pLabel[(i64)b * p.maxU + u];
+      if (u < U - 1) myLab = p.labels[(i64)b * (p.maxU - 1) + u];
+    }
+    sLab[u] = myLab;
+    inBlock = myLab >= v0 && myLab < v0 + kVBlock;
+    const unsigned m = __ballot_sync(0xffffffffu, inBlock);
+    if (lane == 0) sWarpCnt[warp] = __popc(m);
+  }
+  if (warp == kOwnerWarps + 1) {
     tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x < 128) {
+    const unsigned m = __ballot_sync(0xffffffffu, inBlock);
+    int pos = __popc(m & ((1u << lane) - 1));
+    for (int w = 0; w < warp; ++w) pos += sWarpCnt[w];
+    if (inBlock) {
+      sListU[pos] = (short)threadIdx.x;
+      sListV[pos] = (short)(myLab - v0);
+    }
+  }
+  __syncthreads();
+  const int nList = sWarpCnt[0] + sWarpCnt[1] + sWarpCnt[2] + sWarpCnt[3];
+  const int nStaged = min(nList, kMaxStagedLabels);
+
   const uint32_t tBase = tmemBase;
   const uint32_t cPhi = 0, cPlo = p.Ku;
-  const uint32_t cEhi = (PASSES == 2 ? 2 : 1) * p.Ku, cElo = cEhi + TB;
-  const uint32_t cD1 = cEhi + (PASSES == 2 ? 2 : 1) * TB;
+  const uint32_t cEhi = (PSPLIT ? 2 : 1) * p.Ku, cElo = cEhi + TB;
+  const uint32_t cD1 = cEhi + (ESPLIT ? 2 : 1) * TB;
   const uint32_t cD2 = cD1 + TB;
   volatile int* abortp = &abortFlag;
 
-  if (warp == 4) {
-    // ---------------- TMA producer ----------------
+  if (warp == kOwnerWarps) {
+    // ---------------- producer ----------------
+    // All lanes stage the tile's per-frame scalars (row shifts, blank-arc sums, label-arc
+    // occupancies of this block's labels) in shared memory; lane 0 then arms the barrier
+    // and issues the tile copies.  This runs up to S tiles ahead of the owners, so the
+    // scattered global reads are off their critical path.
     if (lane == 0) {
       tma_prefetch_desc(&tmE);
       tma_prefetch_desc(&tmWk);
       tma_prefetch_desc(&tmWmn);
-      int issued = 0;
-      for (int i = 0; i < nTiles; ++i) {
-        const int s = i % S;
-        if (i >= S && !mbar_wait(&barFree[s], ((i / S) - 1) & 1, abortp, p.status,
-                                 kStatusTimeoutStageFree))
-          break;
+    }
+    const float* refg = p.rowRef + (i64)b * p.maxT;
+    const float* eblg = p.eBlank + (i64)b * p.maxT;
+    const float* emg = p.em + (i64)b * p.maxT * p.maxU;
+    int issued = 0;
+    bool ok = true;
+    for (int i = 0; i < nTiles && ok; ++i) {
+      const int s = i % S;
+      if (i >= S) {
+        ok = mbar_wait(&barFree[s], ((i / S) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      const int t0 = i * TB;
+      for (int t = lane; t < TB; t += 32) {
+        const bool live = t0 + t < T;
+        sNref[s][t] = live ? -refg[t0 + t] * kLog2e : 0.0f;
+        if (blankHere) sEbl[s][t] = live ? eblg[t0 + t] : 0.0f;
+        for (int k = 0; k < nStaged; ++k)
+          sEm[s][k][t] = live ? emg[(i64)(t0 + t) * p.maxU + sListU[k]] : 0.0f;
+      }
+      __syncwarp();
+      if (lane == 0) {
         uint8_t* st = smem + (size_t)s * stageBytes;
         mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
-        const int t0 = i * TB;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           tma_load_3d(st + j * kEBoxBytes, &tmE, &barFull[s], v0 + 32 * j, t0, b);
@@ -175,26 +228,27 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
           tma_load_3d(st + kEBytes + j * wBoxBytes, &tmWk, &barFull[s], 32 * j, t0, b);
           tma_load_3d(st + kEBytes + wBytes + j * wBoxBytes, &tmWmn, &barFull[s], 32 * j, t0, b);
         }
-        issued = i + 1;
       }
-      if (*abortp) {
-        for (int i = max(0, issued - S); i < issued; ++i) {
-          const unsigned long long t1 = global_timer_ns();
-          while (!mbar_try_wait(&barFull[i % S], (i / S) & 1) &&
-                 global_timer_ns() - t1 < 50000000ull) {
-          }
+      issued = i + 1;
+    }
+    if (lane == 0 && *abortp) {
+      // after an abort: give the copies still in flight a bounded time to land
+      for (int i = max(0, issued - S); i < issued; ++i) {
+        const unsigned long long t1 = global_timer_ns();
+        while (!mbar_try_wait(&barFull[i % S], (i / S) & 1) &&
+               global_timer_ns() - t1 < 50000000ull) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kOwnerWarps + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);        // B = W tile, K-major (K = u)
-      const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);     // B = W tile, MN-major (K = t)
+      const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);     // B = W tile, K-major (K = u)
+      const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);  // B = W tile, MN-major (K = t)
       const int kSteps1 = p.Ku / 8;
       // expP^T resident in TMEM.  (Its own barrier: a warp whose columns lie beyond the
-      // vocabulary finishes the prologue early and must not be able to complete this phase
-      // with its first per-tile arrival.)
+      // vocabulary finishes the prologue early and must not be able to complete a per-tile
+      // phase with that arrival.)
       bool ok = mbar_wait(&barPReady, 0, abortp, p.status, kStatusTimeoutOperand);
       for (int i = 0; i < nTiles && ok; ++i) {
         const int s = i % S;
@@ -210,7 +264,7 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
           const uint32_t off = (uint32_t)((ks >> 2) * wBoxBytes + (ks & 3) * 32);
           const uint64_t bW = smem_desc_sw128(wK + off, 16, 1024);
           mma_tf32_ts(tBase + cD1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
-          if (PASSES == 2) mma_tf32_ts(tBase + cD1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
+          if (PSPLIT) mma_tf32_ts(tBase + cD1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
         }
         mma_commit(&barD1Full);
         // GEMM2: D2[v, u] += expE^T . W   (accumulates over all tiles)
@@ -221,7 +275,7 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
           // 8 frames = two 4-row atoms 512 bytes apart; 32-column atoms one box apart
           const uint64_t bW = smem_desc_sw128_base32(wMn + ks * 1024, (uint32_t)wBoxBytes, 512);
           mma_tf32_ts(tBase + cD2, tBase + cEhi + ks * 8, bW, idesc2, (i | ks) ? 1u : 0u);
-          if (PASSES == 2) mma_tf32_ts(tBase + cD2, tBase + cElo + ks * 8, bW, idesc2, 1u);
+          if (ESPLIT) mma_tf32_ts(tBase + cD2, tBase + cElo + ks * 8, bW, idesc2, 1u);
         }
         mma_commit(&barE2Free);
         mma_commit(&barFree[s]);
@@ -229,47 +283,33 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
       if (ok) mma_commit(&barD2Done);
     }
   } else {
-    // ---------------- column owners: thread = vocabulary column = TMEM lane ----------------
-    const int vl = threadIdx.x;          // 0..127
+    // ---------------- column owners ----------------
+    // Thread (q, lane) owns vocabulary column v0 + q*32 + lane = TMEM lane q*32 + lane; the
+    // two halves h = 0,1 of the owner warps split the frames of each tile (and the label
+    // positions of the prologue/epilogue) between them.
+    const int q = warp & 3, h = warp >> 2;
+    const int vl = q * 32 + lane;
     const int v = v0 + vl;
     const bool vOk = v < p.V;
-    const uint32_t laneAddr = (uint32_t)(warp * 32) << 16;
-    const float* e_unused = p.E;
-    (void)e_unused;
+    const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
     bool ok = true;
 
     // expP^T[v, u] = exp(P[u,v] - maxP[u]) for u < U, zero beyond: resident A operand of GEMM1
     {
       const float* pp = p.P + (i64)b * p.maxU * p.V;
       const float* mp = p.maxP + (i64)b * p.maxU;
-      for (int u0 = 0; u0 < p.Ku; u0 += 16) {
-        uint32_t hi[16], lo[16];
+      for (int u0 = 8 * h; u0 < p.Ku; u0 += 16) {
+        uint32_t hi[8], lo[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 8; ++j) {
           const int u = u0 + j;
           float x = 0.0f;
-          if (u < U && vOk) x = exp2f((pp[(i64)u * p.V + v] - mp[u]) * kLog2e);
-          if (PASSES == 2) split_tf32(x, hi[j], lo[j]);
+          if (u < U && vOk) x = ex2_approx((pp[(i64)u * p.V + v] - mp[u]) * kLog2e);
+          if (PSPLIT) split_tf32(x, hi[j], lo[j]);
           else hi[j] = __float_as_uint(tf32_round(x));
         }
-        if (u0 + 16 <= p.Ku) {
-          tmem_st16(tBase + laneAddr + cPhi + u0, hi);
-          if (PASSES == 2) tmem_st16(tBase + laneAddr + cPlo + u0, lo);
-        } else {  // Ku is a multiple of 8: a final half block
-          asm volatile(
-              "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
-                  tBase + laneAddr + cPhi + u0),
-              "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]), "r"(hi[4]), "r"(hi[5]), "r"(hi[6]),
-              "r"(hi[7])
-              : "memory");
-          if (PASSES == 2)
-            asm volatile(
-                "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
-                    tBase + laneAddr + cPlo + u0),
-                "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]), "r"(lo[4]), "r"(lo[5]), "r"(lo[6]),
-                "r"(lo[7])
-                : "memory");
-        }
+        tmem_st8(tBase + laneAddr + cPhi + u0, hi);
+        if (PSPLIT) tmem_st8(tBase + laneAddr + cPlo + u0, lo);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -277,29 +317,35 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
       if (lane == 0) mbar_arrive(&barPReady);
     }
 
-    const float* ref = p.rowRef + (i64)b * p.maxT;
-    const float* ebl = p.eBlank + (i64)b * p.maxT;
     const float* emb = p.em + (i64)b * p.maxT * p.maxU;
-    const int nList = sListN;
 
     for (int i = 0; i < nTiles && ok; ++i) {
       const int s = i % S, t0 = i * TB;
       ok = mbar_wait(&barFull[s], (i / S) & 1, abortp, p.status, kStatusTimeoutTma);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // my column of the raw tile: box = warp, 4-byte element `lane` of each 128-byte row
-      const uint8_t* col = smem + (size_t)s * stageBytes + warp * kEBoxBytes + (lane & 3) * 4;
-      float x[TB];
+      // my column of the raw tile: box q, 4-byte element `lane` of each 128-byte row
+      const uint8_t* col = smem + (size_t)s * stageBytes + q * kEBoxBytes + (lane & 3) * 4;
+      const float* nr = sNref[s] + h * TBH;
+      const int tValid = min(TB, T - t0) - h * TBH;  // live frames in my half (may be <= 0)
+      float x[TBH];
+      if (tValid >= TBH) {
 #pragma unroll
-      for (int t = 0; t < TB; ++t) {
-        const float raw = *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-        const int tt = t0 + t;
-        float e = 0.0f;
-        if (tt < T && vOk) e = exp2f((raw - ref[tt]) * kLog2e);
-        x[t] = e;
+        for (int j = 0; j < TBH; ++j) {
+          const int t = h * TBH + j;
+          const float raw =
+              *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+          x[j] = ex2_approx(fmaf(raw, kLog2e, nr[j]));
+        }
+      } else {  // frames at or beyond T_b contribute nothing
+#pragma unroll
+        for (int j = 0; j < TBH; ++j) {
+          const int t = h * TBH + j;
+          const float raw =
+              *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+          x[j] = (j < tValid) ? ex2_approx(fmaf(raw, kLog2e, nr[j])) : 0.0f;
+        }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&barFree[s]);  // raw E tile of this stage no longer needed
       // expE^T of the previous tile must have been consumed by GEMM2 before it is replaced
       if (i > 0) {
         ok = mbar_wait(&barE2Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutMma);
@@ -307,15 +353,15 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
         if (!ok) break;
       }
 #pragma unroll
-      for (int c = 0; c < TB; c += 16) {
-        uint32_t hi[16], lo[16];
+      for (int c = 0; c < TBH; c += 8) {
+        uint32_t hi[8], lo[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (PASSES == 2) split_tf32(x[c + j], hi[j], lo[j]);
+        for (int j = 0; j < 8; ++j) {
+          if (ESPLIT) split_tf32(x[c + j], hi[j], lo[j]);
           else hi[j] = __float_as_uint(tf32_round(x[c + j]));
         }
-        tmem_st16(tBase + laneAddr + cEhi + c, hi);
-        if (PASSES == 2) tmem_st16(tBase + laneAddr + cElo + c, lo);
+        tmem_st8(tBase + laneAddr + cEhi + h * TBH + c, hi);
+        if (ESPLIT) tmem_st8(tBase + laneAddr + cElo + h * TBH + c, lo);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -327,74 +373,69 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float d1[TB];
+      float d1[TBH];
 #pragma unroll
-      for (int c = 0; c < TB; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(tBase + laneAddr + cD1 + c, r);
-        tmem_wait_ld();
+      for (int c = 0; c < TBH; c += 8) {
+        uint32_t r[8];
+        tmem_ld8(tBase + laneAddr + cD1 + h * TBH + c, r);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) d1[c + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 8; ++j) d1[c + j] = __uint_as_float(r[j]);
       }
+      tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&barD1Free);
 #pragma unroll
-      for (int t = 0; t < TB; ++t) d1[t] *= x[t];
+      for (int j = 0; j < TBH; ++j) d1[j] *= x[j];
       if (v == p.blank) {
+        const float* eb = sEbl[s] + h * TBH;
 #pragma unroll
-        for (int t = 0; t < TB; ++t)
-          if (t0 + t < T) d1[t] -= ebl[t0 + t];
+        for (int j = 0; j < TBH; ++j) d1[j] -= eb[j];
       }
-      for (int k = 0; k < nList; ++k) {
+      for (int k = 0; k < nStaged; ++k) {
+        if (sListV[k] == vl) {
+          const float* m = sEm[s][k] + h * TBH;
+#pragma unroll
+          for (int j = 0; j < TBH; ++j) d1[j] -= m[j];
+        }
+      }
+      for (int k = nStaged; k < nList; ++k) {  // more labels in this block than are staged
         if (sListV[k] == vl) {
           const int u = sListU[k];
 #pragma unroll
-          for (int t = 0; t < TB; ++t)
-            if (t0 + t < T) d1[t] -= emb[(i64)(t0 + t) * p.maxU + u];
+          for (int j = 0; j < TBH; ++j)
+            if (j < tValid) d1[j] -= emb[(i64)(t0 + h * TBH + j) * p.maxU + u];
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&barFree[s]);  // stage s (tile + staged scalars) released
       if (vOk) {
+        float* dst = eg + (i64)(t0 + h * TBH) * p.V + v;
+        if (tValid >= TBH) {
 #pragma unroll
-        for (int t = 0; t < TB; ++t)
-          if (t0 + t < p.maxT) eg[(i64)(t0 + t) * p.V + v] = (t0 + t < T) ? delta * d1[t] : 0.0f;
+          for (int j = 0; j < TBH; ++j) dst[(i64)j * p.V] = delta * d1[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBH; ++j)
+            if (t0 + h * TBH + j < p.maxT) dst[(i64)j * p.V] = (j < tValid) ? delta * d1[j] : 0.0f;
+        }
       }
     }
 
     // padded frames beyond the last tile: exact zeros
     if (vOk)
-      for (int t = nTiles * TB; t < p.maxT; ++t) eg[(i64)t * p.V + v] = 0.0f;
+      for (int t = nTiles * TB + h; t < p.maxT; t += 2) eg[(i64)t * p.V + v] = 0.0f;
 
     // pgrads[u, v] = delta * (expP[u,v] * D2[v,u] - sparse)
     if (ok) ok = mbar_wait(&barD2Done, 0, abortp, p.status, kStatusTimeoutMma);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      const int* lab = p.labels + (i64)b * (p.maxU - 1);
-      const float* pb = p.pBlank + (i64)b * p.maxU;
-      const float* pl = p.pLabel + (i64)b * p.maxU;
-      for (int u0 = 0; u0 < p.Ku; u0 += 8) {
+      for (int u0 = 8 * h; u0 < p.Ku; u0 += 16) {
         uint32_t d2[8], xh[8], xl[8];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-            : "=r"(d2[0]), "=r"(d2[1]), "=r"(d2[2]), "=r"(d2[3]), "=r"(d2[4]), "=r"(d2[5]),
-              "=r"(d2[6]), "=r"(d2[7])
-            : "r"(tBase + laneAddr + cD2 + u0)
-            : "memory");
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-            : "=r"(xh[0]), "=r"(xh[1]), "=r"(xh[2]), "=r"(xh[3]), "=r"(xh[4]), "=r"(xh[5]),
-              "=r"(xh[6]), "=r"(xh[7])
-            : "r"(tBase + laneAddr + cPhi + u0)
-            : "memory");
-        if (PASSES == 2) {
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-              : "=r"(xl[0]), "=r"(xl[1]), "=r"(xl[2]), "=r"(xl[3]), "=r"(xl[4]), "=r"(xl[5]),
-                "=r"(xl[6]), "=r"(xl[7])
-              : "r"(tBase + laneAddr + cPlo + u0)
-              : "memory");
-        }
+        tmem_ld8(tBase + laneAddr + cD2 + u0, d2);
+        tmem_ld8(tBase + laneAddr + cPhi + u0, xh);
+        if (PSPLIT) tmem_ld8(tBase + laneAddr + cPlo + u0, xl);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -403,10 +444,10 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
             float val = 0.0f;
             if (u < U) {
               float xp = __uint_as_float(xh[j]);
-              if (PASSES == 2) xp += __uint_as_float(xl[j]);
+              if (PSPLIT) xp += __uint_as_float(xl[j]);
               val = xp * __uint_as_float(d2[j]);
-              if (v == p.blank) val -= pb[u];
-              if (u < U - 1 && lab[u] == v) val -= pl[u];
+              if (v == p.blank) val -= sPb[u];
+              if (sLab[u] == v) val -= sPl[u];
               val *= delta;
             }
             pg[(i64)u * p.V + v] = val;
@@ -420,7 +461,7 @@ __global__ void __launch_bounds__(192, 1) grads_umma_kernel(
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
+  if (warp == kOwnerWarps + 1) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
 }
 
 int pow2_cols(int x) {
@@ -466,30 +507,34 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
   }
 }
 
-template <int TB, int PASSES>
+template <int TB, bool ESPLIT, bool PSPLIT>
 void launch_variant(const CUtensorMap& tmE, const CUtensorMap& tmWk, const CUtensorMap& tmWmn,
                     GradParams p, Dims d, cudaStream_t stream) {
   const int nUB = p.ldW / 32;
   const int stageBytes = 4 * TB * 128 + 2 * nUB * TB * 128;
-  int stages = std::min(3, (225 * 1024 - 1024) / stageBytes);
+  cudaFuncAttributes fa;
+  TB200_CUDA_CHECK(cudaFuncGetAttributes(&fa, grads_umma_kernel<TB, ESPLIT, PSPLIT>));
+  const int room = 227 * 1024 - (int)fa.sharedSizeBytes - 2048;
+  int stages = std::min(3, room / stageBytes);
   if (stages < 1) throw std::invalid_argument("gradient tile does not fit shared memory");
   p.stages = stages;
-  const int cols = (PASSES == 2 ? 2 : 1) * (p.Ku + TB) + TB + p.ldW;
+  const int cols = (PSPLIT ? 2 : 1) * p.Ku + (ESPLIT ? 2 : 1) * TB + TB + p.ldW;
   if (cols > 512) throw std::invalid_argument("gradient tile does not fit tensor memory");
   p.tmemCols = pow2_cols(cols);
   size_t smem = (size_t)stages * stageBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it may hold all 512 TMEM columns
-  TB200_CUDA_CHECK(cudaFuncSetAttribute(grads_umma_kernel<TB, PASSES>,
+  TB200_CUDA_CHECK(cudaFuncSetAttribute(grads_umma_kernel<TB, ESPLIT, PSPLIT>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(div_up(d.V, kVBlock), d.B);
   ScopedKernel sk("grads_umma", stream);
-  grads_umma_kernel<TB, PASSES><<<grid, 192, smem, stream>>>(tmE, tmWk, tmWmn, p);
+  grads_umma_kernel<TB, ESPLIT, PSPLIT><<<grid, kGradThreads, smem, stream>>>(tmE, tmWk, tmWmn, p);
 }
 
+// Largest frame tile whose operands and accumulators fit the 512 TMEM columns:
+// (1|2)*Ku (expP^T) + (1|2)*TB (expE^T) + TB (D1) + ldW (D2).
 int pick_tile(int Ku, int ldW, int passes) {
-  const int f = passes == 2 ? 2 : 1;
-  // columns: f*Ku (expP^T) + f*TB (expE^T) + TB (D1) + ldW (D2) <= 512
-  const int room = (512 - f * Ku - ldW) / (f + 1);
+  const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
+  const int room = (512 - fp * Ku - ldW) / (fe + 1);
   if (room >= 64) return 64;
   if (room >= 48) return 48;
   if (room >= 32) return 32;
@@ -544,12 +589,13 @@ void launch_grads_umma(const float* E, const float* P, const float* rowRef, cons
   const CUtensorMap tmWmn =
       make_tmap_f32_3d(W, (uint64_t)p.ldW, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)p.ldW * 4,
                        (uint64_t)d.maxT * p.ldW * 4, TB, /*atom32=*/true);
-#define GO(TBV, PV) launch_variant<TBV, PV>(tmE, tmWk, tmWmn, p, d, stream)
-  if (passes == 2) {
-    if (TB == 64) GO(64, 2); else if (TB == 48) GO(48, 2); else GO(32, 2);
-  } else {
-    if (TB == 64) GO(64, 1); else if (TB == 48) GO(48, 1); else GO(32, 1);
-  }
+#define GO(TBV, EV, PV) launch_variant<TBV, EV, PV>(tmE, tmWk, tmWmn, p, d, stream)
+#define GO_TB(EV, PV) \
+  do { if (TB == 64) GO(64, EV, PV); else if (TB == 48) GO(48, EV, PV); else GO(32, EV, PV); } while (0)
+  if (passes == 3) GO_TB(true, true);
+  else if (passes == 2) GO_TB(true, false);
+  else GO_TB(false, false);
+#undef GO_TB
 #undef GO
   TB200_CHECK_LAUNCH();
 }

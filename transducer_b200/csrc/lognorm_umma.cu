@@ -289,13 +289,22 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
       }
       const float nref = -ref * kLog2e;
       uint32_t hi[32], lo[32];
+      if (kLeft >= kChunkK) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float e = exp2f(fmaf(x[j], kLog2e, nref));
-        if (j >= kLeft) e = 0.0f;
-        const uint32_t h = __float_as_uint(e) & 0xffffe000u;
-        hi[j] = h;
-        lo[j] = __float_as_uint(e - __uint_as_float(h));
+        for (int j = 0; j < 32; ++j) {
+          const float e = ex2_approx(fmaf(x[j], kLog2e, nref));
+          const uint32_t h = __float_as_uint(e) & 0xffffe000u;
+          hi[j] = h;
+          lo[j] = __float_as_uint(e - __uint_as_float(h));
+        }
+      } else {  // last chunk of a vocabulary that is not a multiple of 32
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float e = (j < kLeft) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
+          const uint32_t h = __float_as_uint(e) & 0xffffe000u;
+          hi[j] = h;
+          lo[j] = __float_as_uint(e - __uint_as_float(h));
+        }
       }
       const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
       tmem_st16(dst, reinterpret_cast<const uint32_t(&)[16]>(hi[0]));
@@ -329,14 +338,18 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
       tc_fence_after();
       const uint32_t src = tBase + laneAddr + (uint32_t)(a * p.nPad + c0);
 #pragma unroll
-      for (int i = 0; i < kDrainCols / 16; ++i) {
-        if (c0 + i * 16 < c1) {
-          uint32_t v[16];
-          tmem_ld16(src + i * 16, v);
-          tmem_wait_ld();
+      for (int i0 = 0; i0 < kDrainCols / 16; i0 += 2) {  // two loads in flight per wait
+        uint32_t v[2][16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sum[i * 16 + j] += __uint_as_float(v[j]);
-        }
+        for (int i = 0; i < 2; ++i)
+          if (c0 + (i0 + i) * 16 < c1) tmem_ld16(src + (i0 + i) * 16, v[i]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          if (c0 + (i0 + i) * 16 < c1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[(i0 + i) * 16 + j] += __uint_as_float(v[i][j]);
+          }
       }
       tc_fence_before();
       __syncwarp();
