@@ -98,6 +98,32 @@ int tb200_viterbi(const float* emissions, const float* predictions,
                   const int* labelLengths, int batchSize, int maxInputLength,
                   int maxLabelLength, int alphabetSize, int blank);
 
+/* tb200_viterbi for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference (whose viterbi always calls cudaMallocAsync, transducer_cuda.cu:364-369).
+ *
+ * Who needs it: a host process whose device memory is entirely claimed by another
+ * allocator (a framework's caching allocator, a server's fixed arena), so that the
+ * driver's stream-ordered pool has nothing left to give; a device or virtual GPU without
+ * memory-pool support, where cudaMallocAsync does not exist; a decoding loop that cannot
+ * afford an allocation's occasional pool growth or synchronisation.
+ *
+ * Same arguments and result as tb200_viterbi.  The temporaries live in a fixed array inside
+ * the library (about 17 MiB, resident on every GPU that loads the library until the process
+ * ends), so the lattice is limited to tb200_viterbi_static_max_nodes() =
+ * 4 Mi nodes of batchSize*maxInputLength*maxLabelLength (and 160 Ki back-pointer words,
+ * batchSize*maxLabelLength*ceil(maxInputLength/32)); larger calls return
+ * TB200_ERR_WORKSPACE without touching anything.  The call performs no allocation of any
+ * kind.  The first call on each device looks up the array's device address and caches it:
+ * make that first call with the device current and before any stream capture begins.
+ * All calls share the one array and it keeps whatever the last call left (nothing in it
+ * needs to be zero on entry), so two calls whose GPU work may overlap -- different streams,
+ * different host threads -- race with each other: serialise them. */
+size_t tb200_viterbi_static_max_nodes(void);
+int tb200_viterbi_static(const float* emissions, const float* predictions,
+                         const float* logNorms, int* labels, const int* inputLengths,
+                         const int* labelLengths, int batchSize, int maxInputLength,
+                         int maxLabelLength, int alphabetSize, int blank);
+
 /* ---- the arithmetic the reference does in torch ops ------------------------- */
 
 /* transducer/torch_binding.py:35-40 and :162-167: logNorms[b,t,u] =

@@ -34,6 +34,8 @@ SIGNATURES = {
     "tb200_forward": (_i, [_p] * 8 + [_i] * 5),
     "tb200_backward": (_i, [_p] * 10 + [_i] * 5),
     "tb200_viterbi": (_i, [_p] * 6 + [_i] * 5),
+    "tb200_viterbi_static_max_nodes": (_z, []),
+    "tb200_viterbi_static": (_i, [_p] * 6 + [_i] * 5),
     "tb200_log_norms_workspace_bytes": (_z, [_i] * 4),
     "tb200_log_norms": (_i, [_p] * 7 + [_i] * 4 + [_p, _z]),
     "tb200_loss_forward_workspace_bytes": (_z, [_i] * 4),

@@ -5,6 +5,7 @@
 
 #include "../../include/transducer.h"
 #include "../../include/transducer_b200.h"
+#include "api_internal.h"
 #include "kernels.h"
 #include "profile.h"
 
@@ -159,6 +160,10 @@ void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
 }
 
 }  // namespace
+
+int api_fail(int code, const std::string& msg) { return fail(code, msg); }
+cudaStream_t api_stream() { return g_stream; }
+
 }  // namespace tb200
 
 using namespace tb200;
