@@ -142,14 +142,19 @@ struct LnParams {
 // So an accumulator only ever sees kGroup chunks (12*kGroup steps); the drain warps then
 // add it, round-to-nearest, into fp32 registers and the MMA starts a fresh accumulator.
 constexpr int kGroup = 2;
-constexpr int kDrainCols = 128;  // accumulator columns owned by one drain warpgroup
-
-template <int NDRAIN>
-__global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
+// NTW   transform warpgroups (1 or 2): with 2, each thread handles 16 of the 32 columns of a
+//       chunk row, which puts two transform warps on every SM sub-partition and hides the
+//       latency of the exp / TMEM-store chain.
+// NDRAIN drain warpgroups, each owning DCOLS accumulator columns (fp32 sums in registers).
+template <int NTW, int NDRAIN, int DCOLS>
+__global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 2) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
     const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
-  constexpr int kProducerWarp = 4 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
-  constexpr int kThreads = (6 + 4 * NDRAIN) * 32;
+  constexpr int kDrainWarp0 = 4 * NTW;
+  constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
+  constexpr int kThreads = (kMmaWarp + 1) * 32;
+  constexpr int kDrainCols = DCOLS;
+  constexpr int kColsPerThread = kChunkK / NTW;  // chunk columns one transform thread handles
   const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
   if (t0 >= T || U <= 0) return;  // before any allocation or barrier
@@ -173,7 +178,7 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&barFull[s], 1);
-      mbar_init(&barReady[s], 4);
+      mbar_init(&barReady[s], 4 * NTW);
       mbar_init(&barDone[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -258,10 +263,12 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
         if (c % kGroup == kGroup - 1 || c == nChunks - 1) mma_commit(&barAccFull[a]);
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < kDrainWarp0) {
     // ---------------- operand transform (thread = frame = TMEM lane) ----------------
-    const int r = threadIdx.x;  // 0..127
-    const uint32_t laneAddr = (uint32_t)(warp * 32) << 16;
+    const int q = warp & 3, hcol = warp >> 2;   // lane quarter, column half of the chunk
+    const int r = q * 32 + lane;                // frame within the tile, 0..127
+    const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
+    constexpr int NC = kColsPerThread;
     float ref = 0.0f;
     bool ok = true;
     for (int c = 0; c < nChunks && ok; ++c) {
@@ -270,58 +277,70 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
       if (!ok) break;
       const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 q = *reinterpret_cast<const float4*>(row + ((j ^ (r & 7)) << 4));
-        x[4 * j] = q.x; x[4 * j + 1] = q.y; x[4 * j + 2] = q.z; x[4 * j + 3] = q.w;
-      }
       const int kLeft = p.V - c * kChunkK;  // valid columns in this chunk
       if (c == 0) {
+        // the frame's shift: maximum of the first 32 entries of the row
         float m = neg_inf();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (j < kLeft) m = fmaxf(m, x[j]);
+        for (int j = 0; j < 8; ++j) {
+          const float4 v4 = *reinterpret_cast<const float4*>(row + ((j ^ (r & 7)) << 4));
+          if (4 * j < kLeft) m = fmaxf(m, v4.x);
+          if (4 * j + 1 < kLeft) m = fmaxf(m, v4.y);
+          if (4 * j + 2 < kLeft) m = fmaxf(m, v4.z);
+          if (4 * j + 3 < kLeft) m = fmaxf(m, v4.w);
+        }
         // a -inf/NaN prefix would poison every term; fall back to 0 and let the
         // range check route the row to the exact path if needed
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
-        sRef[r] = ref;
-        if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
+        if (hcol == 0) {
+          sRef[r] = ref;
+          if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
+        }
+      }
+      float x[NC];
+#pragma unroll
+      for (int j = 0; j < NC / 4; ++j) {
+        const int jj = hcol * (NC / 4) + j;  // 16-byte piece of the 128-byte row
+        const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
+        x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
       }
       const float nref = -ref * kLog2e;
-      uint32_t hi[32], lo[32];
-      if (kLeft >= kChunkK) {
+      const int kLeftMine = kLeft - hcol * NC;
+      uint32_t hi[NC], lo[NC];
+      if (kLeftMine >= NC) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < NC; ++j) {
           const float e = ex2_approx(fmaf(x[j], kLog2e, nref));
-          const uint32_t h = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = h;
-          lo[j] = __float_as_uint(e - __uint_as_float(h));
+          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
+          hi[j] = hbits;
+          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
         }
       } else {  // last chunk of a vocabulary that is not a multiple of 32
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float e = (j < kLeft) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
-          const uint32_t h = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = h;
-          lo[j] = __float_as_uint(e - __uint_as_float(h));
+        for (int j = 0; j < NC; ++j) {
+          const float e = (j < kLeftMine) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
+          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
+          hi[j] = hbits;
+          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
         }
       }
-      const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
-      tmem_st16(dst, reinterpret_cast<const uint32_t(&)[16]>(hi[0]));
-      tmem_st16(dst + 16, reinterpret_cast<const uint32_t(&)[16]>(hi[16]));
-      tmem_st16(dst + 32, reinterpret_cast<const uint32_t(&)[16]>(lo[0]));
-      tmem_st16(dst + 48, reinterpret_cast<const uint32_t(&)[16]>(lo[16]));
+      const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64 + hcol * NC);
+#pragma unroll
+      for (int j = 0; j < NC; j += 16) {
+        tmem_st16(dst + j, reinterpret_cast<const uint32_t(&)[16]>(hi[j]));
+        tmem_st16(dst + 32 + j, reinterpret_cast<const uint32_t(&)[16]>(lo[j]));
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&barReady[s]);
-        if (c == 0) mbar_arrive(&barRef);
+        if (c == 0 && hcol == 0) mbar_arrive(&barRef);
       }
     }
   } else {
     // ---------------- accumulator drain + epilogue ----------------
-    const int h = (warp - 4) >> 2;               // which 128-column slice
+    const int h = (warp - kDrainWarp0) >> 2;     // which column slice
     const int q = warp & 3;                      // TMEM lane quarter this warp may touch
     const int r = q * 32 + lane;
     const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
@@ -337,15 +356,16 @@ __global__ void __launch_bounds__((6 + 4 * NDRAIN) * 32, 1) lognorm_umma_kernel(
       if (!ok) break;
       tc_fence_after();
       const uint32_t src = tBase + laneAddr + (uint32_t)(a * p.nPad + c0);
+      constexpr int kBatch = (DCOLS >= 128) ? 2 : 1;  // TMEM loads in flight per wait
 #pragma unroll
-      for (int i0 = 0; i0 < kDrainCols / 16; i0 += 2) {  // two loads in flight per wait
-        uint32_t v[2][16];
+      for (int i0 = 0; i0 < kDrainCols / 16; i0 += kBatch) {
+        uint32_t v[kBatch][16];
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < kBatch; ++i)
           if (c0 + (i0 + i) * 16 < c1) tmem_ld16(src + (i0 + i) * 16, v[i]);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < kBatch; ++i)
           if (c0 + (i0 + i) * 16 < c1) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) sum[(i0 + i) * 16 + j] += __uint_as_float(v[i][j]);
@@ -498,14 +518,14 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   dim3 grid(div_up(d.maxT, kTileM), d.B);
   {
     ScopedKernel sk("lognorm_umma", stream);
-    if (nPad <= kDrainCols) {
-      TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel<1>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      lognorm_umma_kernel<1><<<grid, 10 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+    if (nPad <= 128) {
+      auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      k<<<grid, 18 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     } else {
-      TB200_CUDA_CHECK(cudaFuncSetAttribute(lognorm_umma_kernel<2>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      lognorm_umma_kernel<2><<<grid, 14 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+      auto k = lognorm_umma_kernel<1, 2, 128>;  // 4 transform + 8 drain (128 columns each) warps
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      k<<<grid, 14 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     }
   }
   TB200_CHECK_LAUNCH();
