@@ -77,7 +77,7 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
 
 constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
 constexpr int kOwnerWarps = 8;
-constexpr int kGradThreads = (kOwnerWarps + 2) * 32;
+constexpr int kGradThreads = (kOwnerWarps + 3) * 32;  // + producer + two MMA issuers
 
 // ESPLIT / PSPLIT: split exp(E) / exp(P) into TF32 hi + lo (two MMAs per k-step) instead
 // of rounding once.
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&barFull[s], 1);
-      mbar_init(&barFree[s], kOwnerWarps + 1);  // owner warps done + MMA commit done reading W
+      mbar_init(&barFree[s], kOwnerWarps + 2);  // owner warps + both MMA issuers done with it
     }
     mbar_init(&barPReady, kOwnerWarps);
     mbar_init(&barEReady, kOwnerWarps);
@@ -241,10 +241,12 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       }
     }
   } else if (warp == kOwnerWarps + 1) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- MMA issuer 1: GEMM1, D1[v, t] = expP^T . W^T per tile ----------------
+    // (GEMM1 and GEMM2 write different accumulators and read different A operands, so each
+    // has its own issuing thread: the barrier waits and commits of one overlap the MMAs of
+    // the other.)
     if (lane == 0) {
-      const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);     // B = W tile, K-major (K = u)
-      const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);  // B = W tile, MN-major (K = t)
+      const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);  // B = W tile, K-major (K = u)
       const int kSteps1 = p.Ku / 8;
       // expP^T resident in TMEM.  (Its own barrier: a warp whose columns lie beyond the
       // vocabulary finishes the prologue early and must not be able to complete a per-tile
@@ -258,8 +260,6 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         if (!ok) break;
         tc_fence_after();
         const uint32_t wK = smem_u32(smem + (size_t)s * stageBytes + kEBytes);
-        const uint32_t wMn = wK + (uint32_t)wBytes;
-        // GEMM1: D1[v, t] = expP^T . W^T  (fresh accumulator every tile)
         for (int ks = 0; ks < kSteps1; ++ks) {
           const uint32_t off = (uint32_t)((ks >> 2) * wBoxBytes + (ks & 3) * 32);
           const uint64_t bW = smem_desc_sw128(wK + off, 16, 1024);
@@ -267,10 +267,21 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
           if (PSPLIT) mma_tf32_ts(tBase + cD1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
         }
         mma_commit(&barD1Full);
-        // GEMM2: D2[v, u] += expE^T . W   (accumulates over all tiles)
-        ok = mbar_wait(&barEReady, i & 1, abortp, p.status, kStatusTimeoutOperand);
+        mma_commit(&barFree[s]);
+      }
+    }
+  } else if (warp == kOwnerWarps + 2) {
+    // ---------------- MMA issuer 2: GEMM2, D2[v, u] += expE^T . W over all tiles ----------------
+    if (lane == 0) {
+      const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);  // B = W tile, MN-major (K = t)
+      bool ok = true;
+      for (int i = 0; i < nTiles && ok; ++i) {
+        const int s = i % S;
+        ok = mbar_wait(&barFull[s], (i / S) & 1, abortp, p.status, kStatusTimeoutTma) &&
+             mbar_wait(&barEReady, i & 1, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t wMn = smem_u32(smem + (size_t)s * stageBytes + kEBytes) + (uint32_t)wBytes;
         for (int ks = 0; ks < TB / 8; ++ks) {
           // 8 frames = two 4-row atoms 512 bytes apart; 32-column atoms one box apart
           const uint64_t bW = smem_desc_sw128_base32(wMn + ks * 1024, (uint32_t)wBoxBytes, 512);

@@ -20,7 +20,7 @@
 //               registers (round-to-nearest) and hand the accumulator back, so the tensor
 //               core's truncating accumulation never runs over more than 24 steps.
 //   next warp   TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage.
-//   last warp   MMA issuer: per 8-wide k-step three kind::tf32 MMAs
+//   last 2 warps MMA issuers (one accumulator each): per 8-wide k-step three kind::tf32 MMAs
 //               hi*Bhi + lo*Bhi + hi*Blo into the current accumulator (the 3xTF32 split
 //               reproduces fp32 products to ~2^-21 relative).
 //
@@ -147,12 +147,12 @@ constexpr int kGroup = 2;
 //       latency of the exp / TMEM-store chain.
 // NDRAIN drain warpgroups, each owning DCOLS accumulator columns (fp32 sums in registers).
 template <int NTW, int NDRAIN, int DCOLS>
-__global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 2) * 32, 1) lognorm_umma_kernel(
+__global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
     const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
   constexpr int kDrainWarp0 = 4 * NTW;
   constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
-  constexpr int kThreads = (kMmaWarp + 1) * 32;
+  constexpr int kThreads = (kMmaWarp + 2) * 32;  // two MMA-issuing warps
   constexpr int kDrainCols = DCOLS;
   constexpr int kColsPerThread = kChunkK / NTW;  // chunk columns one transform thread handles
   const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
@@ -232,19 +232,27 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 2) * 32, 1) lognorm_um
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp >= kMmaWarp) {
+    // ---------------- MMA issuers ----------------
+    // One elected thread in each of two warps.  Issuer m owns accumulator m and therefore
+    // the chunk groups g with g % 2 == m: while one issuer is blocked on its barrier waits
+    // and commits (~800 cycles per chunk, measured), the other keeps the tensor pipe fed.
+    // The two never touch the same accumulator or operand stage, so no order between their
+    // MMAs is needed.  With a single accumulator only issuer 0 works.
+    const int m = warp - kMmaWarp;
+    if (lane == 0 && m < nAcc) {
       const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
       bool ok = true;
       for (int c = 0; c < nChunks && ok; ++c) {
         const int s = c % S, g = c / kGroup, a = g % nAcc;
+        if (a != m) continue;
         const uint32_t ph = (c / S) & 1;
         if (c % kGroup == 0 && g >= nAcc)
           ok = mbar_wait(&barAccEmpty[a], ((g / nAcc) - 1) & 1, abortp, p.status,
                          kStatusTimeoutStageFree);
-        ok = ok && mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma) &&
-             mbar_wait(&barReady[s], ph, abortp, p.status, kStatusTimeoutOperand);
+        // the transform warps arrive on barReady only after they saw barFull complete, so
+        // the copies of this stage (the exp(P) tiles among them) have landed as well
+        ok = ok && mbar_wait(&barReady[s], ph, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
         const uint32_t bHi = smem_u32(smem + (size_t)s * stageBytes + kRawBytes);
@@ -521,11 +529,11 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
     if (nPad <= 128) {
       auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 18 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     } else {
       auto k = lognorm_umma_kernel<1, 2, 128>;  // 4 transform + 8 drain (128 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 14 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+      k<<<grid, 15 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     }
   }
   TB200_CHECK_LAUNCH();
