@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(&barFull[s], 1);
+      mbar_init(&barFull[s], 2);  // the copies (transaction bytes) + the staged scalars
       mbar_init(&barFree[s], kOwnerWarps + 2);  // owner warps + both MMA issuers done with it
     }
     mbar_init(&barPReady, kOwnerWarps);
@@ -210,15 +210,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         if (!ok) break;
       }
       const int t0 = i * TB;
-      for (int t = lane; t < TB; t += 32) {
-        const bool live = t0 + t < T;
-        sNref[s][t] = live ? -refg[t0 + t] * kLog2e : 0.0f;
-        if (blankHere) sEbl[s][t] = live ? eblg[t0 + t] : 0.0f;
-        for (int k = 0; k < nStaged; ++k)
-          sEm[s][k][t] = live ? emg[(i64)(t0 + t) * p.maxU + sListU[k]] : 0.0f;
-      }
-      __syncwarp();
-      if (lane == 0) {
+      if (lane == 0) {  // copies first: their latency overlaps the scalar staging below
         uint8_t* st = smem + (size_t)s * stageBytes;
         mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
 #pragma unroll
@@ -229,6 +221,15 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
           tma_load_3d(st + kEBytes + wBytes + j * wBoxBytes, &tmWmn, &barFull[s], 32 * j, t0, b);
         }
       }
+      for (int t = lane; t < TB; t += 32) {
+        const bool live = t0 + t < T;
+        sNref[s][t] = live ? -refg[t0 + t] * kLog2e : 0.0f;
+        if (blankHere) sEbl[s][t] = live ? eblg[t0 + t] : 0.0f;
+        for (int k = 0; k < nStaged; ++k)
+          sEm[s][k][t] = live ? emg[(i64)(t0 + t) * p.maxU + sListU[k]] : 0.0f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&barFull[s]);
       issued = i + 1;
     }
     if (lane == 0 && *abortp) {
