@@ -319,7 +319,12 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the
 # named kernel; see the summaries under profiles/.  Keyed by (workload, kernel).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    ("c3", "grads_umma"): 2547751680 + 2680469760,     # profiles/grads_umma_c3.md
+    ("c3", "lognorm_umma"): 2604874496 + 16799744,     # profiles/lognorm_umma_c3.md
+    ("c3", "alpha_wavefront"): 44124416 + 120832,      # profiles/wavefront_kernels_c3.md
+    ("c3", "gamma_wavefront"): 66929152 + 7387136,
+}
 
 
 def kernel_algorithmic_bytes(w, il, ll):
