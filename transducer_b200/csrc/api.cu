@@ -99,7 +99,7 @@ struct ForwardWs {
 };
 
 struct BackwardWs {
-  float *expP, *Ws, *EMs, *W, *em, *eBlank, *pBlank, *pLabel, *maxPScratch;
+  float *expP, *Ws, *EMs, *W, *em, *emT, *nref, *ebl, *eBlank, *pBlank, *pLabel, *maxPScratch;
   int* status;
   BackwardWs(Carver& c, const Dims& d) {
     const SkewGeom g = skew_geom(d);
@@ -109,7 +109,10 @@ struct BackwardWs {
     Ws = c.take<float>(B * g.stride);
     EMs = c.take<float>(B * g.stride);
     W = c.take<float>(B * T * ld_w(d));
-    em = c.take<float>(B * T * U);
+    em = c.take<float>(B * T * U);            // SIMT path
+    emT = c.take<float>(B * U * grads_umma_ld_t(d));  // tensor-core path
+    nref = c.take<float>(B * grads_umma_ld_t(d));
+    ebl = c.take<float>(B * grads_umma_ld_t(d));
     eBlank = c.take<float>(B * T);
     pBlank = c.take<float>(B * U);
     pLabel = c.take<float>(B * U);
@@ -358,17 +361,18 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
                       inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
                       g_stream);
     const int passes = g_opt.grad_passes;
-    const bool can = grads_umma_supported(E, d, passes);
+    const bool can = grads_umma_supported(E, egrads, d, passes);
     if (g_opt.grads_path == 2 && !can)
       throw std::invalid_argument(
           "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
-          "maxLabelLength <= 128 and 16-byte aligned emissions");
+          "maxLabelLength <= 128 and 16-byte aligned emissions and egrads");
     if (can && g_opt.grads_path != 1) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
-      launch_unskew_round(ws.Ws, ws.EMs, ws.W, ws.em, inLens, labLens, g, d, g_stream);
-      launch_grads_umma(E, P, st.rowRef, st.maxP, ws.W, ws.em, ws.eBlank, ws.pBlank,
-                        ws.pLabel, labels, deltas, egrads, pgrads, inLens, labLens, d, passes,
-                        ws.status, g_stream);
+      launch_unskew_round(ws.Ws, ws.EMs, st.rowRef, ws.eBlank, ws.W, ws.emT, ws.nref, ws.ebl,
+                          inLens, labLens, g, d, g_stream);
+      launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
+                        labels, deltas, egrads, pgrads, inLens, labLens, d, passes, ws.status,
+                        g_stream);
       return;
     }
     launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);

@@ -5,25 +5,31 @@
 //   egrads[t,v] = delta * ( expE[t,v] * sum_u W[t,u] expP[u,v]  - sparse_E[t,v] )
 //   pgrads[u,v] = delta * ( expP[u,v] * sum_t W[t,u] expE[t,v]  - sparse_P[u,v] )
 // with two batched SGEMMs and ~8 elementwise passes over E-sized tensors, keeping
-// expE = exp(E - maxE) from the forward pass.  Here E is read once, expE is recomputed
-// in registers, every gradient element is written once, and nothing E-sized is stored.
+// expE = exp(E - maxE) from the forward pass.  Here E is read once, expE is recomputed,
+// every gradient element is written once, and nothing E-sized is stored.
 //
 // Work decomposition: one CTA per (utterance b, block of 128 vocabulary columns); it walks
-// the frames of the utterance in tiles of Tb.  Everything is laid out with the VOCABULARY
+// the frames of the utterance in tiles of TB.  Everything is laid out with the VOCABULARY
 // column on the 128 TMEM lanes (UMMA M = 128):
-//   GEMM1  D1[v, t] = sum_u expP^T[v,u] * W[t,u]        A = expP^T in TMEM (resident for the
-//                                                        whole CTA), B = W tile in smem, K-major
-//   GEMM2  D2[v, u] += sum_t expE^T[v,t] * W[t,u]       A = expE^T in TMEM (per tile),
-//                                                        B = the W tile again, MN-major.  An
-//                                                        MN-major TF32 operand must use the
-//                                                        128-byte swizzle with 32-byte atoms, so
-//                                                        the tile is fetched a second time by a
-//                                                        tensor map with that swizzle.
-// Thread v of warps 0-3 owns column v: it exponentiates its column of the raw E tile
-// (TMA -> smem), writes the TF32 hi/lo split straight to TMEM, keeps the fp32 values in
-// registers, and after GEMM1 multiplies them with D1[v, :] to emit egrads[:, v] -- a warp
-// writes 32 consecutive columns of one frame, i.e. coalesced 128-byte stores.  D2 stays in
-// TMEM across all tiles and becomes pgrads[:, v-block] at the end.
+//   GEMM1  D1[v, t] = sum_u expP^T[v,u] * W[t,u]    A = expP^T in TMEM (resident for the whole
+//                                                    CTA), B = W tile in smem, K-major
+//   GEMM2  D2[v, u] += sum_t expE^T[v,t] * W[t,u]   A = expE^T in TMEM (per tile), B = the W
+//                                                    tile again, MN-major.  An MN-major TF32
+//                                                    operand must use the 128-byte swizzle with
+//                                                    32-byte atoms, so the tile is fetched a
+//                                                    second time by a tensor map with that swizzle.
+//
+// All global<->shared traffic is TMA.  Two rings of shared-memory stages:
+//   E ring  raw E tile + the tile's row shifts.  Column-owner thread v turns its column of the
+//           tile into exp(E - ref) IN PLACE (and stores the TF32 split to TMEM), later into the
+//           finished gradient, again in place; a storer thread then writes the tile to egrads
+//           with TMA stores (same tensor-map geometry as E) and releases the stage.
+//   W ring  the two copies of the W tile + the tile's sparse-term rows (blank-arc sums,
+//           label-arc occupancies of the labels that fall into this column block).
+// Roles (13 warps): 8 column-owner warps (TMEM lane quarter x frame half), E loader, W loader,
+// storer, and one MMA-issuing warp per GEMM (different accumulators, so their barrier waits and
+// commits overlap each other's MMAs).  D2 stays in TMEM across all tiles and becomes
+// pgrads[:, v-block] at the end.
 //
 // Operand precision (`passes`): the lattice weights W are always rounded once to TF32
 // (round-to-nearest, 2^-12 relative, unbiased).  passes = 1: exp(E) and exp(P) likewise.
@@ -46,16 +52,18 @@ using namespace sm100;
 
 constexpr int kVBlock = 128;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
+constexpr int kOwnerWarps = 8;
+constexpr int kWarpELoad = 8, kWarpWLoad = 9, kWarpStore = 10, kWarpMma1 = 11, kWarpMma2 = 12;
+constexpr int kGradThreads = 13 * 32;
+constexpr int kMaxRing = 4;
 
 struct GradParams {
-  const float* E;
   const float* P;
-  const float* rowRef;   // [B,maxT]
   const float* maxP;     // [B,maxU]
-  const float* eBlank;   // [B,maxT]
   const float* pBlank;   // [B,maxU]
   const float* pLabel;   // [B,maxU]
-  const float* em;       // [B,maxT,maxU] label-arc occupancies
+  const float* emT;      // [B,maxU,ldT] label-arc occupancies, frames contiguous
   const int* labels;
   const int* inLens;
   const int* labLens;
@@ -64,27 +72,29 @@ struct GradParams {
   float* pgrads;
   int* status;
   int maxT, maxU, V, blank;
+  int ldT;      // maxT rounded up to 4: row length of nref / eBlank / emT
   int ldW;      // columns of W (multiple of 32, <= 128) = GEMM2 N
   int Ku;       // maxU rounded up to 8 = GEMM1 K
-  int stages;
+  int stagesE, stagesW;
   int tmemCols;
 };
+
+struct GradMaps {
+  CUtensorMap E, G, Wk, Wmn, nref, ebl, emT;
+};
+
+__host__ __device__ constexpr int row_stride_bytes(int tb) { return (tb * 4 + 127) & ~127; }
 
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
   hi = __float_as_uint(x) & 0xffffe000u;
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
-constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
-constexpr int kOwnerWarps = 8;
-constexpr int kGradThreads = (kOwnerWarps + 3) * 32;  // + producer + two MMA issuers
-
 // ESPLIT / PSPLIT: split exp(E) / exp(P) into TF32 hi + lo (two MMAs per k-step) instead
 // of rounding once.
 template <int TB, bool ESPLIT, bool PSPLIT>
 __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
-    const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmWk,
-    const __grid_constant__ CUtensorMap tmWmn, const GradParams p) {
+    const __grid_constant__ GradMaps tm, const GradParams p) {
   constexpr int TBH = TB / 2;  // frames per owner half
   static_assert(TBH % 8 == 0, "tile halves move through TMEM in 8-column pieces");
   const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
@@ -106,33 +116,40 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
                                              ~uintptr_t(1023));
-  const int S = p.stages;
+  const int SE = p.stagesE, SW = p.stagesW;
   const int nUB = p.ldW / 32;
-  constexpr int kEBoxBytes = TB * 128;  // one 32-column box of the E tile
-  constexpr int kEBytes = 4 * kEBoxBytes;
-  const int wBoxBytes = TB * 128;
-  const int wBytes = nUB * wBoxBytes;
-  const int stageBytes = kEBytes + 2 * wBytes;  // E tile, W tile (K-major), W tile (MN-major)
+  constexpr int kBoxBytes = TB * 128;          // one 32-column box of a tile
+  constexpr int kEBytes = 4 * kBoxBytes;       // E tile
+  constexpr int kRowBytes = TB * 4;            // one row of per-frame scalars
+  constexpr int kRowStride = row_stride_bytes(TB);  // TMA destinations are 128-byte aligned
+  constexpr int kEStage = kEBytes + 1024;      // + row shifts (padded to keep 1024-byte alignment)
+  const int wBytes = nUB * kBoxBytes;
+  const int wScalarBytes = (1 + kMaxStagedLabels) * kRowStride;
+  const int wStage = (2 * wBytes + wScalarBytes + 1023) & ~1023;
+  uint8_t* smemW = smem + (size_t)SE * kEStage;
 
-  __shared__ uint64_t barFull[3], barFree[3], barPReady, barEReady, barE2Free, barD1Full, barD1Free,
-      barD2Done;
+  __shared__ uint64_t barEFull[kMaxRing], barEFree[kMaxRing], barStore[kMaxRing];
+  __shared__ uint64_t barWFull[kMaxRing], barWFree[kMaxRing];
+  __shared__ uint64_t barPReady, barEReady, barE2Free, barD1Full, barD1Free, barD2Done;
   __shared__ uint32_t tmemBase;
   __shared__ int abortFlag;
   __shared__ int sWarpCnt[4];
   __shared__ short sListU[128], sListV[128];
   __shared__ int sLab[128];
   __shared__ float sPb[128], sPl[128];
-  __shared__ float sNref[3][TB];  // per stage: -rowRef[t] * log2(e) for the tile's frames
-  __shared__ float sEbl[3][TB];   // per stage: blank-arc sums of the tile's frames
-  __shared__ float sEm[3][kMaxStagedLabels][TB];  // per stage: label-arc occupancies
 
   const int nTiles = (T + TB - 1) / TB;
   const bool blankHere = p.blank >= v0 && p.blank < v0 + kVBlock;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&barFull[s], 2);  // the copies (transaction bytes) + the staged scalars
-      mbar_init(&barFree[s], kOwnerWarps + 2);  // owner warps + both MMA issuers done with it
+    for (int s = 0; s < SE; ++s) {
+      mbar_init(&barEFull[s], 1);
+      mbar_init(&barEFree[s], 1);             // the storer, once its TMA stores have read the stage
+      mbar_init(&barStore[s], kOwnerWarps);   // gradient tile complete in shared memory
+    }
+    for (int s = 0; s < SW; ++s) {
+      mbar_init(&barWFull[s], 1);
+      mbar_init(&barWFree[s], kOwnerWarps + 2);  // owner warps + both MMA issuers done with it
     }
     mbar_init(&barPReady, kOwnerWarps);
     mbar_init(&barEReady, kOwnerWarps);
@@ -159,7 +176,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     const unsigned m = __ballot_sync(0xffffffffu, inBlock);
     if (lane == 0) sWarpCnt[warp] = __popc(m);
   }
-  if (warp == kOwnerWarps + 1) {
+  if (warp == kWarpMma1) {
     tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
     tmem_relinquish();
   }
@@ -186,66 +203,92 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   const uint32_t cD2 = cD1 + TB;
   volatile int* abortp = &abortFlag;
 
-  if (warp == kOwnerWarps) {
-    // ---------------- producer ----------------
-    // All lanes stage the tile's per-frame scalars (row shifts, blank-arc sums, label-arc
-    // occupancies of this block's labels) in shared memory; lane 0 then arms the barrier
-    // and issues the tile copies.  This runs up to S tiles ahead of the owners, so the
-    // scattered global reads are off their critical path.
+  if (warp == kWarpELoad) {
+    // ---------------- E loader: raw E tile + row shifts of tile i into E stage i % SE ----------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmE);
-      tma_prefetch_desc(&tmWk);
-      tma_prefetch_desc(&tmWmn);
-    }
-    const float* refg = p.rowRef + (i64)b * p.maxT;
-    const float* eblg = p.eBlank + (i64)b * p.maxT;
-    const float* emg = p.em + (i64)b * p.maxT * p.maxU;
-    int issued = 0;
-    bool ok = true;
-    for (int i = 0; i < nTiles && ok; ++i) {
-      const int s = i % S;
-      if (i >= S) {
-        ok = mbar_wait(&barFree[s], ((i / S) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      const int t0 = i * TB;
-      if (lane == 0) {  // copies first: their latency overlaps the scalar staging below
-        uint8_t* st = smem + (size_t)s * stageBytes;
-        mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
+      tma_prefetch_desc(&tm.E);
+      tma_prefetch_desc(&tm.nref);
+      int issued = 0;
+      for (int i = 0; i < nTiles; ++i) {
+        const int s = i % SE;
+        if (i >= SE && !mbar_wait(&barEFree[s], ((i / SE) - 1) & 1, abortp, p.status,
+                                  kStatusTimeoutStageFree))
+          break;
+        uint8_t* st = smem + (size_t)s * kEStage;
+        const int t0 = i * TB;
+        mbar_arrive_expect_tx(&barEFull[s], (uint32_t)(kEBytes + kRowBytes));
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          tma_load_3d(st + j * kEBoxBytes, &tmE, &barFull[s], v0 + 32 * j, t0, b);
+          tma_load_3d(st + j * kBoxBytes, &tm.E, &barEFull[s], v0 + 32 * j, t0, b);
+        tma_load_3d(st + kEBytes, &tm.nref, &barEFull[s], t0, b, 0);
+        issued = i + 1;
+      }
+      if (*abortp) {  // give copies still in flight a bounded time to land
+        for (int i = max(0, issued - SE); i < issued; ++i) {
+          const unsigned long long t1 = global_timer_ns();
+          while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
+                 global_timer_ns() - t1 < 50000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == kWarpWLoad) {
+    // ---------------- W loader: both W tile copies + sparse-term rows into W stage i % SW ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm.Wk);
+      tma_prefetch_desc(&tm.Wmn);
+      tma_prefetch_desc(&tm.emT);
+      const uint32_t bytes =
+          (uint32_t)(2 * wBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
+      int issued = 0;
+      for (int i = 0; i < nTiles; ++i) {
+        const int s = i % SW;
+        if (i >= SW && !mbar_wait(&barWFree[s], ((i / SW) - 1) & 1, abortp, p.status,
+                                  kStatusTimeoutStageFree))
+          break;
+        uint8_t* st = smemW + (size_t)s * wStage;
+        const int t0 = i * TB;
+        mbar_arrive_expect_tx(&barWFull[s], bytes);
         for (int j = 0; j < nUB; ++j) {
-          tma_load_3d(st + kEBytes + j * wBoxBytes, &tmWk, &barFull[s], 32 * j, t0, b);
-          tma_load_3d(st + kEBytes + wBytes + j * wBoxBytes, &tmWmn, &barFull[s], 32 * j, t0, b);
+          tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
+          tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
         }
-      }
-      for (int t = lane; t < TB; t += 32) {
-        const bool live = t0 + t < T;
-        sNref[s][t] = live ? -refg[t0 + t] * kLog2e : 0.0f;
-        if (blankHere) sEbl[s][t] = live ? eblg[t0 + t] : 0.0f;
+        uint8_t* rows = st + 2 * wBytes;
+        if (blankHere) tma_load_3d(rows, &tm.ebl, &barWFull[s], t0, b, 0);
         for (int k = 0; k < nStaged; ++k)
-          sEm[s][k][t] = live ? emg[(i64)(t0 + t) * p.maxU + sListU[k]] : 0.0f;
+          tma_load_3d(rows + (1 + k) * kRowStride, &tm.emT, &barWFull[s], t0, sListU[k], b);
+        issued = i + 1;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&barFull[s]);
-      issued = i + 1;
-    }
-    if (lane == 0 && *abortp) {
-      // after an abort: give the copies still in flight a bounded time to land
-      for (int i = max(0, issued - S); i < issued; ++i) {
-        const unsigned long long t1 = global_timer_ns();
-        while (!mbar_try_wait(&barFull[i % S], (i / S) & 1) &&
-               global_timer_ns() - t1 < 50000000ull) {
+      if (*abortp) {
+        for (int i = max(0, issued - SW); i < issued; ++i) {
+          const unsigned long long t1 = global_timer_ns();
+          while (!mbar_try_wait(&barWFull[i % SW], (i / SW) & 1) &&
+                 global_timer_ns() - t1 < 50000000ull) {
+          }
         }
       }
     }
-  } else if (warp == kOwnerWarps + 1) {
+  } else if (warp == kWarpStore) {
+    // ---------------- storer: finished gradient tile (in the E stage) -> egrads ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm.G);
+      for (int i = 0; i < nTiles; ++i) {
+        const int s = i % SE;
+        if (!mbar_wait(&barStore[s], (i / SE) & 1, abortp, p.status, kStatusTimeoutOperand)) break;
+        const uint8_t* st = smem + (size_t)s * kEStage;
+        const int t0 = i * TB;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v0 + 32 * j < p.V) tma_store_3d(&tm.G, st + j * kBoxBytes, v0 + 32 * j, t0, b);
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(&barEFree[s]);
+      }
+      // the stores themselves complete before the kernel ends (bulk groups are flushed at exit)
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  } else if (warp == kWarpMma1) {
     // ---------------- MMA issuer 1: GEMM1, D1[v, t] = expP^T . W^T per tile ----------------
-    // (GEMM1 and GEMM2 write different accumulators and read different A operands, so each
-    // has its own issuing thread: the barrier waits and commits of one overlap the MMAs of
-    // the other.)
     if (lane == 0) {
       const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);  // B = W tile, K-major (K = u)
       const int kSteps1 = p.Ku / 8;
@@ -254,43 +297,43 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       // phase with that arrival.)
       bool ok = mbar_wait(&barPReady, 0, abortp, p.status, kStatusTimeoutOperand);
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int s = i % S;
-        ok = mbar_wait(&barFull[s], (i / S) & 1, abortp, p.status, kStatusTimeoutTma);
+        const int s = i % SW;
+        ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
         if (ok && i > 0)
           ok = mbar_wait(&barD1Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t wK = smem_u32(smem + (size_t)s * stageBytes + kEBytes);
+        const uint32_t wK = smem_u32(smemW + (size_t)s * wStage);
         for (int ks = 0; ks < kSteps1; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * wBoxBytes + (ks & 3) * 32);
+          const uint32_t off = (uint32_t)((ks >> 2) * kBoxBytes + (ks & 3) * 32);
           const uint64_t bW = smem_desc_sw128(wK + off, 16, 1024);
           mma_tf32_ts(tBase + cD1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
           if (PSPLIT) mma_tf32_ts(tBase + cD1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
         }
         mma_commit(&barD1Full);
-        mma_commit(&barFree[s]);
+        mma_commit(&barWFree[s]);
       }
     }
-  } else if (warp == kOwnerWarps + 2) {
+  } else if (warp == kWarpMma2) {
     // ---------------- MMA issuer 2: GEMM2, D2[v, u] += expE^T . W over all tiles ----------------
     if (lane == 0) {
       const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);  // B = W tile, MN-major (K = t)
       bool ok = true;
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int s = i % S;
-        ok = mbar_wait(&barFull[s], (i / S) & 1, abortp, p.status, kStatusTimeoutTma) &&
+        const int s = i % SW;
+        ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma) &&
              mbar_wait(&barEReady, i & 1, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t wMn = smem_u32(smem + (size_t)s * stageBytes + kEBytes) + (uint32_t)wBytes;
+        const uint32_t wMn = smem_u32(smemW + (size_t)s * wStage) + (uint32_t)wBytes;
         for (int ks = 0; ks < TB / 8; ++ks) {
           // 8 frames = two 4-row atoms 512 bytes apart; 32-column atoms one box apart
-          const uint64_t bW = smem_desc_sw128_base32(wMn + ks * 1024, (uint32_t)wBoxBytes, 512);
+          const uint64_t bW = smem_desc_sw128_base32(wMn + ks * 1024, (uint32_t)kBoxBytes, 512);
           mma_tf32_ts(tBase + cD2, tBase + cEhi + ks * 8, bW, idesc2, (i | ks) ? 1u : 0u);
           if (ESPLIT) mma_tf32_ts(tBase + cD2, tBase + cElo + ks * 8, bW, idesc2, 1u);
         }
         mma_commit(&barE2Free);
-        mma_commit(&barFree[s]);
+        mma_commit(&barWFree[s]);
       }
       if (ok) mma_commit(&barD2Done);
     }
@@ -329,48 +372,35 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       if (lane == 0) mbar_arrive(&barPReady);
     }
 
-    const float* emb = p.em + (i64)b * p.maxT * p.maxU;
+    const float* embT = p.emT + (i64)b * p.maxU * p.ldT;
 
     for (int i = 0; i < nTiles && ok; ++i) {
-      const int s = i % S, t0 = i * TB;
-      ok = mbar_wait(&barFull[s], (i / S) & 1, abortp, p.status, kStatusTimeoutTma);
+      const int se = i % SE, sw = i % SW, t0 = i * TB;
+      // live frames in my half (may be <= 0); none for a column beyond the vocabulary
+      const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
+
+      // ---- phase A: raw E -> exp(E - ref), in place, and into TMEM as GEMM2's A operand ----
+      ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma);
+      if (ok && i > 0)  // expE^T of the previous tile must have been consumed by GEMM2
+        ok = mbar_wait(&barE2Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutMma);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // my column of the raw tile: box q, 4-byte element `lane` of each 128-byte row
-      const uint8_t* col = smem + (size_t)s * stageBytes + q * kEBoxBytes + (lane & 3) * 4;
-      const float* nr = sNref[s] + h * TBH;
-      const int tValid = min(TB, T - t0) - h * TBH;  // live frames in my half (may be <= 0)
-      float x[TBH];
-      if (tValid >= TBH) {
-#pragma unroll
-        for (int j = 0; j < TBH; ++j) {
-          const int t = h * TBH + j;
-          const float raw =
-              *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-          x[j] = ex2_approx(fmaf(raw, kLog2e, nr[j]));
-        }
-      } else {  // frames at or beyond T_b contribute nothing
-#pragma unroll
-        for (int j = 0; j < TBH; ++j) {
-          const int t = h * TBH + j;
-          const float raw =
-              *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-          x[j] = (j < tValid) ? ex2_approx(fmaf(raw, kLog2e, nr[j])) : 0.0f;
-        }
-      }
-      // expE^T of the previous tile must have been consumed by GEMM2 before it is replaced
-      if (i > 0) {
-        ok = mbar_wait(&barE2Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutMma);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+      uint8_t* stE = smem + (size_t)se * kEStage;
+      // my column: box q, 4-byte element `lane` of each (swizzled) 128-byte row
+      uint8_t* col = stE + q * kBoxBytes + (lane & 3) * 4;
+      const float* nr = reinterpret_cast<const float*>(stE + kEBytes) + h * TBH;
 #pragma unroll
       for (int c = 0; c < TBH; c += 8) {
         uint32_t hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          if (ESPLIT) split_tf32(x[c + j], hi[j], lo[j]);
-          else hi[j] = __float_as_uint(tf32_round(x[c + j]));
+          const int t = h * TBH + c + j;
+          float* cell = reinterpret_cast<float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+          float x = ex2_approx(fmaf(*cell, kLog2e, nr[c + j]));
+          if (c + j >= tValid) x = 0.0f;  // frames at or beyond T_b contribute nothing
+          *cell = x;
+          if (ESPLIT) split_tf32(x, hi[j], lo[j]);
+          else hi[j] = __float_as_uint(tf32_round(x));
         }
         tmem_st8(tBase + laneAddr + cEhi + h * TBH + c, hi);
         if (ESPLIT) tmem_st8(tBase + laneAddr + cElo + h * TBH + c, lo);
@@ -380,8 +410,9 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       __syncwarp();
       if (lane == 0) mbar_arrive(&barEReady);  // phase i
 
-      // egrads[t0.., v] = delta * (expE * D1 - sparse)
-      ok = mbar_wait(&barD1Full, i & 1, abortp, p.status, kStatusTimeoutMma);
+      // ---- phase B: egrads tile = delta * (expE * D1 - sparse), in place ----
+      ok = mbar_wait(&barD1Full, i & 1, abortp, p.status, kStatusTimeoutMma) &&
+           mbar_wait(&barWFull[sw], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -397,40 +428,43 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&barD1Free);
+      const float* rows =
+          reinterpret_cast<const float*>(smemW + (size_t)sw * wStage + 2 * wBytes) + h * TBH;
 #pragma unroll
-      for (int j = 0; j < TBH; ++j) d1[j] *= x[j];
+      for (int j = 0; j < TBH; ++j) {
+        const int t = h * TBH + j;
+        d1[j] *= *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+      }
       if (v == p.blank) {
-        const float* eb = sEbl[s] + h * TBH;
 #pragma unroll
-        for (int j = 0; j < TBH; ++j) d1[j] -= eb[j];
+        for (int j = 0; j < TBH; ++j) d1[j] -= rows[j];
       }
       for (int k = 0; k < nStaged; ++k) {
         if (sListV[k] == vl) {
-          const float* m = sEm[s][k] + h * TBH;
+          const float* m = rows + (1 + k) * (kRowStride / 4);
 #pragma unroll
           for (int j = 0; j < TBH; ++j) d1[j] -= m[j];
         }
       }
       for (int k = nStaged; k < nList; ++k) {  // more labels in this block than are staged
         if (sListV[k] == vl) {
-          const int u = sListU[k];
+          const float* m = embT + (i64)sListU[k] * p.ldT + t0 + h * TBH;
 #pragma unroll
           for (int j = 0; j < TBH; ++j)
-            if (j < tValid) d1[j] -= emb[(i64)(t0 + h * TBH + j) * p.maxU + u];
+            if (j < tValid) d1[j] -= m[j];
         }
       }
+#pragma unroll
+      for (int j = 0; j < TBH; ++j) {
+        const int t = h * TBH + j;
+        *reinterpret_cast<float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4)) =
+            (j < tValid) ? delta * d1[j] : 0.0f;
+      }
+      fence_proxy_async_smem();  // the tile is read next by TMA stores
       __syncwarp();
-      if (lane == 0) mbar_arrive(&barFree[s]);  // stage s (tile + staged scalars) released
-      if (vOk) {
-        float* dst = eg + (i64)(t0 + h * TBH) * p.V + v;
-        if (tValid >= TBH) {
-#pragma unroll
-          for (int j = 0; j < TBH; ++j) dst[(i64)j * p.V] = delta * d1[j];
-        } else {
-#pragma unroll
-          for (int j = 0; j < TBH; ++j)
-            if (t0 + h * TBH + j < p.maxT) dst[(i64)j * p.V] = (j < tValid) ? delta * d1[j] : 0.0f;
-        }
+      if (lane == 0) {
+        mbar_arrive(&barWFree[sw]);   // sparse-term rows no longer needed
+        mbar_arrive(&barStore[se]);   // my part of the gradient tile is in place
       }
     }
 
@@ -473,7 +507,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == kOwnerWarps + 1) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
+  if (warp == kWarpMma1) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
 }
 
 int pow2_cols(int x) {
@@ -482,12 +516,18 @@ int pow2_cols(int x) {
   return c;
 }
 
-// W (skewed) -> W row-major [B,maxT,ldW] rounded to TF32 (round-to-nearest; the tensor
-// core would otherwise truncate), zero outside the valid lattice; em row-major.
+// Re-layout after the reverse sweep, one CTA per 32x32 lattice tile:
+//   Ws (skewed)  -> W [B,maxT,ldW] rounded to TF32 (round-to-nearest; the tensor core would
+//                   otherwise truncate), zero outside the valid lattice;
+//   EMs (skewed) -> emT [B,maxU,ldT]: label-arc occupancies with the frames contiguous, so a
+//                   tile's slice for one label is one TMA row; zero outside the lattice;
+//   rowRef, eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT] (row length a multiple of
+//                   4 floats as TMA requires).
 __global__ void __launch_bounds__(256) unskew_round_kernel(
-    const float* __restrict__ Ws, const float* __restrict__ EMs, float* __restrict__ W,
-    float* __restrict__ em, const int* __restrict__ inLens, const int* __restrict__ labLens,
-    int maxT, int maxU, int ld, i64 latStride, int ldW) {
+    const float* __restrict__ Ws, const float* __restrict__ EMs, const float* __restrict__ rowRef,
+    const float* __restrict__ eBlank, float* __restrict__ W, float* __restrict__ emT,
+    float* __restrict__ nref, float* __restrict__ ebl, const int* __restrict__ inLens,
+    const int* __restrict__ labLens, int maxT, int maxU, int ld, i64 latStride, int ldW, int ldT) {
   __shared__ float tW[32][33], tE[32][33];
   const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
@@ -509,99 +549,122 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
       }
     }
   }
+  if (blockIdx.x == 0 && threadIdx.x < 32) {
+    const int t = t0 + lane;
+    if (t < ldT) {
+      const bool ok = t < T;
+      nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
+      ebl[(i64)b * ldT + t] = ok ? eBlank[(i64)b * maxT + t] : 0.0f;
+    }
+  }
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int tt = w * 4 + k, t = t0 + tt;
-    if (t >= maxT) continue;
-    if (u < ldW) W[((i64)b * maxT + t) * ldW + u] = live ? tf32_round(tW[tt][lane]) : 0.0f;
-    if (u < maxU) em[((i64)b * maxT + t) * maxU + u] = live ? tE[tt][lane] : 0.0f;
+    if (t < maxT && u < ldW) W[((i64)b * maxT + t) * ldW + u] = live ? tf32_round(tW[tt][lane]) : 0.0f;
+    // transposed: lane <-> frame, row <-> label position
+    const int uu = u0 + tt, t2 = t0 + lane;
+    if (uu < maxU && t2 < ldT) emT[((i64)b * maxU + uu) * ldT + t2] = live ? tE[lane][tt] : 0.0f;
   }
 }
 
+struct TileCfg {
+  int TB, SE, SW;
+};
+
+// Tile height and ring depths.  TMEM: (1|2)*Ku (expP^T) + (1|2)*TB (expE^T) + TB (D1) + ldW
+// (D2) <= 512 columns.  Shared memory: SE E stages + SW W stages within the 227 KB of a CTA.
+// Prefer the tallest tile that still leaves three E stages (copies issued two tiles ahead).
+TileCfg pick_tile(int Ku, int ldW, int passes, int staticSmem) {
+  const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
+  const int room = 227 * 1024 - staticSmem - 2048;
+  TileCfg best{0, 0, 0};
+  for (int TB : {64, 48, 32}) {
+    if (fp * Ku + (fe + 1) * TB + ldW > 512) continue;
+    const int eStage = 4 * TB * 128 + 1024;
+    const int wStage = (2 * (ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
+    const int SW = 2;
+    const int SE = std::min(kMaxRing, (room - SW * wStage) / eStage);
+    if (SE < 2) continue;
+    if (best.TB == 0 || (best.SE < 3 && SE >= 3)) best = TileCfg{TB, SE, SW};
+    if (best.SE >= 3) break;
+  }
+  return best;
+}
+
 template <int TB, bool ESPLIT, bool PSPLIT>
-void launch_variant(const CUtensorMap& tmE, const CUtensorMap& tmWk, const CUtensorMap& tmWmn,
-                    GradParams p, Dims d, cudaStream_t stream) {
-  const int nUB = p.ldW / 32;
-  const int stageBytes = 4 * TB * 128 + 2 * nUB * TB * 128;
-  cudaFuncAttributes fa;
-  TB200_CUDA_CHECK(cudaFuncGetAttributes(&fa, grads_umma_kernel<TB, ESPLIT, PSPLIT>));
-  const int room = 227 * 1024 - (int)fa.sharedSizeBytes - 2048;
-  int stages = std::min(3, room / stageBytes);
-  if (stages < 1) throw std::invalid_argument("gradient tile does not fit shared memory");
-  p.stages = stages;
+void launch_variant(const GradMaps& tm, GradParams p, TileCfg cfg, Dims d, cudaStream_t stream) {
+  const int eStage = 4 * TB * 128 + 1024;
+  const int wStage = (2 * (p.ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
+  p.stagesE = cfg.SE;
+  p.stagesW = cfg.SW;
   const int cols = (PSPLIT ? 2 : 1) * p.Ku + (ESPLIT ? 2 : 1) * TB + TB + p.ldW;
-  if (cols > 512) throw std::invalid_argument("gradient tile does not fit tensor memory");
   p.tmemCols = pow2_cols(cols);
-  size_t smem = (size_t)stages * stageBytes + 1024;
+  size_t smem = (size_t)cfg.SE * eStage + (size_t)cfg.SW * wStage + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it may hold all 512 TMEM columns
   TB200_CUDA_CHECK(cudaFuncSetAttribute(grads_umma_kernel<TB, ESPLIT, PSPLIT>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(div_up(d.V, kVBlock), d.B);
   ScopedKernel sk("grads_umma", stream);
-  grads_umma_kernel<TB, ESPLIT, PSPLIT><<<grid, kGradThreads, smem, stream>>>(tmE, tmWk, tmWmn, p);
+  grads_umma_kernel<TB, ESPLIT, PSPLIT><<<grid, kGradThreads, smem, stream>>>(tm, p);
 }
 
-// Largest frame tile whose operands and accumulators fit the 512 TMEM columns:
-// (1|2)*Ku (expP^T) + (1|2)*TB (expE^T) + TB (D1) + ldW (D2).
-int pick_tile(int Ku, int ldW, int passes) {
-  const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
-  const int room = (512 - fp * Ku - ldW) / (fe + 1);
-  if (room >= 64) return 64;
-  if (room >= 48) return 48;
-  if (room >= 32) return 32;
-  return 0;
-}
+constexpr int kStaticSmemBound = 3 * 1024;  // barriers + per-position tables of the kernel
 
 }  // namespace
 
 int grads_umma_ld_w(Dims d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
+int grads_umma_ld_t(Dims d) { return (int)round_up64(d.maxT > 0 ? d.maxT : 1, 4); }
 
-bool grads_umma_supported(const float* E, Dims d, int passes) {
+bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes) {
   if (d.V % 4 != 0 || d.V < 32 || d.maxU < 1 || d.maxU > 128 || d.B > 65535) return false;
-  if ((reinterpret_cast<uintptr_t>(E) & 15) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(E) & 15) != 0 || (reinterpret_cast<uintptr_t>(egrads) & 15) != 0)
+    return false;
   const int Ku = (int)round_up64(d.maxU, 8);
-  return pick_tile(Ku, grads_umma_ld_w(d), passes) > 0;
+  return pick_tile(Ku, grads_umma_ld_w(d), passes, kStaticSmemBound).TB > 0;
 }
 
-void launch_unskew_round(const float* Ws, const float* EMs, float* W, float* em,
+void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
+                         const float* eBlank, float* W, float* emT, float* nref, float* ebl,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
-  const int ldW = grads_umma_ld_w(d);
-  dim3 grid(div_up(ldW, 32), div_up(d.maxT, 32), d.B);
+  const int ldW = grads_umma_ld_w(d), ldT = grads_umma_ld_t(d);
+  dim3 grid(div_up(ldW, 32), div_up(ldT, 32), d.B);
   ScopedKernel sk("lattice_unskew_round", stream);
-  unskew_round_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, W, em, inLens, labLens, d.maxT, d.maxU,
-                                                g.ld, g.stride, ldW);
+  unskew_round_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, rowRef, eBlank, W, emT, nref, ebl, inLens,
+                                                labLens, d.maxT, d.maxU, g.ld, g.stride, ldW, ldT);
   TB200_CHECK_LAUNCH();
 }
 
-void launch_grads_umma(const float* E, const float* P, const float* rowRef, const float* maxP,
-                       const float* W, const float* em, const float* eBlank,
-                       const float* pBlank, const float* pLabel, const int* labels,
-                       const float* deltas, float* egrads, float* pgrads, const int* inLens,
-                       const int* labLens, Dims d, int passes, int* status,
-                       cudaStream_t stream) {
+void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
+                       const float* emT, const float* nref, const float* ebl, const float* pBlank,
+                       const float* pLabel, const int* labels, const float* deltas, float* egrads,
+                       float* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
+                       int* status, cudaStream_t stream) {
   if (d.B <= 0 || d.V <= 0) return;
   GradParams p;
-  p.E = E; p.P = P; p.rowRef = rowRef; p.maxP = maxP; p.eBlank = eBlank; p.pBlank = pBlank;
-  p.pLabel = pLabel; p.em = em; p.labels = labels; p.inLens = inLens; p.labLens = labLens;
-  p.deltas = deltas; p.egrads = egrads; p.pgrads = pgrads; p.status = status;
+  p.P = P; p.maxP = maxP; p.pBlank = pBlank; p.pLabel = pLabel; p.emT = emT; p.labels = labels;
+  p.inLens = inLens; p.labLens = labLens; p.deltas = deltas; p.egrads = egrads; p.pgrads = pgrads;
+  p.status = status;
   p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.blank = d.blank;
+  p.ldT = grads_umma_ld_t(d);
   p.ldW = grads_umma_ld_w(d);
   p.Ku = (int)round_up64(d.maxU, 8);
-  p.stages = 0; p.tmemCols = 0;
-  const int TB = pick_tile(p.Ku, p.ldW, passes);
-  if (TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
-  const CUtensorMap tmE = make_tmap_f32_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B,
-                                           (uint64_t)d.V * 4, (uint64_t)d.maxT * d.V * 4, TB);
-  const CUtensorMap tmWk =
-      make_tmap_f32_3d(W, (uint64_t)p.ldW, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)p.ldW * 4,
-                       (uint64_t)d.maxT * p.ldW * 4, TB);
-  const CUtensorMap tmWmn =
-      make_tmap_f32_3d(W, (uint64_t)p.ldW, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)p.ldW * 4,
-                       (uint64_t)d.maxT * p.ldW * 4, TB, /*atom32=*/true);
-#define GO(TBV, EV, PV) launch_variant<TBV, EV, PV>(tmE, tmWk, tmWmn, p, d, stream)
+  p.stagesE = p.stagesW = p.tmemCols = 0;
+  const TileCfg cfg = pick_tile(p.Ku, p.ldW, passes, kStaticSmemBound);
+  if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
+  const int TB = cfg.TB;
+  const uint64_t V = d.V, T = d.maxT, B = d.B, ldW = p.ldW, ldT = p.ldT, U = d.maxU;
+  GradMaps tm;
+  tm.E = make_tmap_f32_3d(E, V, T, B, V * 4, T * V * 4, TB);
+  tm.G = make_tmap_f32_3d(egrads, V, T, B, V * 4, T * V * 4, TB);
+  tm.Wk = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB);
+  tm.Wmn = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB, /*atom32=*/true);
+  tm.nref = make_tmap_f32_rows(nref, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
+  tm.ebl = make_tmap_f32_rows(ebl, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
+  tm.emT = make_tmap_f32_rows(emT, ldT, U, B, ldT * 4, U * ldT * 4, TB);
+#define GO(TBV, EV, PV) launch_variant<TBV, EV, PV>(tm, p, cfg, d, stream)
 #define GO_TB(EV, PV) \
   do { if (TB == 64) GO(64, EV, PV); else if (TB == 48) GO(48, EV, PV); else GO(32, EV, PV); } while (0)
   if (passes == 3) GO_TB(true, true);

@@ -105,20 +105,21 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
 
 // ---- grads_umma.cu --------------------------------------------------------------
 // Tensor-core gradients: one pass over E produces egrads and pgrads.  Usable when
-// grads_umma_supported(); passes = 2 (E-sized operands split hi/lo, W rounded once) or 1.
-int grads_umma_ld_w(Dims d);
-bool grads_umma_supported(const float* E, Dims d, int passes);
-// Ws/EMs (skewed) -> W [B,maxT,ldW] rounded to TF32, zero outside the valid lattice, and
-// em [B,maxT,maxU].
-void launch_unskew_round(const float* Ws, const float* EMs, float* W, float* em,
+// grads_umma_supported(); passes = 1..3 selects the operand precision (see grads_umma.cu).
+int grads_umma_ld_w(Dims d);  // row length of W: maxU rounded up to 32
+int grads_umma_ld_t(Dims d);  // row length of nref / ebl / emT: maxT rounded up to 4
+bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes);
+// After the reverse sweep: Ws/EMs (skewed) -> W [B,maxT,ldW] rounded to TF32 and
+// emT [B,maxU,ldT]; rowRef/eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT].
+void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
+                         const float* eBlank, float* W, float* emT, float* nref, float* ebl,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream);
-void launch_grads_umma(const float* E, const float* P, const float* rowRef, const float* maxP,
-                       const float* W, const float* em, const float* eBlank,
-                       const float* pBlank, const float* pLabel, const int* labels,
-                       const float* deltas, float* egrads, float* pgrads, const int* inLens,
-                       const int* labLens, Dims d, int passes, int* status,
-                       cudaStream_t stream);
+void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
+                       const float* emT, const float* nref, const float* ebl, const float* pBlank,
+                       const float* pLabel, const int* labels, const float* deltas, float* egrads,
+                       float* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
+                       int* status, cudaStream_t stream);
 
 // ---- maxplus.cu --------------------------------------------------------------
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,

@@ -72,6 +72,32 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
   return m;
 }
 
+CUtensorMap make_tmap_f32_rows(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                               uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0) {
+  // same encoder as above; resolved once there
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  TB200_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+  if (q != cudaDriverEntryPointSuccess || !fn)
+    throw CudaError("cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1Bytes, stride2Bytes};
+  const cuuint32_t box[3] = {box0, 1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult rc = reinterpret_cast<EncodeFn>(fn)(
+      &m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    throw CudaError("cuTensorMapEncodeTiled (rows) failed with code " + std::to_string((int)rc));
+  return m;
+}
+
 }  // namespace sm100
 
 namespace {

@@ -105,6 +105,27 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// 3-D tile store shared -> global (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* src, int x, int y,
+                                             int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until the stores committed by this thread have finished READING shared memory.
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the async
+// proxy (TMA stores, MMA operand fetches).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---- tensor memory ----------------------------------------------------------------
 // Warp-wide.  Writes the base address of `ncols` columns (power of two >= 32) to *dst.
 __device__ __forceinline__ void tmem_alloc(uint32_t* dstSmem, uint32_t ncols) {
@@ -260,6 +281,10 @@ __device__ __forceinline__ float tf32_round(float x) {
 CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                              uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
                              bool atom32 = false);
+
+// fp32 tensor [d2][d1][d0], box [1][1][box0] without swizzle (rows of scalars).
+CUtensorMap make_tmap_f32_rows(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                               uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0);
 
 }  // namespace sm100
 }  // namespace tb200
