@@ -20,16 +20,22 @@
 //                                                    second time by a tensor map with that swizzle.
 //
 // All global<->shared traffic is TMA.  Two rings of shared-memory stages:
-//   E ring  raw E tile + the tile's row shifts.  Column-owner thread v turns its column of the
-//           tile into exp(E - ref) IN PLACE (and stores the TF32 split to TMEM), later into the
-//           finished gradient, again in place; a storer thread then writes the tile to egrads
-//           with TMA stores (same tensor-map geometry as E) and releases the stage.
+//   E ring  raw E tile + the tile's row shifts.  The owner of column v in the exp group turns
+//           its column of the tile into exp(E - ref), split hi + lo for TF32, in TMEM; the owner
+//           in the gradient group reads it back from TMEM together with D1 and writes the
+//           finished gradient over the dead raw tile; a storer thread then writes the tile to
+//           egrads with TMA stores (same tensor-map geometry as E) and releases the stage.
+//           (Shared-memory bandwidth is the scarce resource of this kernel: per tile the TMA
+//           writes, the MMA operand reads and one read + one write by the owners already use
+//           most of it, so the exponentials are not written back to shared memory.)
 //   W ring  the two copies of the W tile + the tile's sparse-term rows (blank-arc sums,
 //           label-arc occupancies of the labels that fall into this column block).
-// Roles (13 warps): 8 column-owner warps (TMEM lane quarter x frame half), E loader, W loader,
-// storer, and one MMA-issuing warp per GEMM (different accumulators, so their barrier waits and
-// commits overlap each other's MMAs).  D2 stays in TMEM across all tiles and becomes
-// pgrads[:, v-block] at the end.
+// Roles (21 warps): 8 column-owner warps of the exp group (TMEM lane quarter x frame half;
+// raw E -> exp(E - ref) in TMEM -- two copies there when the columns allow, so the next tile's
+// exponentials do not wait for GEMM2), 8 column-owner warps of the gradient group (D1 x
+// exponentials from TMEM - sparse terms -> the gradient, into the E stage), E loader, W loader, storer, and one MMA-issuing warp per GEMM (different
+// accumulators, so their barrier waits and commits overlap each other's MMAs).  D2 stays in
+// TMEM across all tiles and becomes pgrads[:, v-block] at the end.
 //
 // Operand precision (`passes`): the lattice weights W are always rounded once to TF32
 // (round-to-nearest, 2^-12 relative, unbiased).  passes = 1: exp(E) and exp(P) likewise.
@@ -53,9 +59,9 @@ using namespace sm100;
 constexpr int kVBlock = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
-constexpr int kOwnerWarps = 8;
-constexpr int kWarpELoad = 8, kWarpWLoad = 9, kWarpStore = 10, kWarpMma1 = 11, kWarpMma2 = 12;
-constexpr int kGradThreads = 13 * 32;
+constexpr int kGroupWarps = 8;  // column-owner warps per group (exp group, gradient group)
+constexpr int kWarpELoad = 16, kWarpWLoad = 17, kWarpStore = 18, kWarpMma1 = 19, kWarpMma2 = 20;
+constexpr int kGradThreads = 21 * 32;
 constexpr int kMaxRing = 4;
 
 struct GradParams {
@@ -76,6 +82,7 @@ struct GradParams {
   int ldW;      // columns of W (multiple of 32, <= 128) = GEMM2 N
   int Ku;       // maxU rounded up to 8 = GEMM1 K
   int stagesE, stagesW;
+  int eBufs;    // copies of the expE^T operand in tensor memory (2 if the columns allow)
   int tmemCols;
 };
 
@@ -128,9 +135,10 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   const int wStage = (2 * wBytes + wScalarBytes + 1023) & ~1023;
   uint8_t* smemW = smem + (size_t)SE * kEStage;
 
-  __shared__ uint64_t barEFull[kMaxRing], barEFree[kMaxRing], barStore[kMaxRing];
+  __shared__ uint64_t barEFull[kMaxRing], barStore[kMaxRing], barEFree[kMaxRing];
   __shared__ uint64_t barWFull[kMaxRing], barWFree[kMaxRing];
-  __shared__ uint64_t barPReady, barEReady, barE2Free, barD1Full, barD1Free, barD2Done;
+  __shared__ uint64_t barEReady[2], barE2Free[2];
+  __shared__ uint64_t barPReady, barD1Full, barD1Free, barD2Done;
   __shared__ uint32_t tmemBase;
   __shared__ int abortFlag;
   __shared__ int sWarpCnt[4];
@@ -144,18 +152,20 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   if (threadIdx.x == 0) {
     for (int s = 0; s < SE; ++s) {
       mbar_init(&barEFull[s], 1);
+      mbar_init(&barStore[s], kGroupWarps);   // gradient tile complete in shared memory
       mbar_init(&barEFree[s], 1);             // the storer, once its TMA stores have read the stage
-      mbar_init(&barStore[s], kOwnerWarps);   // gradient tile complete in shared memory
     }
     for (int s = 0; s < SW; ++s) {
       mbar_init(&barWFull[s], 1);
-      mbar_init(&barWFree[s], kOwnerWarps + 2);  // owner warps + both MMA issuers done with it
+      mbar_init(&barWFree[s], kGroupWarps + 2);  // gradient warps + both MMA issuers done with it
     }
-    mbar_init(&barPReady, kOwnerWarps);
-    mbar_init(&barEReady, kOwnerWarps);
-    mbar_init(&barE2Free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&barEReady[s], kGroupWarps);
+      mbar_init(&barE2Free[s], 1 + kGroupWarps);  // GEMM2 done with it + gradient warps have read it
+    }
+    mbar_init(&barPReady, 2 * kGroupWarps);
     mbar_init(&barD1Full, 1);
-    mbar_init(&barD1Free, kOwnerWarps);
+    mbar_init(&barD1Free, kGroupWarps);
     mbar_init(&barD2Done, 1);
     abortFlag = 0;
     fence_mbar_init();
@@ -198,73 +208,86 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
   const uint32_t tBase = tmemBase;
   const uint32_t cPhi = 0, cPlo = p.Ku;
-  const uint32_t cEhi = (PSPLIT ? 2 : 1) * p.Ku, cElo = cEhi + TB;
-  const uint32_t cD1 = cEhi + (ESPLIT ? 2 : 1) * TB;
+  constexpr uint32_t kECols = (ESPLIT ? 2 : 1) * TB;  // one copy of expE^T (hi, then lo)
+  const int EB = p.eBufs;
+  const uint32_t cE = (PSPLIT ? 2 : 1) * p.Ku;
+  const uint32_t cD1 = cE + EB * kECols;
   const uint32_t cD2 = cD1 + TB;
   volatile int* abortp = &abortFlag;
 
   if (warp == kWarpELoad) {
     // ---------------- E loader: raw E tile + row shifts of tile i into E stage i % SE ----------------
+    // One copy per lane (lanes 0..3 the boxes, lane 4 the shifts): a single thread would issue
+    // them one after the other.
     if (lane == 0) {
       tma_prefetch_desc(&tm.E);
       tma_prefetch_desc(&tm.nref);
-      int issued = 0;
-      for (int i = 0; i < nTiles; ++i) {
-        const int s = i % SE;
-        if (i >= SE && !mbar_wait(&barEFree[s], ((i / SE) - 1) & 1, abortp, p.status,
-                                  kStatusTimeoutStageFree))
-          break;
-        uint8_t* st = smem + (size_t)s * kEStage;
-        const int t0 = i * TB;
-        mbar_arrive_expect_tx(&barEFull[s], (uint32_t)(kEBytes + kRowBytes));
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          tma_load_3d(st + j * kBoxBytes, &tm.E, &barEFull[s], v0 + 32 * j, t0, b);
-        tma_load_3d(st + kEBytes, &tm.nref, &barEFull[s], t0, b, 0);
-        issued = i + 1;
-      }
-      if (*abortp) {  // give copies still in flight a bounded time to land
-        for (int i = max(0, issued - SE); i < issued; ++i) {
-          const unsigned long long t1 = global_timer_ns();
-          while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
-                 global_timer_ns() - t1 < 50000000ull) {
-          }
+    }
+    int issued = 0;
+    for (int i = 0; i < nTiles; ++i) {
+      const int s = i % SE;
+      bool ok = true;
+      if (i >= SE)
+        ok = mbar_wait(&barEFree[s], ((i / SE) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      uint8_t* st = smem + (size_t)s * kEStage;
+      const int t0 = i * TB;
+      if (lane == 0) mbar_arrive_expect_tx(&barEFull[s], (uint32_t)(kEBytes + kRowBytes));
+      __syncwarp();
+      if (lane < 4) tma_load_3d(st + lane * kBoxBytes, &tm.E, &barEFull[s], v0 + 32 * lane, t0, b);
+      else if (lane == 4) tma_load_3d(st + kEBytes, &tm.nref, &barEFull[s], t0, b, 0);
+      issued = i + 1;
+    }
+    if (lane == 0 && *abortp) {  // give copies still in flight a bounded time to land
+      for (int i = max(0, issued - SE); i < issued; ++i) {
+        const unsigned long long t1 = global_timer_ns();
+        while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
+               global_timer_ns() - t1 < 50000000ull) {
         }
       }
     }
   } else if (warp == kWarpWLoad) {
     // ---------------- W loader: both W tile copies + sparse-term rows into W stage i % SW ----------------
+    // Lanes 0..7: the boxes of the two copies; lane 8: blank-arc sums; lanes 9..: one staged
+    // label row each.
     if (lane == 0) {
       tma_prefetch_desc(&tm.Wk);
       tma_prefetch_desc(&tm.Wmn);
       tma_prefetch_desc(&tm.emT);
-      const uint32_t bytes =
-          (uint32_t)(2 * wBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
-      int issued = 0;
-      for (int i = 0; i < nTiles; ++i) {
-        const int s = i % SW;
-        if (i >= SW && !mbar_wait(&barWFree[s], ((i / SW) - 1) & 1, abortp, p.status,
-                                  kStatusTimeoutStageFree))
-          break;
-        uint8_t* st = smemW + (size_t)s * wStage;
-        const int t0 = i * TB;
-        mbar_arrive_expect_tx(&barWFull[s], bytes);
-        for (int j = 0; j < nUB; ++j) {
-          tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
-          tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
+    }
+    const uint32_t bytes =
+        (uint32_t)(2 * wBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
+    const int myU = (lane >= 9 && lane - 9 < nStaged) ? sListU[lane - 9] : -1;
+    int issued = 0;
+    for (int i = 0; i < nTiles; ++i) {
+      const int s = i % SW;
+      bool ok = true;
+      if (i >= SW)
+        ok = mbar_wait(&barWFree[s], ((i / SW) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      uint8_t* st = smemW + (size_t)s * wStage;
+      uint8_t* rows = st + 2 * wBytes;
+      const int t0 = i * TB;
+      if (lane == 0) mbar_arrive_expect_tx(&barWFull[s], bytes);
+      __syncwarp();
+      if (lane < 8) {
+        const int j = lane >> 1;
+        if (j < nUB) {
+          if (lane & 1) tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
+          else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
         }
-        uint8_t* rows = st + 2 * wBytes;
+      } else if (lane == 8) {
         if (blankHere) tma_load_3d(rows, &tm.ebl, &barWFull[s], t0, b, 0);
-        for (int k = 0; k < nStaged; ++k)
-          tma_load_3d(rows + (1 + k) * kRowStride, &tm.emT, &barWFull[s], t0, sListU[k], b);
-        issued = i + 1;
+      } else if (myU >= 0) {
+        tma_load_3d(rows + (1 + lane - 9) * kRowStride, &tm.emT, &barWFull[s], t0, myU, b);
       }
-      if (*abortp) {
-        for (int i = max(0, issued - SW); i < issued; ++i) {
-          const unsigned long long t1 = global_timer_ns();
-          while (!mbar_try_wait(&barWFull[i % SW], (i / SW) & 1) &&
-                 global_timer_ns() - t1 < 50000000ull) {
-          }
+      issued = i + 1;
+    }
+    if (lane == 0 && *abortp) {
+      for (int i = max(0, issued - SW); i < issued; ++i) {
+        const unsigned long long t1 = global_timer_ns();
+        while (!mbar_try_wait(&barWFull[i % SW], (i / SW) & 1) &&
+               global_timer_ns() - t1 < 50000000ull) {
         }
       }
     }
@@ -321,8 +344,10 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       bool ok = true;
       for (int i = 0; i < nTiles && ok; ++i) {
         const int s = i % SW;
+        const int eb = i % EB;
+        const uint32_t cEhi = cE + eb * kECols, cElo = cEhi + TB;
         ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma) &&
-             mbar_wait(&barEReady, i & 1, abortp, p.status, kStatusTimeoutOperand);
+             mbar_wait(&barEReady[eb], (i / EB) & 1, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
         const uint32_t wMn = smem_u32(smemW + (size_t)s * wStage) + (uint32_t)wBytes;
@@ -332,17 +357,20 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
           mma_tf32_ts(tBase + cD2, tBase + cEhi + ks * 8, bW, idesc2, (i | ks) ? 1u : 0u);
           if (ESPLIT) mma_tf32_ts(tBase + cD2, tBase + cElo + ks * 8, bW, idesc2, 1u);
         }
-        mma_commit(&barE2Free);
+        mma_commit(&barE2Free[eb]);
         mma_commit(&barWFree[s]);
       }
       if (ok) mma_commit(&barD2Done);
     }
   } else {
     // ---------------- column owners ----------------
-    // Thread (q, lane) owns vocabulary column v0 + q*32 + lane = TMEM lane q*32 + lane; the
-    // two halves h = 0,1 of the owner warps split the frames of each tile (and the label
-    // positions of the prologue/epilogue) between them.
-    const int q = warp & 3, h = warp >> 2;
+    // Thread (q, lane) owns vocabulary column v0 + q*32 + lane = TMEM lane q*32 + lane.  Two
+    // groups of 8 warps: group 0 turns raw E into exp(E - ref) (shared memory in place + TMEM),
+    // group 1 turns that into the gradient, so tile i+1's exponentials overlap tile i's
+    // gradient arithmetic.  Within a group the halves h = 0,1 split the frames of a tile; all
+    // 16 warps split the label positions of the prologue and the epilogue.
+    const int grp = warp >> 3, q = warp & 3, h = (warp >> 2) & 1;
+    const int part = grp * 2 + h;  // 0..3: share of the prologue / epilogue
     const int vl = q * 32 + lane;
     const int v = v0 + vl;
     const bool vOk = v < p.V;
@@ -353,13 +381,21 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     {
       const float* pp = p.P + (i64)b * p.maxU * p.V;
       const float* mp = p.maxP + (i64)b * p.maxU;
-      for (int u0 = 8 * h; u0 < p.Ku; u0 += 16) {
+      const int vc = min(v, p.V - 1);
+      for (int u0 = 8 * part; u0 < p.Ku; u0 += 32) {
+        // unconditional loads from clamped addresses: all eight are in flight together
+        float raw[8], sh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int uc = min(u0 + j, U - 1);
+          raw[j] = pp[(i64)uc * p.V + vc];
+          sh[j] = mp[uc];
+        }
         uint32_t hi[8], lo[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int u = u0 + j;
-          float x = 0.0f;
-          if (u < U && vOk) x = ex2_approx((pp[(i64)u * p.V + v] - mp[u]) * kLog2e);
+          float x = ex2_approx((raw[j] - sh[j]) * kLog2e);
+          if (u0 + j >= U || !vOk) x = 0.0f;
           if (PSPLIT) split_tf32(x, hi[j], lo[j]);
           else hi[j] = __float_as_uint(tf32_round(x));
         }
@@ -372,112 +408,144 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       if (lane == 0) mbar_arrive(&barPReady);
     }
 
-    const float* embT = p.emT + (i64)b * p.maxU * p.ldT;
+    // my column inside an E stage: box q, 4-byte element `lane` of each (swizzled) 128-byte row
+    const int colOff = q * kBoxBytes + (lane & 3) * 4;
+    const int chunk = lane >> 2;
 
-    for (int i = 0; i < nTiles && ok; ++i) {
-      const int se = i % SE, sw = i % SW, t0 = i * TB;
-      // live frames in my half (may be <= 0); none for a column beyond the vocabulary
-      const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
-
-      // ---- phase A: raw E -> exp(E - ref), in place, and into TMEM as GEMM2's A operand ----
-      ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma);
-      if (ok && i > 0)  // expE^T of the previous tile must have been consumed by GEMM2
-        ok = mbar_wait(&barE2Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutMma);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      uint8_t* stE = smem + (size_t)se * kEStage;
-      // my column: box q, 4-byte element `lane` of each (swizzled) 128-byte row
-      uint8_t* col = stE + q * kBoxBytes + (lane & 3) * 4;
-      const float* nr = reinterpret_cast<const float*>(stE + kEBytes) + h * TBH;
+    if (grp == 0) {
+      // ---- exp group: raw E -> exp(E - ref), in place, and into TMEM as GEMM2's A operand ----
+      for (int i = 0; i < nTiles && ok; ++i) {
+        const int se = i % SE, eb = i % EB, t0 = i * TB;
+        // live frames in my half (may be <= 0); none for a column beyond the vocabulary
+        const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
+        ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma);
+        if (ok && i >= EB)  // this copy of expE^T must have been consumed by GEMM2
+          ok = mbar_wait(&barE2Free[eb], ((i / EB) - 1) & 1, abortp, p.status, kStatusTimeoutMma);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* stE = smem + (size_t)se * kEStage;
+        uint8_t* col = stE + colOff;
+        const float* nr = reinterpret_cast<const float*>(stE + kEBytes) + h * TBH;
+        const uint32_t cEhi = cE + eb * kECols + h * TBH, cElo = cEhi + TB;
+        float xs[TBH];
 #pragma unroll
-      for (int c = 0; c < TBH; c += 8) {
-        uint32_t hi[8], lo[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = h * TBH + c + j;
-          float* cell = reinterpret_cast<float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-          float x = ex2_approx(fmaf(*cell, kLog2e, nr[c + j]));
-          if (c + j >= tValid) x = 0.0f;  // frames at or beyond T_b contribute nothing
-          *cell = x;
-          if (ESPLIT) split_tf32(x, hi[j], lo[j]);
-          else hi[j] = __float_as_uint(tf32_round(x));
+        for (int j = 0; j < TBH; ++j) {
+          const int t = h * TBH + j;
+          xs[j] = fmaf(*reinterpret_cast<const float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)),
+                       kLog2e, nr[j]);
         }
-        tmem_st8(tBase + laneAddr + cEhi + h * TBH + c, hi);
-        if (ESPLIT) tmem_st8(tBase + laneAddr + cElo + h * TBH + c, lo);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&barEReady);  // phase i
-
-      // ---- phase B: egrads tile = delta * (expE * D1 - sparse), in place ----
-      ok = mbar_wait(&barD1Full, i & 1, abortp, p.status, kStatusTimeoutMma) &&
-           mbar_wait(&barWFull[sw], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      float d1[TBH];
 #pragma unroll
-      for (int c = 0; c < TBH; c += 8) {
-        uint32_t r[8];
-        tmem_ld8(tBase + laneAddr + cD1 + h * TBH + c, r);
+        for (int c = 0; c < TBH; c += 8) {
+          uint32_t hi[8], lo[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) d1[c + j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 8; ++j) {
+            float x = ex2_approx(xs[c + j]);
+            if (c + j >= tValid) x = 0.0f;  // frames at or beyond T_b contribute nothing
+            if (ESPLIT) split_tf32(x, hi[j], lo[j]);
+            else hi[j] = __float_as_uint(tf32_round(x));
+          }
+          tmem_st8(tBase + laneAddr + cEhi + c, hi);
+          if (ESPLIT) tmem_st8(tBase + laneAddr + cElo + c, lo);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        // exp(E - ref) of the tile is in TMEM and the raw tile in shared memory is dead
+        if (lane == 0) mbar_arrive(&barEReady[eb]);
       }
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&barD1Free);
-      const float* rows =
-          reinterpret_cast<const float*>(smemW + (size_t)sw * wStage + 2 * wBytes) + h * TBH;
-#pragma unroll
-      for (int j = 0; j < TBH; ++j) {
-        const int t = h * TBH + j;
-        d1[j] *= *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-      }
-      if (v == p.blank) {
-#pragma unroll
-        for (int j = 0; j < TBH; ++j) d1[j] -= rows[j];
-      }
-      for (int k = 0; k < nStaged; ++k) {
+    } else {
+      // ---- gradient group: egrads tile = delta * (expE * D1 - sparse), in place ----
+      const float* embT = p.emT + (i64)b * p.maxU * p.ldT;
+      // which of the block's label positions carry MY column (almost always none)
+      unsigned stagedMine = 0;
+      bool extraMine = false;
+      for (int k = 0; k < nList; ++k) {
         if (sListV[k] == vl) {
-          const float* m = rows + (1 + k) * (kRowStride / 4);
+          if (k < nStaged) stagedMine |= 1u << k;
+          else extraMine = true;
+        }
+      }
+      for (int i = 0; i < nTiles && ok; ++i) {
+        const int se = i % SE, sw = i % SW, t0 = i * TB;
+        const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
+        const int eb = i % EB;
+        ok = mbar_wait(&barD1Full, i & 1, abortp, p.status, kStatusTimeoutMma) &&
+             mbar_wait(&barEReady[eb], (i / EB) & 1, abortp, p.status, kStatusTimeoutOperand);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // expE * D1, both from tensor memory (expE = hi + lo exactly)
+        const uint32_t cEhi = cE + eb * kECols + h * TBH, cElo = cEhi + TB;
+        float d1[TBH];
+#pragma unroll
+        for (int c = 0; c < TBH; c += 8) {
+          uint32_t r[8], xh[8], xl[8];
+          tmem_ld8(tBase + laneAddr + cD1 + h * TBH + c, r);
+          tmem_ld8(tBase + laneAddr + cEhi + c, xh);
+          if (ESPLIT) tmem_ld8(tBase + laneAddr + cElo + c, xl);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float x = __uint_as_float(xh[j]);
+            if (ESPLIT) x += __uint_as_float(xl[j]);
+            d1[c + j] = x * __uint_as_float(r[j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&barD1Free);
+          mbar_arrive(&barE2Free[eb]);
+        }
+        ok = mbar_wait(&barWFull[sw], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        uint8_t* col = smem + (size_t)se * kEStage + colOff;
+        const float* rows =
+            reinterpret_cast<const float*>(smemW + (size_t)sw * wStage + 2 * wBytes) + h * TBH;
+        if (v == p.blank) {
+#pragma unroll
+          for (int j = 0; j < TBH; ++j) d1[j] -= rows[j];
+        }
+        for (unsigned m0 = stagedMine; m0; m0 &= m0 - 1) {
+          const float* m = rows + (1 + (__ffs(m0) - 1)) * (kRowStride / 4);
 #pragma unroll
           for (int j = 0; j < TBH; ++j) d1[j] -= m[j];
         }
-      }
-      for (int k = nStaged; k < nList; ++k) {  // more labels in this block than are staged
-        if (sListV[k] == vl) {
-          const float* m = embT + (i64)sListU[k] * p.ldT + t0 + h * TBH;
+        for (int k = nStaged; extraMine && k < nList; ++k) {  // more labels than are staged
+          if (sListV[k] == vl) {
+            const float* m = embT + (i64)sListU[k] * p.ldT + t0 + h * TBH;
 #pragma unroll
-          for (int j = 0; j < TBH; ++j)
-            if (j < tValid) d1[j] -= m[j];
+            for (int j = 0; j < TBH; ++j)
+              if (j < tValid) d1[j] -= m[j];
+          }
         }
-      }
 #pragma unroll
-      for (int j = 0; j < TBH; ++j) {
-        const int t = h * TBH + j;
-        *reinterpret_cast<float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4)) =
-            (j < tValid) ? delta * d1[j] : 0.0f;
-      }
-      fence_proxy_async_smem();  // the tile is read next by TMA stores
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&barWFree[sw]);   // sparse-term rows no longer needed
-        mbar_arrive(&barStore[se]);   // my part of the gradient tile is in place
+        for (int j = 0; j < TBH; ++j) {
+          const int t = h * TBH + j;
+          *reinterpret_cast<float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)) =
+              (j < tValid) ? delta * d1[j] : 0.0f;
+        }
+        fence_proxy_async_smem();  // the tile is read next by TMA stores
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&barWFree[sw]);   // sparse-term rows no longer needed
+          mbar_arrive(&barStore[se]);   // my part of the gradient tile is in place
+        }
       }
     }
 
     // padded frames beyond the last tile: exact zeros
     if (vOk)
-      for (int t = nTiles * TB + h; t < p.maxT; t += 2) eg[(i64)t * p.V + v] = 0.0f;
+      for (int t = nTiles * TB + part; t < p.maxT; t += 4) eg[(i64)t * p.V + v] = 0.0f;
 
     // pgrads[u, v] = delta * (expP[u,v] * D2[v,u] - sparse)
     if (ok) ok = mbar_wait(&barD2Done, 0, abortp, p.status, kStatusTimeoutMma);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      for (int u0 = 8 * h; u0 < p.Ku; u0 += 16) {
+      for (int u0 = 8 * part; u0 < p.Ku; u0 += 32) {
         uint32_t d2[8], xh[8], xl[8];
         tmem_ld8(tBase + laneAddr + cD2 + u0, d2);
         tmem_ld8(tBase + laneAddr + cPhi + u0, xh);
@@ -569,7 +637,7 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
 }
 
 struct TileCfg {
-  int TB, SE, SW;
+  int TB, SE, SW, EB;
 };
 
 // Tile height and ring depths.  TMEM: (1|2)*Ku (expP^T) + (1|2)*TB (expE^T) + TB (D1) + ldW
@@ -578,15 +646,20 @@ struct TileCfg {
 TileCfg pick_tile(int Ku, int ldW, int passes, int staticSmem) {
   const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
   const int room = 227 * 1024 - staticSmem - 2048;
-  TileCfg best{0, 0, 0};
+  TileCfg best{0, 0, 0, 0};
   for (int TB : {64, 48, 32}) {
-    if (fp * Ku + (fe + 1) * TB + ldW > 512) continue;
+    // two copies of expE^T when the columns allow; a 32-frame tile may fall back to one
+    int EB = 2;
+    if (fp * Ku + (2 * fe + 1) * TB + ldW > 512) {
+      if (TB > 32 || fp * Ku + (fe + 1) * TB + ldW > 512) continue;
+      EB = 1;
+    }
     const int eStage = 4 * TB * 128 + 1024;
     const int wStage = (2 * (ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
     const int SW = 2;
     const int SE = std::min(kMaxRing, (room - SW * wStage) / eStage);
     if (SE < 2) continue;
-    if (best.TB == 0 || (best.SE < 3 && SE >= 3)) best = TileCfg{TB, SE, SW};
+    if (best.TB == 0 || (best.SE < 3 && SE >= 3)) best = TileCfg{TB, SE, SW, EB};
     if (best.SE >= 3) break;
   }
   return best;
@@ -598,7 +671,8 @@ void launch_variant(const GradMaps& tm, GradParams p, TileCfg cfg, Dims d, cudaS
   const int wStage = (2 * (p.ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
   p.stagesE = cfg.SE;
   p.stagesW = cfg.SW;
-  const int cols = (PSPLIT ? 2 : 1) * p.Ku + (ESPLIT ? 2 : 1) * TB + TB + p.ldW;
+  p.eBufs = cfg.EB;
+  const int cols = (PSPLIT ? 2 : 1) * p.Ku + cfg.EB * (ESPLIT ? 2 : 1) * TB + TB + p.ldW;
   p.tmemCols = pow2_cols(cols);
   size_t smem = (size_t)cfg.SE * eStage + (size_t)cfg.SW * wStage + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it may hold all 512 TMEM columns
@@ -651,7 +725,7 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
   p.ldT = grads_umma_ld_t(d);
   p.ldW = grads_umma_ld_w(d);
   p.Ku = (int)round_up64(d.maxU, 8);
-  p.stagesE = p.stagesW = p.tmemCols = 0;
+  p.stagesE = p.stagesW = p.eBufs = p.tmemCols = 0;
   const TileCfg cfg = pick_tile(p.Ku, p.ldW, passes, kStaticSmemBound);
   if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
   const int TB = cfg.TB;
