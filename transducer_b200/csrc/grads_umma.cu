@@ -28,14 +28,17 @@
 //           (Shared-memory bandwidth is the scarce resource of this kernel: per tile the TMA
 //           writes, the MMA operand reads and one read + one write by the owners already use
 //           most of it, so the exponentials are not written back to shared memory.)
-//   W ring  the two copies of the W tile + the tile's sparse-term rows (blank-arc sums,
-//           label-arc occupancies of the labels that fall into this column block).
-// Roles (21 warps): 8 column-owner warps of the exp group (TMEM lane quarter x frame half;
-// raw E -> exp(E - ref) in TMEM -- two copies there when the columns allow, so the next tile's
-// exponentials do not wait for GEMM2), 8 column-owner warps of the gradient group (D1 x
-// exponentials from TMEM - sparse terms -> the gradient, into the E stage), E loader, W loader, storer, and one MMA-issuing warp per GEMM (different
-// accumulators, so their barrier waits and commits overlap each other's MMAs).  D2 stays in
-// TMEM across all tiles and becomes pgrads[:, v-block] at the end.
+//           The stage also carries the tile's sparse-term rows (blank-arc sums, label-arc
+//           occupancies of the labels that fall into this column block).
+//   W ring  the two copies of the W tile; released by the two GEMMs alone.
+// Roles (20 warps): 8 column-owner warps of the exp group (TMEM lane quarter x frame half;
+// raw E -> exp(E - ref) in TMEM), 8 column-owner warps of the gradient group (D1 x exponentials
+// from TMEM - sparse terms -> the gradient, into the E stage), a mover warp (fills E stages,
+// stores finished tiles and refills the stage at once), a W loader warp, and one MMA-issuing
+// warp per GEMM (different accumulators, so their barrier waits and commits overlap each
+// other's MMAs).  expE^T and D1 each have two copies in TMEM when the 512 columns allow, which
+// takes GEMM2 -> next exponentials and gradient reads -> next GEMM1 off the critical path.
+// D2 stays in TMEM across all tiles and becomes pgrads[:, v-block] at the end.
 //
 // Operand precision (`passes`): the lattice weights W are always rounded once to TF32
 // (round-to-nearest, 2^-12 relative, unbiased).  passes = 1: exp(E) and exp(P) likewise.
@@ -60,8 +63,9 @@ constexpr int kVBlock = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kMaxStagedLabels = 16;  // label columns per block whose occupancies are staged
 constexpr int kGroupWarps = 8;  // column-owner warps per group (exp group, gradient group)
-constexpr int kWarpELoad = 16, kWarpWLoad = 17, kWarpStore = 18, kWarpMma1 = 19, kWarpMma2 = 20;
-constexpr int kGradThreads = 21 * 32;
+constexpr int kWarpMove = 16, kWarpWLoad = 17, kWarpMma1 = 18, kWarpMma2 = 19;
+constexpr int kGradThreads = 20 * 32;
+constexpr int kStageRows = 2 + kMaxStagedLabels;  // row shifts, blank-arc sums, staged label rows
 constexpr int kMaxRing = 4;
 
 struct GradParams {
@@ -79,10 +83,12 @@ struct GradParams {
   int* status;
   int maxT, maxU, V, blank;
   int ldT;      // maxT rounded up to 4: row length of nref / eBlank / emT
-  int ldW;      // columns of W (multiple of 32, <= 128) = GEMM2 N
+  int ldW;      // columns of W (multiple of 32, <= 128)
+  int N2;       // GEMM2 N: maxU rounded up to 16 (<= ldW)
   int Ku;       // maxU rounded up to 8 = GEMM1 K
   int stagesE, stagesW;
   int eBufs;    // copies of the expE^T operand in tensor memory (2 if the columns allow)
+  int dBufs;    // copies of the D1 accumulator (likewise)
   int tmemCols;
 };
 
@@ -91,6 +97,9 @@ struct GradMaps {
 };
 
 __host__ __device__ constexpr int row_stride_bytes(int tb) { return (tb * 4 + 127) & ~127; }
+__host__ __device__ constexpr int e_stage_bytes(int tb) {
+  return (4 * tb * 128 + kStageRows * row_stride_bytes(tb) + 1023) & ~1023;
+}
 
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
   hi = __float_as_uint(x) & 0xffffe000u;
@@ -129,16 +138,15 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   constexpr int kEBytes = 4 * kBoxBytes;       // E tile
   constexpr int kRowBytes = TB * 4;            // one row of per-frame scalars
   constexpr int kRowStride = row_stride_bytes(TB);  // TMA destinations are 128-byte aligned
-  constexpr int kEStage = kEBytes + 1024;      // + row shifts (padded to keep 1024-byte alignment)
+  constexpr int kEStage = e_stage_bytes(TB);   // E tile + kStageRows rows of scalars
   const int wBytes = nUB * kBoxBytes;
-  const int wScalarBytes = (1 + kMaxStagedLabels) * kRowStride;
-  const int wStage = (2 * wBytes + wScalarBytes + 1023) & ~1023;
+  const int wStage = 2 * wBytes;               // K-major copy, MN-major copy
   uint8_t* smemW = smem + (size_t)SE * kEStage;
 
-  __shared__ uint64_t barEFull[kMaxRing], barStore[kMaxRing], barEFree[kMaxRing];
+  __shared__ uint64_t barEFull[kMaxRing], barStore[kMaxRing];
   __shared__ uint64_t barWFull[kMaxRing], barWFree[kMaxRing];
-  __shared__ uint64_t barEReady[2], barE2Free[2];
-  __shared__ uint64_t barPReady, barD1Full, barD1Free, barD2Done;
+  __shared__ uint64_t barEReady[2], barE2Free[2], barD1Full[2], barD1Free[2];
+  __shared__ uint64_t barPReady, barD2Done;
   __shared__ uint32_t tmemBase;
   __shared__ int abortFlag;
   __shared__ int sWarpCnt[4];
@@ -153,19 +161,18 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     for (int s = 0; s < SE; ++s) {
       mbar_init(&barEFull[s], 1);
       mbar_init(&barStore[s], kGroupWarps);   // gradient tile complete in shared memory
-      mbar_init(&barEFree[s], 1);             // the storer, once its TMA stores have read the stage
     }
     for (int s = 0; s < SW; ++s) {
       mbar_init(&barWFull[s], 1);
-      mbar_init(&barWFree[s], kGroupWarps + 2);  // gradient warps + both MMA issuers done with it
+      mbar_init(&barWFree[s], 2);             // both MMA issuers done with it
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&barEReady[s], kGroupWarps);
       mbar_init(&barE2Free[s], 1 + kGroupWarps);  // GEMM2 done with it + gradient warps have read it
+      mbar_init(&barD1Full[s], 1);
+      mbar_init(&barD1Free[s], kGroupWarps);
     }
     mbar_init(&barPReady, 2 * kGroupWarps);
-    mbar_init(&barD1Full, 1);
-    mbar_init(&barD1Free, kGroupWarps);
     mbar_init(&barD2Done, 1);
     abortFlag = 0;
     fence_mbar_init();
@@ -209,55 +216,77 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   const uint32_t tBase = tmemBase;
   const uint32_t cPhi = 0, cPlo = p.Ku;
   constexpr uint32_t kECols = (ESPLIT ? 2 : 1) * TB;  // one copy of expE^T (hi, then lo)
-  const int EB = p.eBufs;
+  const int EB = p.eBufs, DB = p.dBufs;
   const uint32_t cE = (PSPLIT ? 2 : 1) * p.Ku;
   const uint32_t cD1 = cE + EB * kECols;
-  const uint32_t cD2 = cD1 + TB;
+  const uint32_t cD2 = cD1 + DB * TB;
   volatile int* abortp = &abortFlag;
 
-  if (warp == kWarpELoad) {
-    // ---------------- E loader: raw E tile + row shifts of tile i into E stage i % SE ----------------
-    // One copy per lane (lanes 0..3 the boxes, lane 4 the shifts): a single thread would issue
-    // them one after the other.
+  if (warp == kWarpMove) {
+    // ---------------- mover: E stage i % SE <- tile i (raw E + scalar rows); finished tile -> egrads ----------------
+    // One TMA load per lane (a single thread would issue them one after the other): lanes 0..3
+    // the boxes of E, lane 4 the row shifts, lane 5 the blank-arc sums, lanes 6.. one staged
+    // label row each.  The same warp stores finished tiles, so a stage is refilled as soon as
+    // its stores have read it.
     if (lane == 0) {
       tma_prefetch_desc(&tm.E);
+      tma_prefetch_desc(&tm.G);
       tma_prefetch_desc(&tm.nref);
+      tma_prefetch_desc(&tm.emT);
     }
-    int issued = 0;
-    for (int i = 0; i < nTiles; ++i) {
-      const int s = i % SE;
-      bool ok = true;
-      if (i >= SE)
-        ok = mbar_wait(&barEFree[s], ((i / SE) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
-      if (!__all_sync(0xffffffffu, ok)) break;
+    const uint32_t bytes =
+        (uint32_t)(kEBytes + kRowBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
+    const int myU = (lane >= 6 && lane - 6 < nStaged) ? sListU[lane - 6] : -1;
+    auto fill = [&](int i) {
+      const int s = i % SE, t0 = i * TB;
       uint8_t* st = smem + (size_t)s * kEStage;
-      const int t0 = i * TB;
-      if (lane == 0) mbar_arrive_expect_tx(&barEFull[s], (uint32_t)(kEBytes + kRowBytes));
+      uint8_t* rows = st + kEBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&barEFull[s], bytes);
       __syncwarp();
       if (lane < 4) tma_load_3d(st + lane * kBoxBytes, &tm.E, &barEFull[s], v0 + 32 * lane, t0, b);
-      else if (lane == 4) tma_load_3d(st + kEBytes, &tm.nref, &barEFull[s], t0, b, 0);
-      issued = i + 1;
+      else if (lane == 4) tma_load_3d(rows, &tm.nref, &barEFull[s], t0, b, 0);
+      else if (lane == 5) {
+        if (blankHere) tma_load_3d(rows + kRowStride, &tm.ebl, &barEFull[s], t0, b, 0);
+      } else if (myU >= 0) {
+        tma_load_3d(rows + (lane - 4) * kRowStride, &tm.emT, &barEFull[s], t0, myU, b);
+      }
+    };
+    int issued = 0;
+    for (; issued < nTiles && issued < SE; ++issued) fill(issued);
+    for (int i = 0; i < nTiles; ++i) {
+      const int s = i % SE;
+      const bool ok = mbar_wait(&barStore[s], (i / SE) & 1, abortp, p.status, kStatusTimeoutOperand);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (lane == 0) {
+        const uint8_t* st = smem + (size_t)s * kEStage;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v0 + 32 * j < p.V) tma_store_3d(&tm.G, st + j * kBoxBytes, v0 + 32 * j, i * TB, b);
+        tma_store_commit();
+        if (issued < nTiles) tma_store_wait_read();  // the stage is about to be overwritten
+      }
+      __syncwarp();
+      if (issued < nTiles) fill(issued++);
     }
-    if (lane == 0 && *abortp) {  // give copies still in flight a bounded time to land
-      for (int i = max(0, issued - SE); i < issued; ++i) {
-        const unsigned long long t1 = global_timer_ns();
-        while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
-               global_timer_ns() - t1 < 50000000ull) {
+    if (lane == 0) {
+      // all stores complete (not only read) before the CTA ends
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (*abortp) {  // give copies still in flight a bounded time to land
+        for (int i = max(0, issued - SE); i < issued; ++i) {
+          const unsigned long long t1 = global_timer_ns();
+          while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
+                 global_timer_ns() - t1 < 50000000ull) {
+          }
         }
       }
     }
   } else if (warp == kWarpWLoad) {
-    // ---------------- W loader: both W tile copies + sparse-term rows into W stage i % SW ----------------
-    // Lanes 0..7: the boxes of the two copies; lane 8: blank-arc sums; lanes 9..: one staged
-    // label row each.
+    // ---------------- W loader: both copies of W tile i into W stage i % SW ----------------
+    // Lanes 0..7: one 32-column box each (even lanes the K-major copy, odd the MN-major one).
     if (lane == 0) {
       tma_prefetch_desc(&tm.Wk);
       tma_prefetch_desc(&tm.Wmn);
-      tma_prefetch_desc(&tm.emT);
     }
-    const uint32_t bytes =
-        (uint32_t)(2 * wBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
-    const int myU = (lane >= 9 && lane - 9 < nStaged) ? sListU[lane - 9] : -1;
     int issued = 0;
     for (int i = 0; i < nTiles; ++i) {
       const int s = i % SW;
@@ -266,20 +295,13 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         ok = mbar_wait(&barWFree[s], ((i / SW) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
       if (!__all_sync(0xffffffffu, ok)) break;
       uint8_t* st = smemW + (size_t)s * wStage;
-      uint8_t* rows = st + 2 * wBytes;
       const int t0 = i * TB;
-      if (lane == 0) mbar_arrive_expect_tx(&barWFull[s], bytes);
+      if (lane == 0) mbar_arrive_expect_tx(&barWFull[s], (uint32_t)(2 * wBytes));
       __syncwarp();
-      if (lane < 8) {
-        const int j = lane >> 1;
-        if (j < nUB) {
-          if (lane & 1) tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
-          else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
-        }
-      } else if (lane == 8) {
-        if (blankHere) tma_load_3d(rows, &tm.ebl, &barWFull[s], t0, b, 0);
-      } else if (myU >= 0) {
-        tma_load_3d(rows + (1 + lane - 9) * kRowStride, &tm.emT, &barWFull[s], t0, myU, b);
+      const int j = lane >> 1;
+      if (lane < 8 && j < nUB) {
+        if (lane & 1) tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
+        else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
       }
       issued = i + 1;
     }
@@ -291,25 +313,6 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         }
       }
     }
-  } else if (warp == kWarpStore) {
-    // ---------------- storer: finished gradient tile (in the E stage) -> egrads ----------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tm.G);
-      for (int i = 0; i < nTiles; ++i) {
-        const int s = i % SE;
-        if (!mbar_wait(&barStore[s], (i / SE) & 1, abortp, p.status, kStatusTimeoutOperand)) break;
-        const uint8_t* st = smem + (size_t)s * kEStage;
-        const int t0 = i * TB;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (v0 + 32 * j < p.V) tma_store_3d(&tm.G, st + j * kBoxBytes, v0 + 32 * j, t0, b);
-        tma_store_commit();
-        tma_store_wait_read();
-        mbar_arrive(&barEFree[s]);
-      }
-      // the stores themselves complete before the kernel ends (bulk groups are flushed at exit)
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    }
   } else if (warp == kWarpMma1) {
     // ---------------- MMA issuer 1: GEMM1, D1[v, t] = expP^T . W^T per tile ----------------
     if (lane == 0) {
@@ -320,27 +323,28 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       // phase with that arrival.)
       bool ok = mbar_wait(&barPReady, 0, abortp, p.status, kStatusTimeoutOperand);
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int s = i % SW;
+        const int s = i % SW, db = i % DB;
         ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
-        if (ok && i > 0)
-          ok = mbar_wait(&barD1Free, (i - 1) & 1, abortp, p.status, kStatusTimeoutOperand);
+        if (ok && i >= DB)  // the gradient warps have read this copy of D1
+          ok = mbar_wait(&barD1Free[db], ((i / DB) - 1) & 1, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
         const uint32_t wK = smem_u32(smemW + (size_t)s * wStage);
+        const uint32_t d1 = tBase + cD1 + db * TB;
         for (int ks = 0; ks < kSteps1; ++ks) {
           const uint32_t off = (uint32_t)((ks >> 2) * kBoxBytes + (ks & 3) * 32);
           const uint64_t bW = smem_desc_sw128(wK + off, 16, 1024);
-          mma_tf32_ts(tBase + cD1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
-          if (PSPLIT) mma_tf32_ts(tBase + cD1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
+          mma_tf32_ts(d1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
+          if (PSPLIT) mma_tf32_ts(d1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
         }
-        mma_commit(&barD1Full);
+        mma_commit(&barD1Full[db]);
         mma_commit(&barWFree[s]);
       }
     }
   } else if (warp == kWarpMma2) {
     // ---------------- MMA issuer 2: GEMM2, D2[v, u] += expE^T . W over all tiles ----------------
     if (lane == 0) {
-      const uint32_t idesc2 = idesc_tf32(128, p.ldW, 0, 1);  // B = W tile, MN-major (K = t)
+      const uint32_t idesc2 = idesc_tf32(128, p.N2, 0, 1);  // B = W tile, MN-major (K = t)
       bool ok = true;
       for (int i = 0; i < nTiles && ok; ++i) {
         const int s = i % SW;
@@ -467,10 +471,11 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         }
       }
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int se = i % SE, sw = i % SW, t0 = i * TB;
+        const int se = i % SE, t0 = i * TB;
         const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
-        const int eb = i % EB;
-        ok = mbar_wait(&barD1Full, i & 1, abortp, p.status, kStatusTimeoutMma) &&
+        const int eb = i % EB, db = i % DB;
+        ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma) &&
+             mbar_wait(&barD1Full[db], (i / DB) & 1, abortp, p.status, kStatusTimeoutMma) &&
              mbar_wait(&barEReady[eb], (i / EB) & 1, abortp, p.status, kStatusTimeoutOperand);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -481,7 +486,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 #pragma unroll
         for (int c = 0; c < TBH; c += 8) {
           uint32_t r[8], xh[8], xl[8];
-          tmem_ld8(tBase + laneAddr + cD1 + h * TBH + c, r);
+          tmem_ld8(tBase + laneAddr + cD1 + db * TB + h * TBH + c, r);
           tmem_ld8(tBase + laneAddr + cEhi + c, xh);
           if (ESPLIT) tmem_ld8(tBase + laneAddr + cElo + c, xl);
           tmem_wait_ld();
@@ -495,15 +500,12 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&barD1Free);
+          mbar_arrive(&barD1Free[db]);
           mbar_arrive(&barE2Free[eb]);
         }
-        ok = mbar_wait(&barWFull[sw], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        uint8_t* col = smem + (size_t)se * kEStage + colOff;
-        const float* rows =
-            reinterpret_cast<const float*>(smemW + (size_t)sw * wStage + 2 * wBytes) + h * TBH;
+        uint8_t* stE = smem + (size_t)se * kEStage;
+        uint8_t* col = stE + colOff;
+        const float* rows = reinterpret_cast<const float*>(stE + kEBytes + kRowStride) + h * TBH;
         if (v == p.blank) {
 #pragma unroll
           for (int j = 0; j < TBH; ++j) d1[j] -= rows[j];
@@ -529,10 +531,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         }
         fence_proxy_async_smem();  // the tile is read next by TMA stores
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&barWFree[sw]);   // sparse-term rows no longer needed
-          mbar_arrive(&barStore[se]);   // my part of the gradient tile is in place
-        }
+        if (lane == 0) mbar_arrive(&barStore[se]);  // my part of the gradient tile is in place
       }
     }
 
@@ -637,42 +636,46 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
 }
 
 struct TileCfg {
-  int TB, SE, SW, EB;
+  int TB, SE, SW, EB, DB;
 };
 
-// Tile height and ring depths.  TMEM: (1|2)*Ku (expP^T) + (1|2)*TB (expE^T) + TB (D1) + ldW
-// (D2) <= 512 columns.  Shared memory: SE E stages + SW W stages within the 227 KB of a CTA.
-// Prefer the tallest tile that still leaves three E stages (copies issued two tiles ahead).
-TileCfg pick_tile(int Ku, int ldW, int passes, int staticSmem) {
+// Tile height, ring depths and TMEM copies.  TMEM: (1|2)*Ku (expP^T) + EB*(1|2)*TB (expE^T) +
+// DB*TB (D1) + N2 (D2) <= 512 columns.  Shared memory: SE E stages + SW W stages within the
+// 227 KB of a CTA.  Preference: at least three E stages (copies issued two tiles ahead), then
+// the double-buffered TMEM operands, then the taller tile.
+TileCfg pick_tile(int Ku, int ldW, int N2, int passes, int staticSmem) {
   const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
   const int room = 227 * 1024 - staticSmem - 2048;
-  TileCfg best{0, 0, 0, 0};
+  TileCfg best{0, 0, 0, 0, 0};
+  long bestScore = -1;
   for (int TB : {64, 48, 32}) {
-    // two copies of expE^T when the columns allow; a 32-frame tile may fall back to one
-    int EB = 2;
-    if (fp * Ku + (2 * fe + 1) * TB + ldW > 512) {
-      if (TB > 32 || fp * Ku + (fe + 1) * TB + ldW > 512) continue;
-      EB = 1;
-    }
-    const int eStage = 4 * TB * 128 + 1024;
-    const int wStage = (2 * (ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
+    const int wStage = 2 * (ldW / 32) * TB * 128;
     const int SW = 2;
-    const int SE = std::min(kMaxRing, (room - SW * wStage) / eStage);
+    const int SE = std::min(kMaxRing, (room - SW * wStage) / e_stage_bytes(TB));
     if (SE < 2) continue;
-    if (best.TB == 0 || (best.SE < 3 && SE >= 3)) best = TileCfg{TB, SE, SW, EB};
-    if (best.SE >= 3) break;
+    for (int bufs = 3; bufs >= 0; --bufs) {  // (EB,DB) = (2,2), (2,1), (1,2), (1,1)
+      const int EB = 1 + (bufs >> 1), DB = 1 + (bufs & 1);
+      if (fp * Ku + EB * fe * TB + DB * TB + N2 > 512) continue;
+      const long score = (long)std::min(SE, 3) * 10000 + (EB + DB) * 1000 + TB;
+      if (score > bestScore) {
+        bestScore = score;
+        best = TileCfg{TB, SE, SW, EB, DB};
+      }
+      break;
+    }
   }
   return best;
 }
 
 template <int TB, bool ESPLIT, bool PSPLIT>
 void launch_variant(const GradMaps& tm, GradParams p, TileCfg cfg, Dims d, cudaStream_t stream) {
-  const int eStage = 4 * TB * 128 + 1024;
-  const int wStage = (2 * (p.ldW / 32) * TB * 128 + (1 + kMaxStagedLabels) * row_stride_bytes(TB) + 1023) & ~1023;
+  const int eStage = e_stage_bytes(TB);
+  const int wStage = 2 * (p.ldW / 32) * TB * 128;
   p.stagesE = cfg.SE;
   p.stagesW = cfg.SW;
   p.eBufs = cfg.EB;
-  const int cols = (PSPLIT ? 2 : 1) * p.Ku + cfg.EB * (ESPLIT ? 2 : 1) * TB + TB + p.ldW;
+  p.dBufs = cfg.DB;
+  const int cols = (PSPLIT ? 2 : 1) * p.Ku + cfg.EB * (ESPLIT ? 2 : 1) * TB + cfg.DB * TB + p.N2;
   p.tmemCols = pow2_cols(cols);
   size_t smem = (size_t)cfg.SE * eStage + (size_t)cfg.SW * wStage + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it may hold all 512 TMEM columns
@@ -695,7 +698,7 @@ bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passe
   if ((reinterpret_cast<uintptr_t>(E) & 15) != 0 || (reinterpret_cast<uintptr_t>(egrads) & 15) != 0)
     return false;
   const int Ku = (int)round_up64(d.maxU, 8);
-  return pick_tile(Ku, grads_umma_ld_w(d), passes, kStaticSmemBound).TB > 0;
+  return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound).TB > 0;
 }
 
 void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
@@ -725,8 +728,9 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
   p.ldT = grads_umma_ld_t(d);
   p.ldW = grads_umma_ld_w(d);
   p.Ku = (int)round_up64(d.maxU, 8);
-  p.stagesE = p.stagesW = p.eBufs = p.tmemCols = 0;
-  const TileCfg cfg = pick_tile(p.Ku, p.ldW, passes, kStaticSmemBound);
+  p.N2 = (int)round_up64(d.maxU, 16);
+  p.stagesE = p.stagesW = p.eBufs = p.dBufs = p.tmemCols = 0;
+  const TileCfg cfg = pick_tile(p.Ku, p.ldW, p.N2, passes, kStaticSmemBound);
   if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
   const int TB = cfg.TB;
   const uint64_t V = d.V, T = d.maxT, B = d.B, ldW = p.ldW, ldT = p.ldT, U = d.maxU;
