@@ -368,8 +368,8 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
           "maxLabelLength <= 128 and 16-byte aligned emissions and egrads");
     if (can && g_opt.grads_path != 1) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
-      launch_unskew_round(ws.Ws, ws.EMs, st.rowRef, ws.eBlank, ws.W, ws.emT, ws.nref, ws.ebl,
-                          inLens, labLens, g, d, g_stream);
+      launch_unskew_round(ws.Ws, ws.EMs, st.rowRef, ws.eBlank, deltas, ws.W, ws.emT, ws.nref,
+                          ws.ebl, inLens, labLens, g, d, g_stream);
       launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
                         labels, deltas, egrads, pgrads, inLens, labLens, d, passes, ws.status,
                         g_stream);

@@ -434,18 +434,28 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         const uint32_t cEhi = cE + eb * kECols + h * TBH, cElo = cEhi + TB;
         float xs[TBH];
 #pragma unroll
-        for (int j = 0; j < TBH; ++j) {
-          const int t = h * TBH + j;
-          xs[j] = fmaf(*reinterpret_cast<const float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)),
-                       kLog2e, nr[j]);
+        for (int j = 0; j < TBH; j += 4) {
+          const float4 sh = *reinterpret_cast<const float4*>(nr + j);
+          const float shj[4] = {sh.x, sh.y, sh.z, sh.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int t = h * TBH + j + k;
+            xs[j + k] = fmaf(
+                *reinterpret_cast<const float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)), kLog2e,
+                shj[k]);
+          }
+        }
+        if (tValid < TBH) {  // last tile of the utterance (or a column beyond the vocabulary):
+#pragma unroll             // frames at or beyond T_b contribute nothing, exp2(-inf) = 0
+          for (int j = 0; j < TBH; ++j)
+            if (j >= tValid) xs[j] = -INFINITY;
         }
 #pragma unroll
         for (int c = 0; c < TBH; c += 8) {
           uint32_t hi[8], lo[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            float x = ex2_approx(xs[c + j]);
-            if (c + j >= tValid) x = 0.0f;  // frames at or beyond T_b contribute nothing
+            const float x = ex2_approx(xs[c + j]);
             if (ESPLIT) split_tf32(x, hi[j], lo[j]);
             else hi[j] = __float_as_uint(tf32_round(x));
           }
@@ -459,7 +469,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         if (lane == 0) mbar_arrive(&barEReady[eb]);
       }
     } else {
-      // ---- gradient group: egrads tile = delta * (expE * D1 - sparse), in place ----
+      // ---- gradient group: egrads tile = expE * D1 - sparse (delta_b is inside W and the rows) ----
       const float* embT = p.emT + (i64)b * p.maxU * p.ldT;
       // which of the block's label positions carry MY column (almost always none)
       unsigned stagedMine = 0;
@@ -526,8 +536,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 #pragma unroll
         for (int j = 0; j < TBH; ++j) {
           const int t = h * TBH + j;
-          *reinterpret_cast<float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)) =
-              (j < tValid) ? delta * d1[j] : 0.0f;
+          // (frames at or beyond T_b: expE and the rows of W are zero there, so is d1)
+          *reinterpret_cast<float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)) = d1[j];
         }
         fence_proxy_async_smem();  // the tile is read next by TMA stores
         __syncwarp();
@@ -559,9 +569,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
               float xp = __uint_as_float(xh[j]);
               if (PSPLIT) xp += __uint_as_float(xl[j]);
               val = xp * __uint_as_float(d2[j]);
-              if (v == p.blank) val -= sPb[u];
-              if (sLab[u] == v) val -= sPl[u];
-              val *= delta;
+              if (v == p.blank) val -= delta * sPb[u];
+              if (sLab[u] == v) val -= delta * sPl[u];
             }
             pg[(i64)u * p.V + v] = val;
           }
@@ -584,19 +593,23 @@ int pow2_cols(int x) {
 }
 
 // Re-layout after the reverse sweep, one CTA per 32x32 lattice tile:
-//   Ws (skewed)  -> W [B,maxT,ldW] rounded to TF32 (round-to-nearest; the tensor core would
-//                   otherwise truncate), zero outside the valid lattice;
-//   EMs (skewed) -> emT [B,maxU,ldT]: label-arc occupancies with the frames contiguous, so a
-//                   tile's slice for one label is one TMA row; zero outside the lattice;
-//   rowRef, eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT] (row length a multiple of
-//                   4 floats as TMA requires).
+//   Ws (skewed)  -> W [B,maxT,ldW] = delta_b * weights, rounded to TF32 (round-to-nearest; the
+//                   tensor core would otherwise truncate), zero outside the valid lattice;
+//   EMs (skewed) -> emT [B,maxU,ldT] = delta_b * label-arc occupancies with the frames
+//                   contiguous, so a tile's slice for one label is one TMA row; zero outside;
+//   rowRef, eBlank -> nref = -rowRef*log2(e) and ebl = delta_b * eBlank, both [B,ldT] (row
+//                   length a multiple of 4 floats as TMA requires).
+// With the upstream gradient delta_b folded in here the gradient kernel never multiplies by it
+// per element, and frames at or beyond T_b come out as exact zeros without a select.
 __global__ void __launch_bounds__(256) unskew_round_kernel(
     const float* __restrict__ Ws, const float* __restrict__ EMs, const float* __restrict__ rowRef,
-    const float* __restrict__ eBlank, float* __restrict__ W, float* __restrict__ emT,
-    float* __restrict__ nref, float* __restrict__ ebl, const int* __restrict__ inLens,
-    const int* __restrict__ labLens, int maxT, int maxU, int ld, i64 latStride, int ldW, int ldT) {
+    const float* __restrict__ eBlank, const float* __restrict__ deltas, float* __restrict__ W,
+    float* __restrict__ emT, float* __restrict__ nref, float* __restrict__ ebl,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int ld,
+    i64 latStride, int ldW, int ldT) {
   __shared__ float tW[32][33], tE[32][33];
   const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
+  const float delta = deltas ? deltas[b] : 1.0f;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int u = u0 + lane;
@@ -608,8 +621,8 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
         float a = 0.0f, c = 0.0f;
         if (t0 + tt < T && u < U) {
           const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
-          a = Ws[o];
-          c = EMs[o];
+          a = Ws[o] * delta;
+          c = EMs[o] * delta;
         }
         tW[tt][lane] = a;
         tE[tt][lane] = c;
@@ -621,7 +634,7 @@ __global__ void __launch_bounds__(256) unskew_round_kernel(
     if (t < ldT) {
       const bool ok = t < T;
       nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
-      ebl[(i64)b * ldT + t] = ok ? eBlank[(i64)b * maxT + t] : 0.0f;
+      ebl[(i64)b * ldT + t] = ok ? eBlank[(i64)b * maxT + t] * delta : 0.0f;
     }
   }
   __syncthreads();
@@ -702,14 +715,15 @@ bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passe
 }
 
 void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
-                         const float* eBlank, float* W, float* emT, float* nref, float* ebl,
+                         const float* eBlank, const float* deltas, float* W, float* emT,
+                         float* nref, float* ebl,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   const int ldW = grads_umma_ld_w(d), ldT = grads_umma_ld_t(d);
   dim3 grid(div_up(ldW, 32), div_up(ldT, 32), d.B);
   ScopedKernel sk("lattice_unskew_round", stream);
-  unskew_round_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, rowRef, eBlank, W, emT, nref, ebl, inLens,
+  unskew_round_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, rowRef, eBlank, deltas, W, emT, nref, ebl, inLens,
                                                 labLens, d.maxT, d.maxU, g.ld, g.stride, ldW, ldT);
   TB200_CHECK_LAUNCH();
 }

@@ -110,9 +110,11 @@ int grads_umma_ld_w(Dims d);  // row length of W: maxU rounded up to 32
 int grads_umma_ld_t(Dims d);  // row length of nref / ebl / emT: maxT rounded up to 4
 bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes);
 // After the reverse sweep: Ws/EMs (skewed) -> W [B,maxT,ldW] rounded to TF32 and
-// emT [B,maxU,ldT]; rowRef/eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT].
+// emT [B,maxU,ldT]; rowRef/eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT].  W, emT
+// and ebl are scaled by deltas[b] (1 if deltas is null).
 void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
-                         const float* eBlank, float* W, float* emT, float* nref, float* ebl,
+                         const float* eBlank, const float* deltas, float* W, float* emT,
+                         float* nref, float* ebl,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream);
 void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
