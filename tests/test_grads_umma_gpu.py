@@ -71,9 +71,15 @@ def test_repeated_labels_and_nonzero_blank_against_oracle():
     E, P, labels, il, ll, deltas = make(B, T, U, V, seed=4, repeat_labels=True, blank=blank)
     _, eg, pg = grads(E, P, labels, il, ll, deltas, path=2, blank=blank)
     n = lambda t: t.cpu().numpy()
+    # against exact arithmetic (float64): tighter than against the reference's own fp32
+    # arithmetic, which is itself 5e-5 away from it on this case
+    truth = O.truth64(n(E), n(P), n(labels), n(il), n(ll), blank=blank)
+    dl = n(deltas).astype(np.float64)[:, None, None]
+    assert abi.rel_to_max(n(eg), truth["egrads"] * dl) <= 1e-4
+    assert abi.rel_to_max(n(pg), truth["pgrads"] * dl) <= 1e-4
     want = O.loss_and_grads(n(E), n(P), n(labels), n(il), n(ll), blank=blank, deltas=n(deltas))
-    assert abi.rel_to_max(n(eg), want["egrads"]) <= 1e-4
-    assert abi.rel_to_max(n(pg), want["pgrads"]) <= 1e-4
+    assert abi.rel_to_max(n(eg), want["egrads"]) <= 3e-4
+    assert abi.rel_to_max(n(pg), want["pgrads"]) <= 3e-4
 
 
 def test_zero_length_utterances_give_zero_gradients():

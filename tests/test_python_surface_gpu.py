@@ -109,8 +109,10 @@ def test_non_default_stream_and_blank():
         vit = TransducerLoss(blank=blank).viterbi(Ed.detach(), Pd.detach(), il.cuda(), ll.cuda())
     s.synchronize()
     assert np.allclose(costs.detach().cpu().numpy(), want["costs"], rtol=1e-5)
-    assert np.abs(Ed.grad.cpu().numpy() - want["egrads"]).max() < 1e-4
-    assert np.abs(Pd.grad.cpu().numpy() - want["pgrads"]).max() < 1e-4
+    # 1e-4 of the largest gradient element (two fp32 evaluations of a sum of 30 occupancies of
+    # magnitude 10 differ by that much in absolute terms)
+    assert np.abs(Ed.grad.cpu().numpy() - want["egrads"]).max() < 1e-4 * np.abs(want["egrads"]).max()
+    assert np.abs(Pd.grad.cpu().numpy() - want["pgrads"]).max() < 1e-4 * np.abs(want["pgrads"]).max()
     wv = O.viterbi(E.numpy(), P.numpy(), il.numpy(), ll.numpy(), blank=blank)
     for b in range(B):
         assert np.array_equal(vit.cpu().numpy()[b, :ll[b]], wv[b, :ll[b]])

@@ -81,6 +81,7 @@ struct LogNormWs {
 // What the forward call leaves for the backward call (opaque to the caller).
 struct SavedState {
   float *alphasS, *LNs, *ELs, *ebl, *rowRef, *maxP;
+  float2* arcs;  // arc terms of the single-warp sweeps (label axis <= 128), else null
   SavedState(Carver& c, const Dims& d) {
     const SkewGeom g = skew_geom(d);
     const size_t B = d.B;
@@ -90,6 +91,8 @@ struct SavedState {
     ebl = c.take<float>(B * d.maxT);
     rowRef = c.take<float>(B * d.maxT);
     maxP = c.take<float>(B * d.maxU);
+    arcs = c.take<float2>(lattice_warp_supported(d) ? B * g.stride : 0);
+    if (!lattice_warp_supported(d)) arcs = nullptr;
   }
 };
 
@@ -324,13 +327,20 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
     LogNormWs ws(c, d);
     const SkewGeom g = skew_geom(d);
     log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws);
-    launch_lattice_prep(E, fw.LN, st.LNs, st.ELs, st.ebl, labels, inLens, labLens, g, d, g_stream);
+    launch_lattice_prep(E, P, fw.LN, st.LNs, st.ELs, st.ebl, st.arcs, labels, inLens, labLens, g, d,
+                        g_stream);
     if (lossSum) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.ticket, 0, sizeof(unsigned), g_stream));
       if (B == 0) TB200_CUDA_CHECK(cudaMemsetAsync(lossSum, 0, sizeof(float), g_stream));
     }
-    launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
-                      d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
+    // The shape alone decides which pair of sweeps runs (the backward call must pick the
+    // reverse sweep that matches the format of the saved alphas).
+    if (lattice_warp_supported(d))
+      launch_alpha_warp(st.arcs, costs, st.alphasS, g, inLens, labLens, d, lossSum,
+                        lossSum ? ws.ticket : nullptr, ws.status, g_stream);
+    else
+      launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
+                        d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
   });
 }
 
@@ -357,26 +367,36 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
     BackwardWs ws(c, d);
     const SkewGeom g = skew_geom(d);
     const int ldW = ld_w(d);
-    launch_gamma_skew(P, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
-                      inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
-                      g_stream);
     const int passes = g_opt.grad_passes;
     const bool can = grads_umma_supported(E, egrads, d, passes);
     if (g_opt.grads_path == 2 && !can)
       throw std::invalid_argument(
           "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
           "maxLabelLength <= 128 and 16-byte aligned emissions and egrads");
-    if (can && g_opt.grads_path != 1) {
+    const bool tensorCore = can && g_opt.grads_path != 1;
+    if (lattice_warp_supported(d)) {
+      // single-warp reverse sweep: blank/label arc occupancies to the skewed lattices
+      // ws.Ws / ws.EMs, then re-laid out for whichever gradient kernels follow
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
-      launch_unskew_round(ws.Ws, ws.EMs, st.rowRef, ws.eBlank, deltas, ws.W, ws.emT, ws.nref,
-                          ws.ebl, inLens, labLens, g, d, g_stream);
-      launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
-                        labels, deltas, egrads, pgrads, inLens, labLens, d, passes, ws.status,
+      launch_gamma_warp(st.arcs, st.alphasS, g, inLens, labLens, ws.Ws, ws.EMs, ws.pBlank,
+                        ws.pLabel, d, ws.status, g_stream);
+      if (tensorCore) {
+        launch_unskew_round(ws.Ws, ws.EMs, st.LNs, st.rowRef, st.maxP, deltas, ws.W, ws.emT,
+                            ws.nref, ws.ebl, inLens, labLens, g, d, true, g_stream);
+        launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
+                          labels, deltas, egrads, pgrads, inLens, labLens, d, passes, ws.status,
+                          g_stream);
+        return;
+      }
+      launch_unskew_round(ws.Ws, ws.EMs, st.LNs, st.rowRef, st.maxP, nullptr, ws.W, ws.em,
+                          nullptr, ws.eBlank, inLens, labLens, g, d, false, g_stream);
+    } else {
+      launch_gamma_skew(P, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
+                        inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
                         g_stream);
-      return;
+      launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
     }
     launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
-    launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
     launch_egrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
                       egrads, inLens, labLens, d, g_stream);
     launch_pgrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,

@@ -592,59 +592,97 @@ int pow2_cols(int x) {
   return c;
 }
 
-// Re-layout after the reverse sweep, one CTA per 32x32 lattice tile:
-//   Ws (skewed)  -> W [B,maxT,ldW] = delta_b * weights, rounded to TF32 (round-to-nearest; the
-//                   tensor core would otherwise truncate), zero outside the valid lattice;
-//   EMs (skewed) -> emT [B,maxU,ldT] = delta_b * label-arc occupancies with the frames
+// Re-layout after the reverse sweep (gamma_warp_kernel), one CTA per 32 frames of one utterance,
+// walking the label axis in 32x32 lattice tiles.  With delta_b the upstream gradient:
+//   stayS + stepS (skewed) -> W [B,maxT,ldW] = delta_b * g * exp(ref(t) + maxP(u) - LN(t,u)),
+//                   g = stay + step, rounded to TF32 (round-to-nearest; the tensor core would
+//                   otherwise truncate), zero outside the valid lattice.  (The exponent is
+//                   clamped at 80: it only gets there where the factored log-normaliser had
+//                   underflowed.)
+//   stepS (skewed) -> emT [B,maxU,ldT] = delta_b * label-arc occupancies with the frames
 //                   contiguous, so a tile's slice for one label is one TMA row; zero outside;
-//   rowRef, eBlank -> nref = -rowRef*log2(e) and ebl = delta_b * eBlank, both [B,ldT] (row
-//                   length a multiple of 4 floats as TMA requires).
-// With the upstream gradient delta_b folded in here the gradient kernel never multiplies by it
-// per element, and frames at or beyond T_b come out as exact zeros without a select.
+//   stayS          -> ebl [B,ldT] = delta_b * sum_u stay(t,u), added in a fixed order;
+//   rowRef         -> nref [B,ldT] = -rowRef * log2(e)   (row lengths: multiples of 4 floats
+//                   as TMA requires).
+// With delta_b folded in here the gradient kernel never multiplies by it per element, and
+// frames at or beyond T_b come out as exact zeros without a select.
+// TC = false serves the SIMT gradient kernels instead: W unrounded and unscaled, the label-arc
+// occupancies row-major [B,maxT,maxU] (through emT), the row sums with row length maxT
+// (through ebl), no nref.
+template <bool TC>
 __global__ void __launch_bounds__(256) unskew_round_kernel(
-    const float* __restrict__ Ws, const float* __restrict__ EMs, const float* __restrict__ rowRef,
-    const float* __restrict__ eBlank, const float* __restrict__ deltas, float* __restrict__ W,
+    const float* __restrict__ stayS, const float* __restrict__ stepS,
+    const float* __restrict__ LNs, const float* __restrict__ rowRef,
+    const float* __restrict__ maxP, const float* __restrict__ deltas, float* __restrict__ W,
     float* __restrict__ emT, float* __restrict__ nref, float* __restrict__ ebl,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int ld,
     i64 latStride, int ldW, int ldT) {
-  __shared__ float tW[32][33], tE[32][33];
-  const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
-  const float delta = deltas ? deltas[b] : 1.0f;
+  __shared__ float tW[32][33], tE[32][33], tS[32][33];
+  const int b = blockIdx.y, t0 = blockIdx.x * 32;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int u = u0 + lane;
-  const bool live = t0 < T && u0 < U;
-  if (live) {
-    for (int ds = w; ds < 63; ds += 8) {
-      const int tt = ds - lane;
-      if (tt >= 0 && tt < 32) {
-        float a = 0.0f, c = 0.0f;
-        if (t0 + tt < T && u < U) {
-          const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
-          a = Ws[o] * delta;
-          c = EMs[o] * delta;
+  const float delta = (TC && deltas) ? deltas[b] : 1.0f;
+  float rowSum[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // frames t0 + 4w + k, complete in every lane
+  for (int u0 = 0; u0 < ldW; u0 += 32) {
+    const int u = u0 + lane;
+    const bool live = t0 < T && u0 < U;
+    if (live) {
+      const float mp = maxP[(i64)b * maxU + min(u, U - 1)];
+      for (int ds = w; ds < 63; ds += 8) {
+        const int tt = ds - lane;
+        if (tt >= 0 && tt < 32) {
+          float a = 0.0f, c = 0.0f, st = 0.0f;
+          const int t = t0 + tt;
+          if (t < T && u < U) {
+            const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
+            st = stayS[o];
+            const float sp = stepS[o];
+            const float sh = fminf((rowRef[(i64)b * maxT + t] + mp) - LNs[o], 80.0f);
+            a = (st + sp) * expf(sh) * delta;
+            c = sp * delta;
+          }
+          tW[tt][lane] = a;
+          tE[tt][lane] = c;
+          tS[tt][lane] = st;
         }
-        tW[tt][lane] = a;
-        tE[tt][lane] = c;
       }
     }
-  }
-  if (blockIdx.x == 0 && threadIdx.x < 32) {
-    const int t = t0 + lane;
-    if (t < ldT) {
-      const bool ok = t < T;
-      nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
-      ebl[(i64)b * ldT + t] = ok ? eBlank[(i64)b * maxT + t] * delta : 0.0f;
-    }
-  }
-  __syncthreads();
+    __syncthreads();
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int tt = w * 4 + k, t = t0 + tt;
-    if (t < maxT && u < ldW) W[((i64)b * maxT + t) * ldW + u] = live ? tf32_round(tW[tt][lane]) : 0.0f;
-    // transposed: lane <-> frame, row <-> label position
-    const int uu = u0 + tt, t2 = t0 + lane;
-    if (uu < maxU && t2 < ldT) emT[((i64)b * maxU + uu) * ldT + t2] = live ? tE[lane][tt] : 0.0f;
+    for (int k = 0; k < 4; ++k) {
+      const int tt = w * 4 + k, t = t0 + tt;
+      if (t < maxT && u < ldW)
+        W[((i64)b * maxT + t) * ldW + u] = live ? (TC ? tf32_round(tW[tt][lane]) : tW[tt][lane]) : 0.0f;
+      if (TC) {  // transposed: lane <-> frame, row <-> label position
+        const int uu = u0 + tt, t2 = t0 + lane;
+        if (uu < maxU && t2 < ldT) emT[((i64)b * maxU + uu) * ldT + t2] = live ? tE[lane][tt] : 0.0f;
+      } else if (t < maxT && u < maxU) {
+        emT[((i64)b * maxT + t) * maxU + u] = live ? tE[tt][lane] : 0.0f;
+      }
+      if (live) {
+        float v = tS[tt][lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        rowSum[k] += v;
+      }
+    }
+    __syncthreads();
+  }
+  if (lane < 4) {
+    const int t = t0 + w * 4 + lane;
+    const bool ok = t < T;
+    float rs = rowSum[0];
+    if (lane == 1) rs = rowSum[1];
+    if (lane == 2) rs = rowSum[2];
+    if (lane == 3) rs = rowSum[3];
+    if (TC) {
+      if (t < ldT) {
+        nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
+        ebl[(i64)b * ldT + t] = ok ? rs * delta : 0.0f;
+      }
+    } else if (t < maxT) {
+      ebl[(i64)b * maxT + t] = ok ? rs : 0.0f;
+    }
   }
 }
 
@@ -714,17 +752,23 @@ bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passe
   return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound).TB > 0;
 }
 
-void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
-                         const float* eBlank, const float* deltas, float* W, float* emT,
-                         float* nref, float* ebl,
-                         const int* inLens, const int* labLens, SkewGeom g, Dims d,
+void launch_unskew_round(const float* stayS, const float* stepS, const float* LNs,
+                         const float* rowRef, const float* maxP, const float* deltas, float* W,
+                         float* emT, float* nref, float* ebl, const int* inLens,
+                         const int* labLens, SkewGeom g, Dims d, bool tensorCore,
                          cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   const int ldW = grads_umma_ld_w(d), ldT = grads_umma_ld_t(d);
-  dim3 grid(div_up(ldW, 32), div_up(ldT, 32), d.B);
+  dim3 grid(div_up(ldT, 32), d.B);
   ScopedKernel sk("lattice_unskew_round", stream);
-  unskew_round_kernel<<<grid, 256, 0, stream>>>(Ws, EMs, rowRef, eBlank, deltas, W, emT, nref, ebl, inLens,
-                                                labLens, d.maxT, d.maxU, g.ld, g.stride, ldW, ldT);
+  if (tensorCore)
+    unskew_round_kernel<true><<<grid, 256, 0, stream>>>(stayS, stepS, LNs, rowRef, maxP, deltas, W,
+                                                        emT, nref, ebl, inLens, labLens, d.maxT,
+                                                        d.maxU, g.ld, g.stride, ldW, ldT);
+  else
+    unskew_round_kernel<false><<<grid, 256, 0, stream>>>(stayS, stepS, LNs, rowRef, maxP, nullptr,
+                                                         W, emT, nullptr, ebl, inLens, labLens,
+                                                         d.maxT, d.maxU, g.ld, g.stride, ldW, ldT);
   TB200_CHECK_LAUNCH();
 }
 

@@ -43,10 +43,18 @@ struct SkewGeom {
 };
 SkewGeom skew_geom(Dims d);
 
+// "No such arc" in the skewed arc-term array of the single-warp sweeps: a large negative
+// finite float (-5.97e29) whose four bytes are equal, so that memset can write it.
+constexpr unsigned kNoArcBits = 0xF0F0F0F0u;
+constexpr int kNoArcByte = 0xF0;
+
 // LN (row-major) -> LNs (skewed); ELs[t,u] = E[t,label_u] (skewed); ebl[b,t] = E[t,blank].
-void launch_lattice_prep(const float* E, const float* LN, float* LNs, float* ELs, float* ebl,
-                         const int* labels, const int* inLens, const int* labLens, SkewGeom g,
-                         Dims d, cudaStream_t stream);
+// If arcs is not null: arcs[t,u] (skewed, [B,nDiag,ld] float2) = log2-unit log-probabilities of
+// the blank arc and the label arc leaving node (t,u), kNoArcBits where there is none.
+void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
+                         float* ELs, float* ebl, float2* arcs, const int* labels,
+                         const int* inLens, const int* labLens, SkewGeom g, Dims d,
+                         cudaStream_t stream);
 
 void launch_alpha_skew(const float* P, float* costs, float* alphasS, const float* LNs,
                        const float* ELs, const float* ebl, SkewGeom g, const int* labels,
@@ -109,19 +117,40 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
 int grads_umma_ld_w(Dims d);  // row length of W: maxU rounded up to 32
 int grads_umma_ld_t(Dims d);  // row length of nref / ebl / emT: maxT rounded up to 4
 bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes);
-// After the reverse sweep: Ws/EMs (skewed) -> W [B,maxT,ldW] rounded to TF32 and
-// emT [B,maxU,ldT]; rowRef/eBlank -> nref = -rowRef*log2(e) and ebl, both [B,ldT].  W, emT
-// and ebl are scaled by deltas[b] (1 if deltas is null).
-void launch_unskew_round(const float* Ws, const float* EMs, const float* rowRef,
-                         const float* eBlank, const float* deltas, float* W, float* emT,
-                         float* nref, float* ebl,
-                         const int* inLens, const int* labLens, SkewGeom g, Dims d,
+// After the reverse sweep of lattice_warp.cu: stayS/stepS/LNs (skewed) ->
+//   tensorCore: W [B,maxT,ldW] rounded to TF32, emT [B,maxU,ldT], ebl [B,ldT] (row sums of
+//               stay); rowRef -> nref = -rowRef*log2(e) [B,ldT].  W, emT and ebl are scaled by
+//               deltas[b] (1 if deltas is null).  Operands of launch_grads_umma.
+//   otherwise:  W [B,maxT,ldW] unrounded and unscaled, em [B,maxT,maxU] (passed as emT),
+//               eBlank [B,maxT] (passed as ebl); nref and deltas unused.  Operands of the SIMT
+//               gradient kernels.
+void launch_unskew_round(const float* stayS, const float* stepS, const float* LNs,
+                         const float* rowRef, const float* maxP, const float* deltas, float* W,
+                         float* emT, float* nref, float* ebl, const int* inLens,
+                         const int* labLens, SkewGeom g, Dims d, bool tensorCore,
                          cudaStream_t stream);
 void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
                        const float* emT, const float* nref, const float* ebl, const float* pBlank,
                        const float* pLabel, const int* labels, const float* deltas, float* egrads,
                        float* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
                        int* status, cudaStream_t stream);
+
+// ---- lattice_warp.cu -------------------------------------------------------------
+// Single-warp lattice sweeps on skewed lattices for label axes of at most 128 positions.
+bool lattice_warp_supported(Dims d);
+// alpha recursion from the arc terms; writes costs (and the loss sum, see launch_alpha_skew)
+// and alphasS -- in LOG2 units, for launch_gamma_warp only (the nodes of the stored diagonals
+// that lie outside the lattice receive large negative numbers).  status: device error word (a copy that never lands
+// is recorded there and the cost becomes NaN).
+void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, SkewGeom g,
+                       const int* inLens, const int* labLens, Dims d, float* lossSum,
+                       unsigned* ticket, int* status, cudaStream_t stream);
+// Reverse sweep: blank-arc and label-arc occupancies of every valid node to the skewed
+// lattices stayS / stepS (the terminating blank counts as the blank arc of node (T-1,U-1)),
+// their sums over frames to pBlank / pLabel [B,maxU].
+void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, const int* inLens,
+                       const int* labLens, float* stayS, float* stepS, float* pBlank,
+                       float* pLabel, Dims d, int* status, cudaStream_t stream);
 
 // ---- maxplus.cu --------------------------------------------------------------
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,

@@ -599,13 +599,19 @@ void launch_gamma_skew(const float* P, const float* alphasS, const float* LNs,
 namespace {
 
 // One CTA per 32x32 (t,u) tile.  Reads LN row-major and gathers E[t,label_u]; writes
-// both skewed.  Column tile 0 also writes ebl[t] = E[t,blank].
+// both skewed.  Column tile 0 also writes ebl[t] = E[t,blank].  With `arcs` it also writes,
+// skewed and in log2 units, the log-probabilities of the two arcs leaving every valid node:
+//   arcs[t,u].x = (E[t,blank]   + P[u,blank]   - LN[t,u]) * log2(e)
+//   arcs[t,u].y = (E[t,label_u] + P[u,label_u] - LN[t,u]) * log2(e),  u < U-1
+// (the caller pre-fills the array with a large negative number: nodes outside the lattice and
+// the label arc of the last position keep it).
 __global__ void __launch_bounds__(256) lattice_prep_kernel(
-    const float* __restrict__ E, const float* __restrict__ LN, float* __restrict__ LNs,
-    float* __restrict__ ELs, float* __restrict__ ebl, const int* __restrict__ labels,
-    const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
-    int blank, int ld, i64 latStride) {
-  __shared__ float tLn[32][33], tEl[32][33];
+    const float* __restrict__ E, const float* __restrict__ P, const float* __restrict__ LN,
+    float* __restrict__ LNs, float* __restrict__ ELs, float* __restrict__ ebl,
+    float2* __restrict__ arcs, const int* __restrict__ labels, const int* __restrict__ inLens,
+    const int* __restrict__ labLens, int maxT, int maxU, int V, int blank, int ld,
+    i64 latStride) {
+  __shared__ float tLn[32][33], tEl[32][33], tEb[32];
   const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
   if (t0 >= T || u0 >= U) return;
@@ -615,6 +621,12 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   const int* lab = labels + (i64)b * (maxU - 1);
   const int u = u0 + lane;
   const int myLab = (u < U - 1) ? lab[u] : blank;
+  float pbl = 0.0f, plab = 0.0f;
+  if (arcs != nullptr && u < U) {
+    const float* p = P + (i64)b * maxU * V;
+    pbl = p[(i64)u * V + blank];
+    plab = p[(i64)u * V + myLab];
+  }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int tt = w * 4 + k, t = t0 + tt;
@@ -626,16 +638,26 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     tLn[tt][lane] = a;
     tEl[tt][lane] = c;
   }
-  if (u0 == 0 && threadIdx.x < 32 && t0 + lane < T)
-    ebl[(i64)b * maxT + t0 + lane] = e[(i64)(t0 + lane) * V + blank];
+  if (threadIdx.x < 32) {
+    const float v = (t0 + lane < T) ? e[(i64)(t0 + lane) * V + blank] : 0.0f;
+    tEb[lane] = v;
+    if (u0 == 0 && t0 + lane < T) ebl[(i64)b * maxT + t0 + lane] = v;
+  }
   __syncthreads();
   // diagonal s = t + u of this tile: s - (t0+u0) in [0, 62]; lane <-> u
   for (int ds = w; ds < 63; ds += 8) {
     const int tt = ds - lane;
     if (tt >= 0 && tt < 32 && t0 + tt < T && u < U) {
       const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
-      LNs[o] = tLn[tt][lane];
-      ELs[o] = tEl[tt][lane];
+      const float lnv = tLn[tt][lane], elv = tEl[tt][lane];
+      LNs[o] = lnv;
+      ELs[o] = elv;
+      if (arcs != nullptr) {
+        float2 f;
+        f.x = ((tEb[tt] + pbl) - lnv) * 1.4426950408889634f;
+        f.y = (u < U - 1) ? ((elv + plab) - lnv) * 1.4426950408889634f : __uint_as_float(kNoArcBits);
+        arcs[o] = f;
+      }
     }
   }
 }
@@ -680,14 +702,18 @@ __global__ void __launch_bounds__(256) lattice_unskew_kernel(
 
 }  // namespace
 
-void launch_lattice_prep(const float* E, const float* LN, float* LNs, float* ELs, float* ebl,
-                         const int* labels, const int* inLens, const int* labLens, SkewGeom g,
-                         Dims d, cudaStream_t stream) {
+void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
+                         float* ELs, float* ebl, float2* arcs, const int* labels,
+                         const int* inLens, const int* labLens, SkewGeom g, Dims d,
+                         cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  if (arcs != nullptr)
+    TB200_CUDA_CHECK(cudaMemsetAsync(arcs, kNoArcByte, sizeof(float2) * (size_t)d.B * g.stride, stream));
   dim3 grid(div_up(d.maxU, 32), div_up(d.maxT, 32), d.B);
   ScopedKernel sk("lattice_prep", stream);
-  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, LN, LNs, ELs, ebl, labels, inLens, labLens,
-                                                d.maxT, d.maxU, d.V, d.blank, g.ld, g.stride);
+  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, P, LN, LNs, ELs, ebl, arcs, labels, inLens,
+                                                labLens, d.maxT, d.maxU, d.V, d.blank, g.ld,
+                                                g.stride);
   TB200_CHECK_LAUNCH();
 }
 
