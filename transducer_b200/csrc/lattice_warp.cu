@@ -1,9 +1,9 @@
 // Lattice sweeps for label axes of at most 128 positions: the recursion runs in ONE warp.
 //
 // The wavefront kernels of lattice.cu spend a block barrier and a shared-memory exchange on
-// every anti-diagonal.  Here lane l of a single warp owns the label positions u = l + 32 r;
-// all nodes of a diagonal are independent, the value that crosses from u-1 (or u+1) arrives
-// by one warp shuffle per r, and nothing else sits on the dependent chain:
+// every anti-diagonal.  Here lane l of a single warp owns the label positions u = 4l .. 4l+3;
+// all nodes of a diagonal are independent, the one value per lane that crosses from the
+// neighbouring lane arrives by a warp shuffle, and nothing else sits on the dependent chain:
 //   * the arc log-probabilities of every node were combined once by lattice_prep_kernel into
 //     the skewed array arcs[d][u] = (blank arc, label arc) in log2 units, a large negative
 //     finite number where the arc or the node does not exist -- so the recursion needs no
@@ -61,7 +61,6 @@ __device__ __forceinline__ void finish_cost_w(float* costs, int b, float cost, i
 // stored in log2 units too: the reverse sweep must form a(t,u) + arc with the very same
 // rounding as here, or the occupancies stop being a conserved flow (the rounding of an alpha
 // of magnitude 1e4 is 1e-3, and such errors would compound along the 2000 steps of a path).
-template <int NR>
 __global__ void __launch_bounds__(32) alpha_warp_kernel(
     const float2* __restrict__ arcs, float* __restrict__ costs, float* __restrict__ alphas, int ld,
     i64 latStride, int nDiag, const int* __restrict__ inLens, const int* __restrict__ labLens,
@@ -101,9 +100,14 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 
   // large negative and finite: the identity of the recursion without -inf arithmetic
   const float kNone = __uint_as_float(kNoArcBits);
-  float stayIn[NR], stepOut[NR];
+  // Lane l owns the label positions u = 4l + r, r = 0..3: the value crossing from u-1 is the
+  // lane's own for r > 0 and comes from lane l-1 by ONE shuffle per diagonal for r = 0; the
+  // four arc pairs and the four alphas of a lane are contiguous (two 16-byte loads, one store).
+  const int u0 = 4 * lane;
+  const bool act = u0 < ld;  // rows are ld <= 128 wide
+  float stayIn[4], stepOut[4];
 #pragma unroll
-  for (int r = 0; r < NR; ++r) stayIn[r] = stepOut[r] = kNone;
+  for (int r = 0; r < 4; ++r) stayIn[r] = stepOut[r] = kNone;
   if (lane == 0) stayIn[0] = 0.0f;  // alpha(0,0) = 0
   float cost = 0.0f;
   bool owner = false, ok = true;
@@ -125,31 +129,35 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 #pragma unroll 2
     for (int dd = 0; dd < nd; ++dd) {
       const int d = k * kDiag + dd;
-      float2 f[NR];
-      float rot[NR], left[NR], m[NR], e[NR], a[NR];
+      float4 f01 = make_float4(kNone, kNone, kNone, kNone), f23 = f01;
+      if (act) {
+        const float4* src = reinterpret_cast<const float4*>(blk + dd * ld + u0);
+        f01 = src[0];
+        f23 = src[1];
+      }
+      const float fx[4] = {f01.x, f01.z, f23.x, f23.z}, fy[4] = {f01.y, f01.w, f23.y, f23.w};
+      const float up = __shfl_up_sync(0xffffffffu, stepOut[3], 1);
+      float left[4], m[4], e[4], a[4];
+      left[0] = lane ? up : kNone;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) f[r] = blk[dd * ld + lane + 32 * r];
+      for (int r = 1; r < 4; ++r) left[r] = stepOut[r - 1];
 #pragma unroll
-      for (int r = 0; r < NR; ++r) rot[r] = __shfl_sync(0xffffffffu, stepOut[r], (lane + 31) & 31);
-#pragma unroll
-      for (int r = 0; r < NR; ++r) left[r] = lane ? rot[r] : (r ? rot[r ? r - 1 : 0] : kNone);
-#pragma unroll
-      for (int r = 0; r < NR; ++r) {
+      for (int r = 0; r < 4; ++r) {
         m[r] = fmaxf(left[r], stayIn[r]);
         e[r] = ex2_approx(-fabsf(left[r] - stayIn[r]));
       }
 #pragma unroll
-      for (int r = 0; r < NR; ++r) a[r] = m[r] + lg2_approx(1.0f + e[r]);
+      for (int r = 0; r < 4; ++r) a[r] = m[r] + lg2_approx(1.0f + e[r]);
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        stayIn[r] = a[r] + f[r].x;
-        stepOut[r] = a[r] + f[r].y;
-        al[d * ld + lane + 32 * r] = a[r];
+      for (int r = 0; r < 4; ++r) {
+        stayIn[r] = a[r] + fx[r];
+        stepOut[r] = a[r] + fy[r];
       }
+      if (act) *reinterpret_cast<float4*>(al + d * ld + u0) = make_float4(a[0], a[1], a[2], a[3]);
       if (d == S - 1) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
-          if (lane + 32 * r == U - 1) {
+        for (int r = 0; r < 4; ++r)
+          if (u0 + r == U - 1) {
             cost = -stayIn[r] * kLn2F;
             owner = true;
           }
@@ -181,15 +189,17 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 //   kernel, so FB and FL of the arcs entering a node add up to 1 to within the error of ex2/lg2)
 //   g(t,u) = stay + step,            g(T-1,U-1) = 1 (the terminating blank, booked as stay)
 // Warp 0 runs the recursion on (FB, FL) pairs staged in shared memory and hands (stay, step)
-// back the same way.  Warps 1..4 (thread <-> label position u): one thread issues the bulk
+// back the same way.  The helper warps (kHelperGroups groups of four, thread <-> label position
+// u, the diagonals of a block dealt round-robin to the groups): one thread issues the bulk
 // copies of the arc terms and the alphas, kRing-1 blocks ahead; all of them turn the block
 // after the current one into (FB, FL), write the (stay, step) of the block before it to the
 // skewed lattices stayS / stepS, and accumulate per label position sum_t stay -> pBlank[u],
-// sum_t step -> pLabel[u] in a fixed order.
+// sum_t step -> pLabel[u] in a fixed order (per group, the groups' partial sums added in
+// group order at the end).
 // Block k holds the diagonals dTop(k) = S-1-16k down to dLo(k) = max(dTop-15, 0).
-constexpr int kGammaThreads = 160;
+constexpr int kHelperGroups = 3;  // helper group j takes the diagonals dd = j (mod 3) of a block
+constexpr int kGammaThreads = 32 + 128 * kHelperGroups;
 
-template <int NR>
 __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     const float2* __restrict__ arcs, const float* __restrict__ alphas, int ld, i64 latStride,
     const int* __restrict__ inLens, const int* __restrict__ labLens, float* __restrict__ stayS,
@@ -202,6 +212,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   float2 (*G)[kDiag][128] = F + 2;
   __shared__ uint64_t bar[kRing];
   __shared__ int abortFlag;
+  __shared__ float sAcc[kHelperGroups][2][128];
   const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
   const bool empty = (T <= 0 || U <= 0);
@@ -234,18 +245,23 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
       bulk_load_1d(dst + arcBytes, al + (size_t)dLo * ld, b2, &bar[k % kRing]);
     }
   };
-  const int hu = tid - 32;  // helper threads: label position
+  const int hu = (tid - 32) & 127;   // helper threads: label position
+  const int hg = (tid - 32) >> 7;    //                 group
   float accB = 0.0f, accL = 0.0f;
   auto stage = [&](int k) -> bool {  // helpers: (FB, FL) of block k -> F[k & 1]
     bool ok = mbar_wait(&bar[k % kRing], (k / kRing) & 1, &abortFlag, status, kStatusTimeoutTma);
     ok = __all_sync(0xffffffffu, ok);
-    if (!ok || hu >= ld) return ok;
+    if (!ok) return ok;
     const int dTop = S - 1 - k * kDiag, dLo = max(dTop - (kDiag - 1), 0), nd = dTop - dLo + 1;
+    if (hu >= ld) {  // beyond the row: no node
+      for (int dd = hg; dd < nd; dd += kHelperGroups) F[k & 1][dd][hu] = make_float2(0.0f, 0.0f);
+      return ok;
+    }
     const uint8_t* src = smemG + (size_t)(k % kRing) * slotBytes;
     const float2* tb = reinterpret_cast<const float2*>(src);
     const float* aa = reinterpret_cast<const float*>(src + arcBytes);
-#pragma unroll 4
-    for (int dd = 0; dd < nd; ++dd) {
+#pragma unroll 3
+    for (int dd = hg; dd < nd; dd += kHelperGroups) {
       const int row = dTop - dd - dLo, t = dTop - dd - hu;
       const float2 arc = tb[row * ld + hu];
       const float a = aa[row * ld + hu], adn = aa[(row + 1) * ld + hu];
@@ -262,8 +278,8 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   auto post = [&](int k) {  // helpers: (stay, step) of block k -> global, running sums
     if (hu >= U) return;
     const int dTop = S - 1 - k * kDiag, nd = min(kDiag, dTop + 1);
-#pragma unroll 4
-    for (int dd = 0; dd < nd; ++dd) {
+#pragma unroll 3
+    for (int dd = hg; dd < nd; dd += kHelperGroups) {
       const int d = dTop - dd, t = d - hu;
       if (t >= 0 && t < T) {
         const float2 g = G[k & 1][dd][hu];
@@ -281,9 +297,12 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   if (warp > 0) stage(0);
   __syncthreads();
 
-  float g[NR];
+  // recursion warp: lane l owns u = 4l + r; the value crossing from u+1 is the lane's own
+  // for r < 3 and comes from lane l+1 by one shuffle per diagonal for r = 3
+  const int u0 = 4 * lane;
+  float g[4];
 #pragma unroll
-  for (int r = 0; r < NR; ++r) g[r] = (lane + 32 * r == U - 1) ? 1.0f : 0.0f;
+  for (int r = 0; r < 4; ++r) g[r] = (u0 + r == U - 1) ? 1.0f : 0.0f;
 
   bool ok = true;
   for (int k = 0; k < nBlocks && ok; ++k) {
@@ -298,21 +317,22 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
       const int nd = min(kDiag, S - k * kDiag);
 #pragma unroll 4
       for (int dd = 0; dd < nd; ++dd) {
-        float2 f[NR], o[NR];
-        float rot[NR];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) f[r] = F[k & 1][dd][lane + 32 * r];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) rot[r] = __shfl_sync(0xffffffffu, g[r], (lane + 1) & 31);
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const float right = (lane < 31) ? rot[r] : (r < NR - 1 ? rot[r < NR - 1 ? r + 1 : r] : 0.0f);
-          o[r].x = g[r] * f[r].x;
-          o[r].y = right * f[r].y;
-          g[r] = o[r].x + o[r].y;
-        }
-#pragma unroll
-        for (int r = 0; r < NR; ++r) G[k & 1][dd][lane + 32 * r] = o[r];
+        const float4* src = reinterpret_cast<const float4*>(&F[k & 1][dd][u0]);
+        const float4 f01 = src[0], f23 = src[1];
+        const float dn = __shfl_down_sync(0xffffffffu, g[0], 1);
+        const float right3 = (lane < 31) ? dn : 0.0f;
+        float4 o01, o23;
+        o01.x = g[0] * f01.x;  o01.y = g[1] * f01.y;       // u0:   stay, step
+        o01.z = g[1] * f01.z;  o01.w = g[2] * f01.w;       // u0+1
+        o23.x = g[2] * f23.x;  o23.y = g[3] * f23.y;       // u0+2
+        o23.z = g[3] * f23.z;  o23.w = right3 * f23.w;     // u0+3
+        g[0] = o01.x + o01.y;
+        g[1] = o01.z + o01.w;
+        g[2] = o23.x + o23.y;
+        g[3] = o23.z + o23.w;
+        float4* dst = reinterpret_cast<float4*>(&G[k & 1][dd][u0]);
+        dst[0] = o01;
+        dst[1] = o23;
       }
     }
     __syncthreads();
@@ -320,11 +340,20 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   }
   if (warp > 0) {
     if (ok) post(nBlocks - 1);
-    if (hu < U) {
-      const float bad = __int_as_float(0x7fc00000);  // a copy never landed: visible in the result
-      pBlank[(i64)b * maxU + hu] = ok ? accB : bad;
-      pLabel[(i64)b * maxU + hu] = ok ? ((hu < U - 1) ? accL : 0.0f) : bad;
+    sAcc[hg][0][hu] = accB;
+    sAcc[hg][1][hu] = accL;
+  }
+  __syncthreads();
+  if (warp > 0 && hg == 0 && hu < U) {
+    float sb = 0.0f, sl = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kHelperGroups; ++j) {
+      sb += sAcc[j][0][hu];
+      sl += sAcc[j][1][hu];
     }
+    const float bad = __int_as_float(0x7fc00000);  // a copy never landed: visible in the result
+    pBlank[(i64)b * maxU + hu] = ok ? sb : bad;
+    pLabel[(i64)b * maxU + hu] = ok ? ((hu < U - 1) ? sl : 0.0f) : bad;
   }
   if (!ok && tid == 32) {  // give the copies still in flight a bounded time to land
     for (int j = max(0, min(issuedN, nBlocks) - kRing); j < min(issuedN, nBlocks); ++j) {
@@ -351,20 +380,10 @@ void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, SkewGeo
   if (d.B <= 0) return;
   const int smem = kRing * kDiag * g.ld * 8;
   ScopedKernel sk("alpha_warp", stream);
-#define CALL(NR)                                                                                \
-  do {                                                                                          \
-    allow_dyn_smem(alpha_warp_kernel<NR>, smem);                                                \
-    alpha_warp_kernel<NR><<<d.B, 32, smem, stream>>>(arcs, costs, alphasS, g.ld, g.stride,      \
-                                                     g.nDiag, inLens, labLens, d.B, d.maxT,     \
-                                                     d.maxU, lossSum, ticket, status);          \
-  } while (0)
-  switch (g.ld / 32) {
-    case 1: CALL(1); break;
-    case 2: CALL(2); break;
-    case 3: CALL(3); break;
-    default: CALL(4); break;
-  }
-#undef CALL
+  allow_dyn_smem(alpha_warp_kernel, smem);
+  alpha_warp_kernel<<<d.B, 32, smem, stream>>>(arcs, costs, alphasS, g.ld, g.stride, g.nDiag,
+                                               inLens, labLens, d.B, d.maxT, d.maxU, lossSum,
+                                               ticket, status);
   TB200_CHECK_LAUNCH();
 }
 
@@ -375,20 +394,10 @@ void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, con
   const int slotBytes = kDiag * g.ld * 8 + (kDiag + 2) * g.ld * 4;
   const int smem = kRing * slotBytes + 4 * kDiag * 128 * (int)sizeof(float2);
   ScopedKernel sk("gamma_warp", stream);
-#define CALL(NR)                                                                               \
-  do {                                                                                         \
-    allow_dyn_smem(gamma_warp_kernel<NR>, smem);                                               \
-    gamma_warp_kernel<NR><<<d.B, kGammaThreads, smem, stream>>>(                               \
-        arcs, alphasS, g.ld, g.stride, inLens, labLens, stayS, stepS, pBlank, pLabel, d.maxT,  \
-        d.maxU, status);                                                                       \
-  } while (0)
-  switch (g.ld / 32) {
-    case 1: CALL(1); break;
-    case 2: CALL(2); break;
-    case 3: CALL(3); break;
-    default: CALL(4); break;
-  }
-#undef CALL
+  allow_dyn_smem(gamma_warp_kernel, smem);
+  gamma_warp_kernel<<<d.B, kGammaThreads, smem, stream>>>(arcs, alphasS, g.ld, g.stride, inLens,
+                                                          labLens, stayS, stepS, pBlank, pLabel,
+                                                          d.maxT, d.maxU, status);
   TB200_CHECK_LAUNCH();
 }
 
