@@ -145,7 +145,8 @@ void need(size_t have, size_t want, const void* ws) {
 // Log-normalisers plus the row shifts.  With the exact path rowRef is the true row
 // maximum of E.
 void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
-                    const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws) {
+                    const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws,
+                    bool fixup = true) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
   const bool can = lognorm_umma_supported(E, P, d);
@@ -157,7 +158,8 @@ void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
     // the kernel needs somewhere to put the row shifts even if the caller does not want them
     float* mp = maxP ? maxP : ws.maxPScratch;
     if (!rowRef) throw std::invalid_argument("rowRef must not be null");
-    launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split, ws.status, g_stream);
+    launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split, ws.status, fixup,
+                        g_stream);
     return;
   }
   launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
@@ -326,8 +328,9 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
     ForwardWs fw(c, d);
     LogNormWs ws(c, d);
     const SkewGeom g = skew_geom(d);
-    log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws);
-    launch_lattice_prep(E, P, fw.LN, st.LNs, st.ELs, st.ebl, st.arcs, labels, inLens, labLens, g, d,
+    // (nodes the tensor-core log-normaliser could not represent are recomputed by the re-layout)
+    log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws, /*fixup=*/false);
+    launch_lattice_prep(E, P, fw.LN, st.LNs, st.arcs ? nullptr : st.ELs, st.ebl, st.arcs, labels, inLens, labLens, g, d,
                         g_stream);
     if (lossSum) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.ticket, 0, sizeof(unsigned), g_stream));

@@ -48,7 +48,9 @@ SkewGeom skew_geom(Dims d);
 constexpr unsigned kNoArcBits = 0xF0F0F0F0u;
 constexpr int kNoArcByte = 0xF0;
 
-// LN (row-major) -> LNs (skewed); ELs[t,u] = E[t,label_u] (skewed); ebl[b,t] = E[t,blank].
+// LN (row-major) -> LNs (skewed); ELs[t,u] = E[t,label_u] (skewed, skipped if null);
+// ebl[b,t] = E[t,blank].  NaN entries of LN (nodes the tensor-core log-normaliser marked)
+// are recomputed here with the exact fp32 logsumexp.
 // If arcs is not null: arcs[t,u] (skewed, [B,nDiag,ld] float2) = log2-unit log-probabilities of
 // the blank arc and the label arc leaving node (t,u), kNoArcBits where there is none.
 void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
@@ -107,9 +109,11 @@ void launch_exp_rows(const float* P, float* expP, float* maxP, const int* labLen
 // caller): [0] first device-side error code (0 = none), [1] nodes recomputed exactly.
 bool lognorm_umma_supported(const float* E, const float* P, Dims d);
 size_t lognorm_umma_workspace_floats(Dims d);
+// Nodes whose factored sum left the fp32 range come out of the kernel as NaN; with `fixup` a
+// second kernel recomputes them exactly, without it the caller must (lattice_prep does).
 void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
-                         int* status, cudaStream_t stream);
+                         int* status, bool fixup, cudaStream_t stream);
 
 // ---- grads_umma.cu --------------------------------------------------------------
 // Tensor-core gradients: one pass over E produces egrads and pgrads.  Usable when

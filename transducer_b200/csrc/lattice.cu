@@ -635,6 +635,23 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
       a = ln[(i64)t * maxU + u];
       c = e[(i64)t * V + myLab];
     }
+    // marked by the tensor-core log-normaliser (its factored sum left the fp32 range):
+    // exact logsumexp by the whole warp
+    unsigned todo = __ballot_sync(0xffffffffu, a != a);
+    while (todo) {
+      const int src = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const float* er = e + (i64)t * V;
+      const float* pr = P + ((i64)b * maxU + u0 + src) * V;
+      float m = neg_inf();
+      for (int v = lane; v < V; v += 32) m = fmaxf(m, er[v] + pr[v]);
+      m = warp_max(m);
+      float s = 0.0f;
+      if (m != neg_inf() && m != pos_inf())
+        for (int v = lane; v < V; v += 32) s += expf((er[v] + pr[v]) - m);
+      s = warp_sum(s);
+      if (lane == src) a = logf(s) + m;
+    }
     tLn[tt][lane] = a;
     tEl[tt][lane] = c;
   }
@@ -651,7 +668,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
       const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
       const float lnv = tLn[tt][lane], elv = tEl[tt][lane];
       LNs[o] = lnv;
-      ELs[o] = elv;
+      if (ELs != nullptr) ELs[o] = elv;
       if (arcs != nullptr) {
         float2 f;
         f.x = ((tEb[tt] + pbl) - lnv) * 1.4426950408889634f;

@@ -122,29 +122,42 @@ __global__ void __launch_bounds__(256) expp_split_kernel(
   const int U = min(labLens[b] + 1, maxU);
   float* hi = bHi + ((i64)b * nPad + u) * kPad;
   float* lo = bLo + ((i64)b * nPad + u) * kPad;
+  // rows are read and written as float4 (the caller guarantees V % 4 == 0 and 16-byte aligned
+  // P; kPad is a multiple of 32)
+  float4* hi4 = reinterpret_cast<float4*>(hi);
+  float4* lo4 = reinterpret_cast<float4*>(lo);
   if (u >= U) {
-    for (int v = threadIdx.x; v < kPad; v += blockDim.x) { hi[v] = 0.0f; lo[v] = 0.0f; }
+    const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int v = threadIdx.x; v < kPad / 4; v += blockDim.x) { hi4[v] = z; lo4[v] = z; }
     if (u < maxU && threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = 0.0f;
     return;
   }
   const float* p = P + ((i64)b * maxU + u) * V;
+  const float4* p4 = reinterpret_cast<const float4*>(p);
   float m = neg_inf();
-  for (int v = threadIdx.x; v < V; v += blockDim.x) m = fmaxf(m, p[v]);
+  for (int v = threadIdx.x; v < V / 4; v += blockDim.x) {
+    const float4 x = p4[v];
+    m = fmaxf(fmaxf(m, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
+  }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
   m = red[0];
 #pragma unroll
   for (int k = 1; k < 8; ++k) m = fmaxf(m, red[k]);
-  for (int v = threadIdx.x; v < kPad; v += blockDim.x) {
-    float h = 0.0f, l = 0.0f;
-    if (v < V) {
-      const float x = expf(p[v] - m);
-      h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-      l = tf32_round(x - h);
+  for (int v = threadIdx.x; v < kPad / 4; v += blockDim.x) {
+    float xs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, h[4], l[4];
+    if (4 * v < V) {
+      const float4 x = p4[v];
+      xs[0] = expf(x.x - m); xs[1] = expf(x.y - m); xs[2] = expf(x.z - m); xs[3] = expf(x.w - m);
     }
-    hi[v] = h;
-    lo[v] = l;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      h[k] = __uint_as_float(__float_as_uint(xs[k]) & 0xffffe000u);
+      l[k] = tf32_round(xs[k] - h[k]);
+    }
+    hi4[v] = make_float4(h[0], h[1], h[2], h[3]);
+    lo4[v] = make_float4(l[0], l[1], l[2], l[3]);
   }
   if (threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = m;
 }
@@ -495,9 +508,9 @@ int pow2_at_least(int x) {
 }  // namespace
 
 bool lognorm_umma_supported(const float* E, const float* P, Dims d) {
-  (void)P;
   return d.V % 4 == 0 && d.V >= 32 && d.maxU >= 1 && d.maxU <= 256 &&
-         (reinterpret_cast<uintptr_t>(E) & 15) == 0 && d.B <= 65535;
+         (reinterpret_cast<uintptr_t>(E) & 15) == 0 && (reinterpret_cast<uintptr_t>(P) & 15) == 0 &&
+         d.B <= 65535;
 }
 
 size_t lognorm_umma_workspace_floats(Dims d) {
@@ -508,7 +521,7 @@ size_t lognorm_umma_workspace_floats(Dims d) {
 
 void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
-                         int* status, cudaStream_t stream) {
+                         int* status, bool fixup, cudaStream_t stream) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   const int nPad = (int)round_up64(d.maxU, 16);
   const int kPad = (int)round_up64(d.V, kChunkK);
@@ -563,7 +576,7 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
     }
   }
   TB200_CHECK_LAUNCH();
-  {
+  if (fixup) {
     ScopedKernel sk("lognorm_fixup", stream);
     lognorm_fixup_kernel<<<148 * 2, 256, 0, stream>>>(E, P, LN, inLens, labLens, d.B, d.maxT,
                                                       d.maxU, d.V);
