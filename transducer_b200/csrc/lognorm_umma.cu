@@ -181,9 +181,8 @@ struct LnParams {
 // So an accumulator only ever sees kGroup chunks (12*kGroup steps); the drain warps then
 // add it, round-to-nearest, into fp32 registers and the MMA starts a fresh accumulator.
 constexpr int kGroup = 2;
-// NTW   transform warpgroups (1 or 2): with 2, each thread handles 16 of the 32 columns of a
-//       chunk row, which puts two transform warps on every SM sub-partition and hides the
-//       latency of the exp / TMEM-store chain.
+// NTW   transform warpgroups (1 or 2): with 2, the groups take alternate chunks, so that one
+//       group's wait for its tile and for its TMEM stores overlaps the other's exponentials.
 // NDRAIN drain warpgroups, each owning DCOLS accumulator columns (fp32 sums in registers).
 template <int NTW, int NDRAIN, int DCOLS>
 __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_umma_kernel(
@@ -193,7 +192,6 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
   constexpr int kThreads = (kMmaWarp + 2) * 32;  // two MMA-issuing warps
   constexpr int kDrainCols = DCOLS;
-  constexpr int kColsPerThread = kChunkK / NTW;  // chunk columns one transform thread handles
   const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
   if (t0 >= T || U <= 0) return;  // before any allocation or barrier
@@ -217,7 +215,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&barFull[s], 1);
-      mbar_init(&barReady[s], 4 * NTW);
+      mbar_init(&barReady[s], 4);   // the one transform group that owns the chunk
       mbar_init(&barDone[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -312,13 +310,17 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     }
   } else if (warp < kDrainWarp0) {
     // ---------------- operand transform (thread = frame = TMEM lane) ----------------
-    const int q = warp & 3, hcol = warp >> 2;   // lane quarter, column half of the chunk
+    const int q = warp & 3, grp = warp >> 2;    // lane quarter, transform group
     const int r = q * 32 + lane;                // frame within the tile, 0..127
     const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
-    constexpr int NC = kColsPerThread;
     float ref = 0.0f;
     bool ok = true;
-    for (int c = 0; c < nChunks && ok; ++c) {
+    if (grp > 0) {  // the frame's shift is found by group 0 in chunk 0
+      ok = mbar_wait(&barRef, 0, abortp, p.status, kStatusTimeoutOperand);
+      ok = __all_sync(0xffffffffu, ok);
+      ref = sRef[r];
+    }
+    for (int c = grp; c < nChunks && ok; c += NTW) {
       const int s = c % S;
       ok = mbar_wait(&barFull[s], (c / S) & 1, abortp, p.status, kStatusTimeoutTma);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
@@ -339,50 +341,48 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         // a -inf/NaN prefix would poison every term; fall back to 0 and let the
         // range check route the row to the exact path if needed
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
-        if (hcol == 0) {
-          sRef[r] = ref;
-          if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
-        }
-      }
-      float x[NC];
-#pragma unroll
-      for (int j = 0; j < NC / 4; ++j) {
-        const int jj = hcol * (NC / 4) + j;  // 16-byte piece of the 128-byte row
-        const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
-        x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
+        sRef[r] = ref;
+        if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
       }
       const float nref = -ref * kLog2e;
-      const int kLeftMine = kLeft - hcol * NC;
-      uint32_t hi[NC], lo[NC];
-      if (kLeftMine >= NC) {
+      const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-          const float e = ex2_approx(fmaf(x[j], kLog2e, nref));
-          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = hbits;
-          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
+      for (int half = 0; half < 2; ++half) {  // 16 columns at a time (registers)
+        float x[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int jj = half * 4 + j;  // 16-byte piece of the 128-byte row
+          const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
+          x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
         }
-      } else {  // last chunk of a vocabulary that is not a multiple of 32
+        const int kLeftMine = kLeft - half * 16;
+        uint32_t hi[16], lo[16];
+        if (kLeftMine >= 16) {
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-          const float e = (j < kLeftMine) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
-          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = hbits;
-          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
+          for (int j = 0; j < 16; ++j) {
+            const float e = ex2_approx(fmaf(x[j], kLog2e, nref));
+            const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
+            hi[j] = hbits;
+            lo[j] = __float_as_uint(e - __uint_as_float(hbits));
+          }
+        } else {  // last chunk of a vocabulary that is not a multiple of 32
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float e = (j < kLeftMine) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
+            const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
+            hi[j] = hbits;
+            lo[j] = __float_as_uint(e - __uint_as_float(hbits));
+          }
         }
-      }
-      const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64 + hcol * NC);
-#pragma unroll
-      for (int j = 0; j < NC; j += 16) {
-        tmem_st16(dst + j, reinterpret_cast<const uint32_t(&)[16]>(hi[j]));
-        tmem_st16(dst + 32 + j, reinterpret_cast<const uint32_t(&)[16]>(lo[j]));
+        tmem_st16(dst + half * 16, hi);
+        tmem_st16(dst + 32 + half * 16, lo);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&barReady[s]);
-        if (c == 0 && hcol == 0) mbar_arrive(&barRef);
+        if (c == 0) mbar_arrive(&barRef);
       }
     }
   } else {
@@ -550,8 +550,12 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   // each).  Two accumulators let the MMA run while the previous group is drained; a wide
   // label axis leaves room for only one.  One CTA per SM (the kernel asks for > 114 KB).
   const int maxStagesSmem = (int)((220 * 1024 - 2048) / stageBytes);
+  // (With two accumulators the two MMA-issuing threads take the chunks in groups of two, so a
+  // stage has a single consumer, in program order, only when there are exactly four stages;
+  // with fewer, a fast issuer could mistake an older phase of a stage's barrier for its own.)
   int nAcc = 2;
   int stages = std::min(4, std::min(maxStagesSmem, (512 - 2 * nPad) / 64));
+  if (stages < 4) stages = 0;  // fall through to the single-accumulator, single-issuer form
   if (stages < 2) {
     nAcc = 1;
     stages = std::min(4, std::min(maxStagesSmem, (512 - nPad) / 64));
@@ -565,7 +569,9 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   dim3 grid(div_up(d.maxT, kTileM), d.B);
   {
     ScopedKernel sk("lognorm_umma", stream);
-    if (nPad <= 128) {
+    // the two-group transform and the two MMA issuers rely on exactly four stages (each stage
+    // then has one consumer of each kind, in program order)
+    if (nPad <= 128 && stages == 4 && nAcc == 2) {
       auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
