@@ -240,8 +240,6 @@ def main():
 
     # ---- timed region: K steps, device-timed, max over ranks -----------------------
     launches0 = _lib.lib.tb200_launch_count()
-    _lib.lib.tb200_profile_reset()
-    _lib.lib.tb200_profile_enable(1)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
@@ -250,9 +248,21 @@ def main():
             step()
         ev1.record()
         barrier()
-    _lib.lib.tb200_profile_enable(0)
-    launches = _lib.lib.tb200_launch_count() - launches0
-    ms_total = ev0.elapsed_time(ev1)
+        launches = _lib.lib.tb200_launch_count() - launches0
+        ms_total = ev0.elapsed_time(ev1)
+        # Same K steps once more with every kernel bracketed by CUDA events on its stream (the
+        # library's own accounting): per-kernel durations for the roofline.  Kept out of the
+        # headline region because the event records themselves cost a few microseconds each.
+        _lib.lib.tb200_profile_reset()
+        _lib.lib.tb200_profile_enable(1)
+        evp0, evp1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        evp0.record()
+        for _ in range(args.steps):
+            step()
+        evp1.record()
+        barrier()
+        _lib.lib.tb200_profile_enable(0)
+        ms_profiled_step = evp0.elapsed_time(evp1) / args.steps
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if distributed:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -285,6 +295,7 @@ def main():
              "hbm_floor_ms": alg["total"] / (peaks["hbm_gbs"] * 1e9) * 1e3,
              "frac_of_hbm_roofline": alg["total"] / (peaks["hbm_gbs"] * 1e9) / (ms_step * 1e-3),
              "kernel_ms_per_step": total_kernel_ms,
+             "ms_per_step_with_kernel_events": ms_profiled_step,
              "kernels": {k: round(v["ms_per_launch"] * v["launches"] / args.steps, 4)
                          for k, v in per_kernel.items()}}
 

@@ -105,6 +105,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kTileM = 128;
+constexpr int kMaxSMs = 256;                      // slots for the partial sums of split tiles
 constexpr int kChunkK = 32;                       // floats per K-chunk = one 128-byte swizzle row
 constexpr int kRawBytes = kTileM * kChunkK * 4;   // 16 KB
 constexpr float kLog2e = 1.4426950408889634f;
@@ -173,6 +174,10 @@ struct LnParams {
   const int* labLens;
   int* status;       // [0] first error code, [1] number of nodes handed to the fix-up
   int maxT, maxU, V, nPad, stages, nAcc, tmemCols;
+  // last-wave splitting (see lognorm_umma_kernel)
+  int B, tilesX, nSM;
+  float* partial;    // [nSM][kTileM][nPad] partial sums of split tiles
+  unsigned* tickets; // [nSM] parts finished per split tile (zero on entry, zero again on exit)
 };
 
 // Chunks per accumulation group.  The tensor core adds into its fp32 accumulator with
@@ -184,6 +189,19 @@ constexpr int kGroup = 2;
 // NTW   transform warpgroups (1 or 2): with 2, the groups take alternate chunks, so that one
 //       group's wait for its tile and for its TMEM stores overlaps the other's exponentials.
 // NDRAIN drain warpgroups, each owning DCOLS accumulator columns (fp32 sums in registers).
+//
+// Work items.  A tile (128 frames of one utterance x the whole vocabulary) takes the same time
+// whatever it holds, and one CTA fits an SM, so n live tiles on nSM SMs cost ceil(n / nSM)
+// rounds: 454 tiles on 148 SMs pay for 592.  The tiles of the last, partly filled round are
+// therefore split along the vocabulary into k = min(8, nSM / rem) parts (rem = n mod nSM):
+// part 0 runs in the tile's own CTA, parts 1..k-1 in `worker` CTAs appended to the grid (the
+// hardware dispatches CTAs in index order, so they start exactly when the last round does).
+// Every part keeps the frame's shift of the whole tile (a part that does not begin at chunk 0
+// first fetches chunk 0 for it and feeds zeros to the tensor core for that chunk), writes its
+// partial sums to `partial`, and the part that finishes last adds the parts in index order.
+// The grid is (tilesX * B + nSM) x 1; lengths are on the device, so every CTA derives the
+// schedule from them itself (B <= 1024; larger batches are not split).
+constexpr int kMaxParts = 8;
 template <int NTW, int NDRAIN, int DCOLS>
 __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
@@ -192,9 +210,75 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
   constexpr int kThreads = (kMmaWarp + 2) * 32;  // two MMA-issuing warps
   constexpr int kDrainCols = DCOLS;
-  const int b = blockIdx.y, t0 = blockIdx.x * kTileM;
+  // ---- which work item is this CTA? (warp 0 scans the lengths; before any allocation) ----
+  __shared__ int sItem[6];  // b, tile, part, parts, split-tile index, valid
+  if (threadIdx.x < 32) {
+    const int lane0 = threadIdx.x;
+    const int nNatural = p.tilesX * p.B;
+    const bool worker = (int)blockIdx.x >= nNatural;
+    const int myB = worker ? -1 : (int)blockIdx.x / p.tilesX, myX = worker ? 0 : (int)blockIdx.x % p.tilesX;
+    auto liveTiles = [&](int bb) {
+      if (bb >= p.B) return 0;
+      const int Tb = min(p.inLens[bb], p.maxT), Ub = min(p.labLens[bb] + 1, p.maxU);
+      return (Tb > 0 && Ub > 0) ? (Tb + kTileM - 1) / kTileM : 0;
+    };
+    int n = 0, before = 0;  // live tiles in all, and in the utterances before mine
+    for (int b0 = 0; b0 < p.B; b0 += 32) {
+      const int v = liveTiles(b0 + lane0);
+      const int tot = __reduce_add_sync(0xffffffffu, v);
+      const int pre = __reduce_add_sync(0xffffffffu, (b0 + lane0 < myB) ? v : 0);
+      n += tot;
+      before += pre;
+    }
+    const int full = (n / p.nSM) * p.nSM, rem = n - full;
+    int k = (rem > 0 && p.B <= 1024) ? min(kMaxParts, p.nSM / rem) : 1;
+    k = min(k, ((p.V + kChunkK - 1) / kChunkK) / 16);  // a part is worth >= 16 chunks
+    if (k < 2) k = 1;
+    int ib = -1, ix = 0, part = 0, parts = 1, split = 0, valid = 0;
+    if (!worker) {
+      if (myX < liveTiles(myB)) {
+        valid = 1; ib = myB; ix = myX;
+        const int r = before + myX;
+        if (k > 1 && r >= full) { parts = k; split = r - full; }
+      }
+    } else if (k > 1) {
+      const int w = (int)blockIdx.x - nNatural;
+      if (w < rem * (k - 1)) {
+        split = w / (k - 1);
+        part = 1 + w % (k - 1);
+        parts = k;
+        // locate the tile of live rank full + split
+        const int target = full + split;
+        int run = 0;
+        for (int b0 = 0; b0 < p.B && !valid; b0 += 32) {
+          const int v = liveTiles(b0 + lane0);
+          int incl = v;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane0 >= o) incl += up;
+          }
+          const int lo = run + incl - v, hi = run + incl;  // my utterance holds ranks [lo, hi)
+          const unsigned hit = __ballot_sync(0xffffffffu, target >= lo && target < hi);
+          if (hit) {
+            const int src = __ffs(hit) - 1;
+            ib = b0 + src;
+            ix = target - __shfl_sync(0xffffffffu, lo, src);
+            valid = 1;
+          }
+          run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+      }
+    }
+    if (lane0 == 0) {
+      sItem[0] = ib; sItem[1] = ix; sItem[2] = part; sItem[3] = parts; sItem[4] = split; sItem[5] = valid;
+    }
+  }
+  __syncthreads();
+  if (!sItem[5]) return;
+  const int b = sItem[0], t0 = sItem[1] * kTileM;
+  const int part = sItem[2], parts = sItem[3], splitIdx = sItem[4];
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
-  if (t0 >= T || U <= 0) return;  // before any allocation or barrier
 
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
@@ -207,9 +291,15 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   __shared__ int abortFlag;
   __shared__ float sMaxP[256];
   __shared__ float sRef[kTileM];
+  __shared__ int sLast;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nChunks = (p.V + kChunkK - 1) / kChunkK;
+  // this part's chunks [cBegin, cEnd); iteration i of the pipeline handles chunk chunkOf(i)
+  const int nChunksAll = (p.V + kChunkK - 1) / kChunkK;
+  const int cBegin = (int)((i64)part * nChunksAll / parts), cEnd = (int)((i64)(part + 1) * nChunksAll / parts);
+  const bool refFirst = part > 0;  // iteration 0 fetches chunk 0 for the frames' shifts only
+  const int nChunks = cEnd - cBegin + (refFirst ? 1 : 0);  // pipeline iterations
+  auto chunkOf = [&](int i) { return refFirst ? (i == 0 ? 0 : cBegin + i - 1) : cBegin + i; };
   const int nGroups = (nChunks + kGroup - 1) / kGroup;
 
   if (threadIdx.x == 0) {
@@ -253,9 +343,10 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
           break;
         uint8_t* st = smem + (size_t)s * stageBytes;
         mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
-        tma_load_3d(st, &tmE, &barFull[s], c * kChunkK, t0, b);
-        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], c * kChunkK, 0, b);
-        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], c * kChunkK, 0, b);
+        const int col = chunkOf(c) * kChunkK;
+        tma_load_3d(st, &tmE, &barFull[s], col, t0, b);
+        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], col, 0, b);
+        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], col, 0, b);
         issued = c + 1;
       }
       if (*abortp) {
@@ -326,7 +417,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
       if (!ok) break;
       const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
-      const int kLeft = p.V - c * kChunkK;  // valid columns in this chunk
+      const int kLeft = p.V - chunkOf(c) * kChunkK;  // valid columns in this chunk
+      const bool refOnly = refFirst && c == 0;           // its terms belong to part 0
       if (c == 0) {
         // the frame's shift: maximum of the first 32 entries of the row
         float m = neg_inf();
@@ -342,7 +434,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         // range check route the row to the exact path if needed
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
         sRef[r] = ref;
-        if (t0 + r < T) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
+        if (t0 + r < T && part == 0) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
       }
       const float nref = -ref * kLog2e;
       const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
@@ -355,7 +447,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
           const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
           x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
         }
-        const int kLeftMine = kLeft - half * 16;
+        const int kLeftMine = refOnly ? 0 : kLeft - half * 16;
         uint32_t hi[16], lo[16];
         if (kLeftMine >= 16) {
 #pragma unroll
@@ -424,6 +516,36 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     }
     if (ok) ok = mbar_wait(&barRef, 0, abortp, p.status, kStatusTimeoutOperand);
     ok = __all_sync(0xffffffffu, ok);
+    if (parts > 1) {
+      // split tile: park the partial sums; the part that finishes last adds all of them in
+      // part order (so the result does not depend on which part that is) and goes on
+      float* mine = p.partial + ((size_t)(splitIdx * parts + part) * kTileM + r) * p.nPad + c0;
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < kDrainCols; ++j)
+          if (c0 + j < c1) mine[j] = sum[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
+      if (warp == kDrainWarp0 && lane == 0) {
+        const unsigned done = atomicAdd(&p.tickets[splitIdx], 1u);
+        sLast = (done == (unsigned)(parts - 1)) ? 1 : 0;
+        if (sLast) p.tickets[splitIdx] = 0u;  // ready for the next launch
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
+      if (!sLast) ok = false;  // nothing more to do here
+      if (ok) {
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
+        for (int z = 0; z < parts; ++z) {
+          const float* src = p.partial + ((size_t)(splitIdx * parts + z) * kTileM + r) * p.nPad + c0;
+#pragma unroll
+          for (int j = 0; j < kDrainCols; ++j)
+            if (c0 + j < c1) sum[j] += __ldcg(src + j);
+        }
+      }
+    }
     if (ok) {
       const int t = t0 + r;
       const float ref = sRef[r];
@@ -516,7 +638,8 @@ bool lognorm_umma_supported(const float* E, const float* P, Dims d) {
 size_t lognorm_umma_workspace_floats(Dims d) {
   const size_t nPad = (size_t)round_up64(d.maxU > 0 ? d.maxU : 1, 16);
   const size_t kPad = (size_t)round_up64(d.V, kChunkK);
-  return 2 * (size_t)d.B * nPad * kPad;
+  // exp(P) hi and lo; partial sums of split tiles (one slot per SM at most); their tickets
+  return 2 * (size_t)d.B * nPad * kPad + (size_t)kMaxSMs * kTileM * nPad + kMaxSMs;
 }
 
 void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
@@ -545,6 +668,15 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   p.LN = LN; p.rowRef = rowRef; p.maxP = maxP; p.inLens = inLens; p.labLens = labLens;
   p.status = status;
   p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.nPad = nPad;
+  int dev = 0, nSM = 0;
+  TB200_CUDA_CHECK(cudaGetDevice(&dev));
+  TB200_CUDA_CHECK(cudaDeviceGetAttribute(&nSM, cudaDevAttrMultiProcessorCount, dev));
+  p.B = d.B;
+  p.tilesX = div_up(d.maxT, kTileM);
+  p.nSM = std::min(nSM, kMaxSMs);
+  p.partial = bLo + (size_t)d.B * nPad * kPad;
+  p.tickets = reinterpret_cast<unsigned*>(p.partial + (size_t)kMaxSMs * kTileM * nPad);
+  TB200_CUDA_CHECK(cudaMemsetAsync(p.tickets, 0, sizeof(unsigned) * kMaxSMs, stream));
   const int stageBytes = kRawBytes + 2 * nPad * kChunkK * 4;
   // Tensor memory (512 columns): accumulators first, then the operand stages (64 columns
   // each).  Two accumulators let the MMA run while the previous group is drained; a wide
@@ -566,7 +698,7 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   p.tmemCols = pow2_at_least(nAcc * nPad + stages * 64);
   size_t smem = (size_t)stages * stageBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  dim3 grid(div_up(d.maxT, kTileM), d.B);
+  dim3 grid((unsigned)(p.tilesX * d.B + p.nSM));  // one CTA per tile + workers for split tiles
   {
     ScopedKernel sk("lognorm_umma", stream);
     // the two-group transform and the two MMA issuers rely on exactly four stages (each stage
