@@ -331,10 +331,13 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the
 # named kernel; see the summaries under profiles/.  Keyed by (workload, kernel).
 NCU_TRAFFIC_BYTES = {
-    ("c3", "grads_umma"): 2547751680 + 2680469760,     # profiles/grads_umma_c3.md
-    ("c3", "lognorm_umma"): 2604874496 + 16799744,     # profiles/lognorm_umma_c3.md
-    ("c3", "alpha_wavefront"): 44124416 + 120832,      # profiles/wavefront_kernels_c3.md
-    ("c3", "gamma_wavefront"): 66929152 + 7387136,
+    ("c3", "grads_umma"): 2450743552 + 2682491136,     # profiles/launch_list_bench_c3.md
+    ("c3", "lognorm_umma"): 2604641792 + 14880512,
+    ("c3", "alpha_warp"): 59774208 + 2307072,          # profiles/lattice_sweeps_c3.md
+    ("c3", "gamma_warp"): 90813184 + 11543040,
+    ("c3", "lattice_prep"): 532794368 + 42867200,
+    ("c3", "expp_split"): 147243264 + 231990016,
+    ("c3", "lattice_unskew_round"): 64985856 + 17259264,
 }
 
 
@@ -351,6 +354,8 @@ def kernel_algorithmic_bytes(w, il, ll):
         "lognorm_umma": 4.0 * V * (sum_t + sum_u) + 4.0 * sum_tu,
         "alpha_wavefront": 3 * 4.0 * sum_tu,
         "gamma_wavefront": 5 * 4.0 * sum_tu,
+        "alpha_warp": 3 * 4.0 * sum_tu,    # arc terms (2 floats) in, alpha out
+        "gamma_warp": 5 * 4.0 * sum_tu,    # arc terms + alpha in, stay + step out
         "egrad_simt": 4.0 * V * sum_t + 4.0 * V * n * w.T + 4.0 * V * sum_u,
         "pgrad_simt": 4.0 * V * sum_t + 4.0 * V * n * (w.U + 1) + 4.0 * V * sum_u,
         "grads_umma": 4.0 * V * (sum_t + sum_u) + 4.0 * V * n * (w.T + w.U + 1) + 4.0 * sum_tu,
