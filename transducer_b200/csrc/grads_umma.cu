@@ -593,7 +593,7 @@ int pow2_cols(int x) {
 }
 
 // Re-layout after the reverse sweep (gamma_warp_kernel), one CTA per 32 frames of one utterance,
-// walking the label axis in 32x32 lattice tiles.  With delta_b the upstream gradient:
+// the (up to four) 32x32 lattice tiles of the label axis side by side.  With delta_b the upstream gradient:
 //   stayS + stepS (skewed) -> W [B,maxT,ldW] = delta_b * g * exp(ref(t) + maxP(u) - LN(t,u)),
 //                   g = stay + step, rounded to TF32 (round-to-nearest; the tensor core would
 //                   otherwise truncate), zero outside the valid lattice.  (The exponent is
@@ -610,71 +610,83 @@ int pow2_cols(int x) {
 // occupancies row-major [B,maxT,maxU] (through emT), the row sums with row length maxT
 // (through ebl), no nref.
 template <bool TC>
-__global__ void __launch_bounds__(256) unskew_round_kernel(
+__global__ void __launch_bounds__(1024) unskew_round_kernel(
     const float* __restrict__ stayS, const float* __restrict__ stepS,
     const float* __restrict__ LNs, const float* __restrict__ rowRef,
     const float* __restrict__ maxP, const float* __restrict__ deltas, float* __restrict__ W,
     float* __restrict__ emT, float* __restrict__ nref, float* __restrict__ ebl,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int ld,
     i64 latStride, int ldW, int ldT) {
-  __shared__ float tW[32][33], tE[32][33], tS[32][33];
+  // 32 warps: 8 per 32-wide block of label positions (ldW <= 128), all four blocks at once
+  extern __shared__ float smemU[];
+  float (*tW)[32][33] = reinterpret_cast<float (*)[32][33]>(smemU);                // [4]
+  float (*tE)[32][33] = tW + 4;
+  float (*tS)[32][33] = tE + 4;
+  __shared__ float sRow[4][32];
   const int b = blockIdx.y, t0 = blockIdx.x * 32;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, w = (threadIdx.x >> 5) & 7, ub = threadIdx.x >> 8;
   const float delta = (TC && deltas) ? deltas[b] : 1.0f;
-  float rowSum[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // frames t0 + 4w + k, complete in every lane
-  for (int u0 = 0; u0 < ldW; u0 += 32) {
-    const int u = u0 + lane;
-    const bool live = t0 < T && u0 < U;
-    if (live) {
-      const float mp = maxP[(i64)b * maxU + min(u, U - 1)];
-      for (int ds = w; ds < 63; ds += 8) {
-        const int tt = ds - lane;
-        if (tt >= 0 && tt < 32) {
-          float a = 0.0f, c = 0.0f, st = 0.0f;
-          const int t = t0 + tt;
-          if (t < T && u < U) {
-            const i64 o = (i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u;
-            st = stayS[o];
-            const float sp = stepS[o];
-            const float sh = fminf((rowRef[(i64)b * maxT + t] + mp) - LNs[o], 80.0f);
-            a = (st + sp) * expf(sh) * delta;
-            c = sp * delta;
-          }
-          tW[tt][lane] = a;
-          tE[tt][lane] = c;
-          tS[tt][lane] = st;
-        }
-      }
-    }
-    __syncthreads();
+  const int u0 = ub * 32, u = u0 + lane;
+  const bool inRange = u0 < ldW;
+  const bool live = inRange && t0 < T && u0 < U;
+  if (live) {
+    const int uc = min(u, U - 1);
+    const float mp = maxP[(i64)b * maxU + uc];
+    // Lane `lane` of local warp w holds the tile's diagonals ds = w + 8i with 0 <= ds - lane < 32:
+    // exactly four of them.  All their loads are issued before the first use (unconditional,
+    // clamped into the lattice).
+    const int i0 = (lane > w) ? (lane - w + 7) >> 3 : 0;
+    float vSt[4], vSp[4], vLn[4], vRef[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int tt = w * 4 + k, t = t0 + tt;
+    for (int j = 0; j < 4; ++j) {
+      const int tt = w + 8 * (i0 + j) - lane;
+      const int tc = min(t0 + tt, T - 1);
+      const i64 o = (i64)b * latStride + (i64)(tc + uc) * ld + uc;
+      vSt[j] = stayS[o];
+      vSp[j] = stepS[o];
+      vLn[j] = LNs[o];
+      vRef[j] = rowRef[(i64)b * maxT + tc];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int tt = w + 8 * (i0 + j) - lane;
+      float a = 0.0f, c = 0.0f, st = 0.0f;
+      if (t0 + tt < T && u < U) {
+        st = vSt[j];
+        const float sh = fminf((vRef[j] + mp) - vLn[j], 80.0f);
+        a = (st + vSp[j]) * expf(sh) * delta;
+        c = vSp[j] * delta;
+      }
+      tW[ub][tt][lane] = a;
+      tE[ub][tt][lane] = c;
+      tS[ub][tt][lane] = st;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int tt = w * 4 + k, t = t0 + tt;
+    if (inRange) {
       if (t < maxT && u < ldW)
-        W[((i64)b * maxT + t) * ldW + u] = live ? (TC ? tf32_round(tW[tt][lane]) : tW[tt][lane]) : 0.0f;
+        W[((i64)b * maxT + t) * ldW + u] = live ? (TC ? tf32_round(tW[ub][tt][lane]) : tW[ub][tt][lane]) : 0.0f;
       if (TC) {  // transposed: lane <-> frame, row <-> label position
         const int uu = u0 + tt, t2 = t0 + lane;
-        if (uu < maxU && t2 < ldT) emT[((i64)b * maxU + uu) * ldT + t2] = live ? tE[lane][tt] : 0.0f;
+        if (uu < maxU && t2 < ldT) emT[((i64)b * maxU + uu) * ldT + t2] = live ? tE[ub][lane][tt] : 0.0f;
       } else if (t < maxT && u < maxU) {
-        emT[((i64)b * maxT + t) * maxU + u] = live ? tE[tt][lane] : 0.0f;
-      }
-      if (live) {
-        float v = tS[tt][lane];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        rowSum[k] += v;
+        emT[((i64)b * maxT + t) * maxU + u] = live ? tE[ub][tt][lane] : 0.0f;
       }
     }
-    __syncthreads();
+    float v = live ? tS[ub][tt][lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) sRow[ub][tt] = v;
   }
-  if (lane < 4) {
-    const int t = t0 + w * 4 + lane;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int t = t0 + lane;
     const bool ok = t < T;
-    float rs = rowSum[0];
-    if (lane == 1) rs = rowSum[1];
-    if (lane == 2) rs = rowSum[2];
-    if (lane == 3) rs = rowSum[3];
+    const float rs = ((sRow[0][lane] + sRow[1][lane]) + sRow[2][lane]) + sRow[3][lane];
     if (TC) {
       if (t < ldT) {
         nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
@@ -761,12 +773,21 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
   const int ldW = grads_umma_ld_w(d), ldT = grads_umma_ld_t(d);
   dim3 grid(div_up(ldT, 32), d.B);
   ScopedKernel sk("lattice_unskew_round", stream);
+  const int smem = 12 * 32 * 33 * (int)sizeof(float);
+  static bool attrSet = false;
+  if (!attrSet) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(unskew_round_kernel<true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(unskew_round_kernel<false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attrSet = true;
+  }
   if (tensorCore)
-    unskew_round_kernel<true><<<grid, 256, 0, stream>>>(stayS, stepS, LNs, rowRef, maxP, deltas, W,
+    unskew_round_kernel<true><<<grid, 1024, smem, stream>>>(stayS, stepS, LNs, rowRef, maxP, deltas, W,
                                                         emT, nref, ebl, inLens, labLens, d.maxT,
                                                         d.maxU, g.ld, g.stride, ldW, ldT);
   else
-    unskew_round_kernel<false><<<grid, 256, 0, stream>>>(stayS, stepS, LNs, rowRef, maxP, nullptr,
+    unskew_round_kernel<false><<<grid, 1024, smem, stream>>>(stayS, stepS, LNs, rowRef, maxP, nullptr,
                                                          W, emT, nullptr, ebl, inLens, labLens,
                                                          d.maxT, d.maxU, g.ld, g.stride, ldW, ldT);
   TB200_CHECK_LAUNCH();

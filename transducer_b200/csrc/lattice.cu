@@ -627,13 +627,26 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     pbl = p[(i64)u * V + blank];
     plab = p[(i64)u * V + myLab];
   }
+  // all loads first (unconditional, clamped into the lattice): the gathers of the four rows
+  // are in flight together
+  float va[4], vc[4];
+  {
+    const int uc = min(u, U - 1);
+    const int labc = (uc < U - 1) ? lab[uc] : blank;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int tc = min(t0 + w * 4 + k, T - 1);
+      va[k] = ln[(i64)tc * maxU + uc];
+      vc[k] = e[(i64)tc * V + labc];
+    }
+  }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int tt = w * 4 + k, t = t0 + tt;
     float a = 0.0f, c = 0.0f;
     if (t < T && u < U) {
-      a = ln[(i64)t * maxU + u];
-      c = e[(i64)t * V + myLab];
+      a = va[k];
+      c = vc[k];
     }
     // marked by the tensor-core log-normaliser (its factored sum left the fp32 range):
     // exact logsumexp by the whole warp
