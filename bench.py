@@ -365,30 +365,27 @@ def kernel_algorithmic_bytes(w, il, ll):
 
 
 def run_e2e(w, crit, device_case, dev, distributed, world, steps):
-    """fwd+bwd through TransducerLoss with HOST buffers: every step copies this step's
-    inputs from pinned host memory to the device and the costs and both gradients back."""
+    """fwd+bwd with HOST buffers through the library's host-buffer entry point
+    (HostLossPipeline): every step copies this step's inputs from pinned host memory to the
+    device and the costs and both gradients back, chunk by chunk, copies in both directions
+    overlapping the kernels."""
     import torch.distributed as dist
+    from transducer_b200 import HostLossPipeline
     E, P, labels, il, ll = device_case
     host = [t.detach().cpu().pin_memory() for t in (E, P, labels, il, ll)]
     B = E.shape[0]
     out_costs = torch.empty(B, dtype=torch.float32).pin_memory()
     out_eg = torch.empty(E.shape, dtype=torch.float32).pin_memory()
     out_pg = torch.empty(P.shape, dtype=torch.float32).pin_memory()
-    deltas = torch.ones(B, device=dev)
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in (out_costs, out_eg, out_pg))
+    pipe = HostLossPipeline(blank=crit.blank, chunk=2, slots=4, device=dev)
 
     def step():
-        e, p, lab, a, b = [t.to(dev, non_blocking=True) for t in host]
-        e.requires_grad_(True)
-        p.requires_grad_(True)
-        costs = crit(e, p, lab, a, b)
+        loss_sum = pipe(*host, out_costs, out_eg, out_pg)
         if distributed:
-            dist.all_reduce(crit.last_loss_sum)
-        costs.backward(deltas)
-        out_costs.copy_(costs.detach(), non_blocking=True)
-        out_eg.copy_(e.grad, non_blocking=True)
-        out_pg.copy_(p.grad, non_blocking=True)
+            dist.all_reduce(loss_sum)
+        return loss_sum
 
     step()
     torch.cuda.synchronize()
@@ -405,7 +402,8 @@ def run_e2e(w, crit, device_case, dev, distributed, world, steps):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item() / steps
     return {"value": world * B / (ms * 1e-3), "unit": "utterances/s", "ms_per_step": ms,
-            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps}
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
+            "api": "transducer_b200.HostLossPipeline(chunk=2, slots=4)"}
 
 
 if __name__ == "__main__":

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 import torch
 
+import abi
 from conftest import kat_arrays
 from oracle import oracle as O
 from transducer_b200 import TransducerLoss
@@ -116,3 +117,31 @@ def test_non_default_stream_and_blank():
     wv = O.viterbi(E.numpy(), P.numpy(), il.numpy(), ll.numpy(), blank=blank)
     for b in range(B):
         assert np.array_equal(vit.cpu().numpy()[b, :ll[b]], wv[b, :ll[b]])
+
+
+def test_host_pipeline_matches_whole_batch_call():
+    from transducer_b200 import HostLossPipeline
+    g = torch.Generator().manual_seed(11)
+    B, T, U, V = 7, 90, 12, 256
+    E = torch.randn((B, T, V), generator=g).pin_memory()
+    P = torch.randn((B, U, V), generator=g).pin_memory()
+    labels = torch.randint(1, V, (B, U - 1), generator=g, dtype=torch.int32).pin_memory()
+    il = torch.randint(T // 2, T + 1, (B,), generator=g, dtype=torch.int32).pin_memory()
+    ll = torch.randint(0, U, (B,), generator=g, dtype=torch.int32).pin_memory()
+    deltas = torch.rand((B,), generator=g).add_(0.5).pin_memory()
+    costs = torch.empty(B).pin_memory()
+    eg = torch.empty_like(E).pin_memory()
+    pg = torch.empty_like(P).pin_memory()
+    pipe = HostLossPipeline(chunk=3, slots=2)      # chunks of 3, 3 and 1 utterances
+    for _ in range(2):                             # second call reuses the slots
+        loss_sum = pipe(E, P, labels, il, ll, costs, eg, pg, deltas)
+        torch.cuda.synchronize()
+    Ed, Pd = E.cuda().requires_grad_(True), P.cuda().requires_grad_(True)
+    want = TransducerLoss()(Ed, Pd, labels.cuda(), il.cuda(), ll.cuda())
+    want.backward(deltas.cuda())
+    assert torch.allclose(costs, want.detach().cpu(), rtol=1e-6, atol=1e-5)
+    assert abs(loss_sum.item() - want.sum().item()) <= 1e-5 * abs(want.sum().item())
+    assert abi.rel_to_max(eg.numpy(), Ed.grad.cpu().numpy()) <= 1e-5
+    assert abi.rel_to_max(pg.numpy(), Pd.grad.cpu().numpy()) <= 1e-5
+    with pytest.raises(ValueError):
+        pipe(E.cuda(), P, labels, il, ll, costs, eg, pg)

@@ -3,5 +3,6 @@
 Drop-in for the CUDA path of awni/transducer (transducer/__init__.py:1 exports the
 same single name)."""
 from .torch_binding import TransducerLoss
+from .host_pipeline import HostLossPipeline
 
-__all__ = ["TransducerLoss"]
+__all__ = ["TransducerLoss", "HostLossPipeline"]
