@@ -577,38 +577,28 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   if (warp == kMmaWarp) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
 }
 
-// Recomputes marked nodes (NaN in LN) with the exact fp32 logsumexp.  Each warp scans
-// 32 consecutive nodes per iteration; marked ones are evaluated by the whole warp.
+// Recomputes marked nodes (NaN in LN) with the exact fp32 logsumexp.  One warp per frame
+// (b, t): it scans the frame's nodes 32 at a time; marked ones are evaluated by the whole warp.
 __global__ void __launch_bounds__(256) lognorm_fixup_kernel(
     const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ LN,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int B, int maxT, int maxU,
     int V) {
   const int lane = threadIdx.x & 31;
-  const i64 warpsTotal = (i64)gridDim.x * (blockDim.x >> 5);
-  const i64 cells = (i64)B * maxT * maxU;
-  for (i64 base = ((i64)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; base < cells;
-       base += warpsTotal * 32) {
-    const i64 idx = base + lane;
-    bool marked = false;
-    if (idx < cells) {
-      const int u = (int)(idx % maxU);
-      const int t = (int)((idx / maxU) % maxT);
-      const int b = (int)(idx / ((i64)maxU * maxT));
-      if (t < min(inLens[b], maxT) && u < min(labLens[b] + 1, maxU)) {
-        const float v = LN[idx];
-        marked = (v != v);
-      }
-    }
-    unsigned todo = __ballot_sync(0xffffffffu, marked);
+  const i64 row = (i64)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= (i64)B * maxT) return;
+  const int b = (int)(row / maxT), t = (int)(row % maxT);
+  if (t >= min(inLens[b], maxT)) return;
+  const int U = min(labLens[b] + 1, maxU);
+  const float* er = E + row * V;
+  float* ln = LN + row * maxU;
+  for (int u0 = 0; u0 < U; u0 += 32) {
+    const int u = u0 + lane;
+    const float v0 = (u < U) ? ln[u] : 0.0f;
+    unsigned todo = __ballot_sync(0xffffffffu, v0 != v0);
     while (todo) {
       const int src = __ffs(todo) - 1;
       todo &= todo - 1;
-      const i64 k = base + src;
-      const int u = (int)(k % maxU);
-      const int t = (int)((k / maxU) % maxT);
-      const int b = (int)(k / ((i64)maxU * maxT));
-      const float* er = E + ((i64)b * maxT + t) * V;
-      const float* pr = P + ((i64)b * maxU + u) * V;
+      const float* pr = P + ((i64)b * maxU + u0 + src) * V;
       float m = neg_inf();
       for (int v = lane; v < V; v += 32) m = fmaxf(m, er[v] + pr[v]);
       m = warp_max(m);
@@ -616,7 +606,7 @@ __global__ void __launch_bounds__(256) lognorm_fixup_kernel(
       if (m != neg_inf() && m != pos_inf())
         for (int v = lane; v < V; v += 32) s += expf((er[v] + pr[v]) - m);
       s = warp_sum(s);
-      if (lane == 0) LN[k] = logf(s) + m;
+      if (lane == 0) ln[u0 + src] = logf(s) + m;
     }
   }
 }
@@ -716,8 +706,9 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   TB200_CHECK_LAUNCH();
   if (fixup) {
     ScopedKernel sk("lognorm_fixup", stream);
-    lognorm_fixup_kernel<<<148 * 2, 256, 0, stream>>>(E, P, LN, inLens, labLens, d.B, d.maxT,
-                                                      d.maxU, d.V);
+    const unsigned rows = (unsigned)d.B * (unsigned)d.maxT;
+    lognorm_fixup_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(E, P, LN, inLens, labLens, d.B,
+                                                             d.maxT, d.maxU, d.V);
   }
   TB200_CHECK_LAUNCH();
 }
