@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 // sum_t step -> pLabel[u] in a fixed order (per group, the groups' partial sums added in
 // group order at the end).
 // Block k holds the diagonals dTop(k) = S-1-16k down to dLo(k) = max(dTop-15, 0).
-constexpr int kHelperGroups = 3;  // helper group j takes the diagonals dd = j (mod 3) of a block
+constexpr int kHelperGroups = 4;  // helper group j takes the diagonals dd = j (mod 4) of a block
 constexpr int kGammaThreads = 32 + 128 * kHelperGroups;
 
 __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     const uint8_t* src = smemG + (size_t)(k % kRing) * slotBytes;
     const float2* tb = reinterpret_cast<const float2*>(src);
     const float* aa = reinterpret_cast<const float*>(src + arcBytes);
-#pragma unroll 3
+#pragma unroll 4
     for (int dd = hg; dd < nd; dd += kHelperGroups) {
       const int row = dTop - dd - dLo, t = dTop - dd - hu;
       const float2 arc = tb[row * ld + hu];
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   auto post = [&](int k) {  // helpers: (stay, step) of block k -> global, running sums
     if (hu >= U) return;
     const int dTop = S - 1 - k * kDiag, nd = min(kDiag, dTop + 1);
-#pragma unroll 3
+#pragma unroll 4
     for (int dd = hg; dd < nd; dd += kHelperGroups) {
       const int d = dTop - dd, t = d - hu;
       if (t >= 0 && t < T) {
