@@ -190,6 +190,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step eagerly instead of replaying a captured CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -216,7 +218,9 @@ def main():
     B = w.B
     E, P, labels, il, ll = workloads.generate(w, dev, first=rank * B, count=B)
     deltas = torch.ones(B, device=dev)
-    crit = TransducerLoss(blank=w.blank)
+    # lengths come from the workload generator and fit the padded shapes: skip the wrapper's
+    # per-call read-back of their maxima (a host synchronisation; it also forbids graph capture)
+    crit = TransducerLoss(blank=w.blank, validate_lengths=False)
     E.requires_grad_(True)
     P.requires_grad_(True)
 
@@ -238,6 +242,32 @@ def main():
         step()
     barrier()
 
+    # The step only enqueues kernels, memsets and (N > 1) one NCCL all-reduce: capture it once in
+    # a CUDA graph and replay it, which removes the host-side launch gaps between the kernels.
+    eager_step, graphed = step, False
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            n0 = _lib.lib.tb200_launch_count()
+            with torch.cuda.graph(graph, stream=side):
+                captured_sum = eager_step()
+            kernels_per_step = _lib.lib.tb200_launch_count() - n0  # kernel nodes of the graph
+            torch.cuda.current_stream().wait_stream(side)
+
+            def step():
+                graph.replay()
+                return captured_sum
+            graphed = True
+            for _ in range(2):
+                step()
+            barrier()
+        except Exception as exc:  # capture is an optimisation; the eager step is always valid
+            print("bench.py: CUDA graph capture failed (%s); running eagerly" % exc, file=sys.stderr)
+            step = eager_step
+            torch.cuda.synchronize()
+
     # ---- timed region: K steps, device-timed, max over ranks -----------------------
     launches0 = _lib.lib.tb200_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -248,7 +278,9 @@ def main():
             step()
         ev1.record()
         barrier()
-        launches = _lib.lib.tb200_launch_count() - launches0
+        # (a replayed graph launches its kernel nodes without passing the library's counter)
+        launches = kernels_per_step * args.steps if graphed \
+            else _lib.lib.tb200_launch_count() - launches0
         ms_total = ev0.elapsed_time(ev1)
         # Same K steps once more with every kernel bracketed by CUDA events on its stream (the
         # library's own accounting): per-kernel durations for the roofline.  Kept out of the
@@ -258,7 +290,7 @@ def main():
         evp0, evp1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         evp0.record()
         for _ in range(args.steps):
-            step()
+            eager_step()   # (event records are not captured in the graph)
         evp1.record()
         barrier()
         _lib.lib.tb200_profile_enable(0)
@@ -320,7 +352,7 @@ def main():
             if w.name == "c3" else None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(w, world, B),
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roofline, "whole_step": whole, "cpu_baseline": cpu,
+            "cuda_graph": graphed, "roofline": roofline, "whole_step": whole, "cpu_baseline": cpu,
             "loss_sum": loss_sum,
         }
         print(json.dumps(line), flush=True)

@@ -145,3 +145,56 @@ def test_host_pipeline_matches_whole_batch_call():
     assert abi.rel_to_max(pg.numpy(), Pd.grad.cpu().numpy()) <= 1e-5
     with pytest.raises(ValueError):
         pipe(E.cuda(), P, labels, il, ll, costs, eg, pg)
+
+
+def test_forward_backward_can_be_captured_in_a_cuda_graph():
+    """The fused calls only enqueue work (kernels, memsets) on the chosen stream, so a training
+    step can be captured once and replayed."""
+    g = torch.Generator().manual_seed(5)
+    B, T, U, V = 3, 70, 9, 128
+    E = torch.randn((B, T, V), generator=g).cuda()
+    P = torch.randn((B, U, V), generator=g).cuda()
+    labels = torch.randint(1, V, (B, U - 1), generator=g, dtype=torch.int32).cuda()
+    il = torch.tensor([T, T - 9, T - 30], dtype=torch.int32).cuda()
+    ll = torch.tensor([U - 1, 3, 0], dtype=torch.int32).cuda()
+    fwd = abi.loss_forward(E, P, labels, il, ll)          # warm-up outside capture (attributes)
+    want_eg, want_pg = abi.loss_backward(E, P, labels, il, ll, fwd)
+    want_costs = fwd["costs"].clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):   # abi.* enqueue on torch's current stream
+        cap = abi.loss_forward(E, P, labels, il, ll)
+        eg, pg = abi.loss_backward(E, P, labels, il, ll, cap)
+    E2 = E.clone()
+    E.mul_(0.5)                                            # new inputs in the captured buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    assert not torch.allclose(cap["costs"], want_costs)
+    E.copy_(E2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(cap["costs"], want_costs)
+    assert torch.equal(eg, want_eg) and torch.equal(pg, want_pg)
+
+
+def test_wrapper_without_length_validation_gives_the_same_result():
+    g = torch.Generator().manual_seed(6)
+    B, T, U, V = 2, 40, 7, 64
+    E = torch.randn((B, T, V), generator=g).cuda().requires_grad_(True)
+    P = torch.randn((B, U, V), generator=g).cuda().requires_grad_(True)
+    labels = torch.randint(1, V, (B, U - 1), generator=g, dtype=torch.int32).cuda()
+    il = torch.tensor([T, T - 5], dtype=torch.int32).cuda()
+    ll = torch.tensor([U - 1, 2], dtype=torch.int32).cuda()
+    want = TransducerLoss()(E, P, labels, il, ll)
+    want.sum().backward()
+    want_eg, want_pg = E.grad.clone(), P.grad.clone()
+    E.grad = None
+    P.grad = None
+    costs = TransducerLoss(validate_lengths=False)(E, P, labels, il, ll)
+    costs.sum().backward()
+    assert torch.equal(costs.detach(), want.detach())
+    assert torch.equal(E.grad, want_eg) and torch.equal(P.grad, want_pg)
+    # the default wrapper still refuses lengths that do not fit (it reads them back)
+    with pytest.raises(ValueError):
+        TransducerLoss()(E, P, labels, il + 100, ll)

@@ -36,8 +36,10 @@ class Transducer(torch.autograd.Function):
     """Autograd node for the loss (transducer/torch_binding.py:23-90)."""
 
     @staticmethod
-    def forward(ctx, emissions, predictions, labels, input_lengths, label_lengths, blank=0):
-        certify_inputs(emissions, predictions, labels, input_lengths, label_lengths)
+    def forward(ctx, emissions, predictions, labels, input_lengths, label_lengths, blank=0,
+                validate_lengths=True):
+        certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
+                       validate_lengths)
         device = emissions.device
         emissions = emissions.contiguous()
         predictions = predictions.contiguous()
@@ -81,7 +83,7 @@ class Transducer(torch.autograd.Function):
                 input_lengths.data_ptr(), label_lengths.data_ptr(), saved.data_ptr(),
                 saved.numel(), deltas.data_ptr(), egrads.data_ptr(), pgrads.data_ptr(),
                 B, T, U, V, ctx.blank, ws.data_ptr(), nbytes)
-        return egrads, pgrads, None, None, None, None
+        return egrads, pgrads, None, None, None, None, None
 
 
 class TransducerLoss(torch.nn.Module):
@@ -93,15 +95,22 @@ class TransducerLoss(torch.nn.Module):
 
     Arguments:
         blank (int, optional): id of the blank label (default 0).
+        validate_lengths (bool, optional): compare the largest input / label length with the
+            padded shapes, as the reference does (default).  That check reads two numbers back
+            from the device, i.e. it synchronises the host with the stream on every call;
+            pass False to skip it when the lengths are known to fit -- the call then only
+            enqueues work (and can be captured in a CUDA graph).  No counterpart in the
+            reference.
 
     After each call ``last_loss_sum`` holds a detached 1-element device tensor with
     sum_b costs[b], produced by the kernel itself; a data-parallel caller can
     all-reduce it without launching a reduction.
     """
 
-    def __init__(self, blank=0):
+    def __init__(self, blank=0, validate_lengths=True):
         super(TransducerLoss, self).__init__()
         self.blank = blank
+        self.validate_lengths = validate_lengths
         self.last_loss_sum = None
 
     def forward(self, emissions, predictions, labels, input_lengths, label_lengths):
@@ -114,7 +123,8 @@ class TransducerLoss(torch.nn.Module):
         predictions.
         """
         costs, loss_sum = Transducer.apply(
-            emissions, predictions, labels, input_lengths, label_lengths, self.blank)
+            emissions, predictions, labels, input_lengths, label_lengths, self.blank,
+            self.validate_lengths)
         self.last_loss_sum = loss_sum
         return costs
 
@@ -155,7 +165,8 @@ def check_dim(var, dim, name):
         raise ValueError("{} must be {}D".format(name, dim))
 
 
-def certify_inputs(emissions, predictions, labels, input_lengths, label_lengths):
+def certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
+                   validate_lengths=True):
     """Argument checks with the reference's exception types and messages
     (transducer/torch_binding.py:195-229).  Dimensionality is checked first here so a
     wrong rank reports itself rather than an index error."""
@@ -187,7 +198,7 @@ def certify_inputs(emissions, predictions, labels, input_lengths, label_lengths)
     devices = {t.device for t in (emissions, predictions, labels, input_lengths, label_lengths)}
     if len(devices) != 1:
         raise ValueError("all inputs must be on the same device.")
-    if batch == 0:
+    if batch == 0 or not validate_lengths:
         return
     # one device->host transfer for both maxima (the reference does two, :222-229)
     max_t, max_u = torch.stack((input_lengths.max(), label_lengths.max())).tolist()
