@@ -126,13 +126,15 @@ struct BackwardWs {
 struct ViterbiWs {
   float *LN, *rowRef, *maxP, *best;
   uint32_t* decBits;
+  float4* nodes;  // skewed per-node operands of the single-warp sweep (label axis <= 256)
   ViterbiWs(Carver& c, const Dims& d) {
     const size_t B = d.B, T = d.maxT, U = d.maxU;
     LN = c.take<float>(B * T * U);
     rowRef = c.take<float>(B * T);
     maxP = c.take<float>(B * U);
     best = c.take<float>(B * T * U);
-    decBits = c.take<uint32_t>(viterbi_decbits_words(d));
+    decBits = c.take<uint32_t>(std::max(viterbi_decbits_words(d), viterbi_warp_decbits_words(d)));
+    nodes = c.take<float4>(viterbi_warp_nodes(d));
   }
 };
 
@@ -428,8 +430,12 @@ int tb200_viterbi_decode(const float* E, const float* P, const int* inLens,
     LogNormWs lw(c, d);
     log_norms_impl(E, P, ws.LN, ws.rowRef, ws.maxP, inLens, labLens, d, lw);
     launch_maxplus(E, P, ws.best, inLens, labLens, d, g_stream);
-    launch_viterbi_lattice(E, P, ws.LN, ws.best, ws.decBits, labels, inLens, labLens, d,
-                           g_stream);
+    if (viterbi_warp_supported(d))
+      launch_viterbi_warp(E, P, ws.LN, ws.best, ws.nodes, ws.decBits, labels, inLens, labLens, d,
+                          lw.status, g_stream);
+    else
+      launch_viterbi_lattice(E, P, ws.LN, ws.best, ws.decBits, labels, inLens, labLens, d,
+                             g_stream);
   });
 }
 

@@ -156,6 +156,16 @@ void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, con
                        const int* labLens, float* stayS, float* stepS, float* pBlank,
                        float* pLabel, Dims d, int* status, cudaStream_t stream);
 
+// Viterbi sweep in one warp per utterance (label axis <= 256): same results as
+// launch_viterbi_lattice.  `nodes` is scratch of viterbi_warp_nodes(d) float4, decBits of
+// viterbi_warp_decbits_words(d) words.
+bool viterbi_warp_supported(Dims d);
+size_t viterbi_warp_nodes(Dims d);
+size_t viterbi_warp_decbits_words(Dims d);  // its decision bits are packed along t+u
+void launch_viterbi_warp(const float* E, const float* P, const float* LN, const float* best,
+                         float4* nodes, uint32_t* decBits, int* labels, const int* inLens,
+                         const int* labLens, Dims d, int* status, cudaStream_t stream);
+
 // ---- maxplus.cu --------------------------------------------------------------
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,
                     const int* labLens, Dims d, cudaStream_t stream);

@@ -18,6 +18,8 @@
 //
 //   alpha   transducer/transducer_cpu.cpp:30-79   (transducer_cuda.cu:32-97)
 //   reverse transducer/transducer_cpu.cpp:81-143  (transducer_cuda.cu:99-176)
+#include <algorithm>
+
 #include "kernels.h"
 #include "profile.h"
 #include "sm100.cuh"
@@ -365,6 +367,248 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// Viterbi: max-plus sweep in one warp, bit-packed decisions, backtrack, label argmax
+// ---------------------------------------------------------------------------
+// Per node the sweep needs E[t,blank], LN[t,u] and best[t,u] (the max-plus label score of
+// maxplus.cu); viterbi_prep_kernel lays them out skewed as one float4 per node, so that a block
+// of diagonals is one bulk copy.  The scores are formed in the reference's operation order,
+// ((score + E[t,blank]) + P[u,blank]) - LN and (score + best) - LN, so every comparison, and
+// with it the path, is bit-identical to transducer_cpu.cpp:145-222.
+// Nodes outside the lattice hold the record (-1e30, 0, -1e30): whatever enters them leaves as
+// about -1e30, which loses every comparison against a real score.  With that the sweep needs
+// no case distinctions at all: the blank arc into frame 0 and the label arc into position 0
+// come from such nodes (or from the -inf fed to lane 0) and lose by themselves.
+constexpr float kNoNode = -1.0e30f;
+
+__global__ void __launch_bounds__(256) viterbi_fill_kernel(float4* __restrict__ nodes, i64 n) {
+  const float4 none = make_float4(kNoNode, 0.0f, kNoNode, 0.0f);
+  for (i64 k = (i64)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += (i64)gridDim.x * blockDim.x)
+    nodes[k] = none;
+}
+
+__global__ void __launch_bounds__(256) viterbi_prep_kernel(
+    const float* __restrict__ E, const float* __restrict__ LN, const float* __restrict__ best,
+    float4* __restrict__ nodes, const int* __restrict__ inLens, const int* __restrict__ labLens,
+    int maxT, int maxU, int V, int blank, int ld, i64 latStride) {
+  __shared__ float tLn[32][33], tBs[32][33], tEb[32];
+  const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
+  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  if (t0 >= T || u0 >= U) return;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const float* ln = LN + (i64)b * maxT * maxU;
+  const float* bs = best + (i64)b * maxT * maxU;
+  const int u = u0 + lane, uc = min(u, U - 1), ub = min(u, max(U - 2, 0));
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int tt = w * 4 + k, tc = min(t0 + tt, T - 1);
+    tLn[tt][lane] = ln[(i64)tc * maxU + uc];
+    // the label arc of the last position does not exist
+    tBs[tt][lane] = (u < U - 1) ? bs[(i64)tc * maxU + ub] : kNoNode;
+  }
+  if (threadIdx.x < 32)
+    tEb[lane] = E[((i64)b * maxT + min(t0 + lane, T - 1)) * V + blank];
+  __syncthreads();
+  for (int ds = w; ds < 63; ds += 8) {
+    const int tt = ds - lane;
+    if (tt >= 0 && tt < 32 && t0 + tt < T && u < U)
+      nodes[(i64)b * latStride + (i64)(t0 + u0 + ds) * ld + u] =
+          make_float4(tEb[tt], tLn[tt][lane], tBs[tt][lane], 0.0f);
+  }
+}
+
+// Decision bits of the single-warp sweep are packed along the DIAGONAL d = t + u: word
+// [(b*maxU + u)*wordsD + d/32] bit (d%32) is 1 when node (t,u) was entered by the label arc
+// from (t,u-1).  All positions then flush their words at the same steps.
+__host__ __device__ inline int viterbi_words_d(int maxT, int maxU) { return (maxT + maxU + 31) / 32; }
+
+// NPL label positions per lane: u = NPL*lane + r.  256 threads: warp 0 sweeps, then thread 0
+// backtracks and all warps resolve the labels on the path.
+template <int NPL>
+__global__ void __launch_bounds__(256) viterbi_warp_kernel(
+    const float* __restrict__ E, const float* __restrict__ P, const float4* __restrict__ nodes,
+    int ld, i64 latStride, int nDiag, int ringDepth, uint32_t* __restrict__ decBits,
+    int* __restrict__ labelsOut, const int* __restrict__ inLens, const int* __restrict__ labLens,
+    int maxT, int maxU, int V, int blank, int* status) {
+  extern __shared__ __align__(128) uint8_t smemV[];
+  __shared__ uint64_t bar[kRing];
+  __shared__ int abortFlag;
+  __shared__ int sFrame[256];  // frame at which label u-1 was emitted (U <= 256 here)
+  const int b = blockIdx.x, i = threadIdx.x, lane = i & 31, warp = i >> 5;
+  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  if (T <= 0 || U <= 0) return;
+  const float* e = E + (i64)b * maxT * V;
+  const float* p = P + (i64)b * maxU * V;
+  const float4* nd = nodes + (i64)b * latStride;
+  const int wordsD = viterbi_words_d(maxT, maxU);
+  uint32_t* dec = decBits + (i64)b * maxU * wordsD;
+  for (int u = i; u < U; u += 256) sFrame[u] = -1;
+  if (i == 0) {
+    for (int s = 0; s < kRing; ++s) mbar_init(&bar[s], 1);
+    abortFlag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    float4* ring = reinterpret_cast<float4*>(smemV);  // [ringDepth][kDiag * ld]
+    const int S = T + U - 1;
+    const int nBlocks = (S + kDiag - 1) / kDiag;
+    const int slot = kDiag * ld;
+    auto issue = [&](int k) {  // lane 0
+      if (k < nBlocks) {
+        const int rows = min(kDiag, nDiag - k * kDiag);
+        const uint32_t bytes = (uint32_t)(rows * ld) * 16u;
+        mbar_arrive_expect_tx(&bar[k % ringDepth], bytes);
+        bulk_load_1d(ring + (size_t)(k % ringDepth) * slot, nd + (size_t)k * slot, bytes,
+                     &bar[k % ringDepth]);
+      }
+    };
+    if (lane == 0)
+      for (int k = 0; k < ringDepth - 1; ++k) issue(k);
+    const int u0 = NPL * lane;
+    float pbl[NPL], stay[NPL], stepOut[NPL];
+    uint32_t bits[NPL];
+    uint32_t* decU[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+      pbl[r] = (u0 + r < U) ? p[(i64)(u0 + r) * V + blank] : 0.0f;
+      stay[r] = stepOut[r] = kNoNode;
+      bits[r] = 0u;
+      decU[r] = dec + (i64)min(u0 + r, maxU - 1) * wordsD;
+    }
+    if (lane == 0) stay[0] = 0.0f;  // score 0 enters the origin (as if by its blank arc)
+    bool ok = true;
+    int kFail = 0;
+    for (int k = 0; k < nBlocks; ++k) {
+      if (lane == 0) {
+        fence_proxy_async_smem();
+        issue(k + ringDepth - 1);
+      }
+      ok = mbar_wait(&bar[k % ringDepth], (k / ringDepth) & 1, &abortFlag, status, kStatusTimeoutTma);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        kFail = k;
+        break;
+      }
+      const float4* blk = ring + (size_t)(k % ringDepth) * slot;
+      const int ndg = min(kDiag, S - k * kDiag);
+#pragma unroll 2
+      for (int dd = 0; dd < ndg; ++dd) {
+        const int d = k * kDiag + dd;
+        float4 nv[NPL];
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) nv[r] = blk[dd * ld + min(u0 + r, ld - 1)];
+        const float up = __shfl_up_sync(0xffffffffu, stepOut[NPL - 1], 1);
+        const uint32_t bit = 1u << (d & 31);
+        float left[NPL];
+        left[0] = lane ? up : neg_inf();
+#pragma unroll
+        for (int r = 1; r < NPL; ++r) left[r] = stepOut[r - 1];
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+          // the larger of the two arcs, the blank arc on ties (strict '>', as the reference)
+          const bool takeStep = left[r] > stay[r];
+          const float sc = takeStep ? left[r] : stay[r];
+          bits[r] |= takeStep ? bit : 0u;
+          stay[r] = ((sc + nv[r].x) + pbl[r]) - nv[r].y;   // E[t,blank], LN[t,u]
+          stepOut[r] = (sc + nv[r].z) - nv[r].y;           // best[t,u]
+        }
+        if ((d & 31) == 31 || d == S - 1) {
+#pragma unroll
+          for (int r = 0; r < NPL; ++r) {
+            if (u0 + r < U) decU[r][d >> 5] = bits[r];
+            bits[r] = 0u;
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {  // give the copies still in flight a bounded time to land
+      for (int j = kFail; j < min(kFail + ringDepth, nBlocks); ++j) {
+        const unsigned long long t1 = global_timer_ns();
+        while (!mbar_try_wait(&bar[j % ringDepth], (j / ringDepth) & 1) &&
+               global_timer_ns() - t1 < 50000000ull) {
+        }
+      }
+    }
+    __threadfence_block();
+  }
+  __syncthreads();
+  if (abortFlag) return;
+
+  // Backtrack from (T-1,U-1) along row u in diagonal coordinates d = t + u.  Each iteration
+  // consumes either one label or one 32-diagonal word of blanks, so it ends within
+  // U + (T+U)/32 + 1 iterations; the explicit cap only guards against corrupted scratch.
+  // (Node (0,u), u > 0, is always entered by its label arc, so the scan of a row never runs
+  // into the bits of nodes before frame 0.)
+  if (i == 0) {
+    int t = T - 1, u = U - 1;
+    int guard = U + wordsD + 2;
+    while (u > 0 && t >= 0 && guard-- > 0) {
+      const int d = t + u;
+      const uint32_t keep = 0xffffffffu >> (31 - (d & 31));
+      const uint32_t w = ((volatile uint32_t*)dec)[(i64)u * wordsD + (d >> 5)] & keep;
+      if (w == 0u) { t = (d & ~31) - 1 - u; continue; }
+      t = (d & ~31) + (31 - __clz(w)) - u;
+      sFrame[u] = t;
+      --u;
+    }
+  }
+  __syncthreads();
+
+  // Label on each emitting arc of the path: lowest-index argmax over v != blank
+  // of E[t,v] + P[u-1,v] (strict '>' in index order, as the reference's getMax).
+  int* out = labelsOut + (i64)b * (maxU - 1);
+  const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(e) | reinterpret_cast<uintptr_t>(p)) & 15) == 0;
+  for (int u = 1 + warp; u < U; u += 8) {
+    const int t = sFrame[u];
+    if (t < 0) continue;
+    const float* er = e + (i64)t * V;
+    const float* pr = p + (i64)(u - 1) * V;
+    float m = neg_inf();
+    int arg = 0x7fffffff;
+    if (vec4) {  // 16 loads in flight per lane; each lane still visits its entries in index order
+      const float4* e4 = reinterpret_cast<const float4*>(er);
+      const float4* p4 = reinterpret_cast<const float4*>(pr);
+      const int n4 = V >> 2;
+      for (int q0 = lane; q0 < n4; q0 += 128) {
+        float4 a[4], c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int q = min(q0 + 32 * j, n4 - 1);
+          a[j] = e4[q];
+          c[j] = p4[q];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int q = q0 + 32 * j;
+          if (q < n4) {
+            const float x[4] = {a[j].x + c[j].x, a[j].y + c[j].y, a[j].z + c[j].z, a[j].w + c[j].w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const int v = 4 * q + h;
+              if (v != blank && x[h] > m) { m = x[h]; arg = v; }
+            }
+          }
+        }
+      }
+    } else {
+      for (int v = lane; v < V; v += 32) {
+        if (v == blank) continue;
+        const float x = er[v] + pr[v];
+        if (x > m) { m = x; arg = v; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const int a2 = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (m2 > m || (m2 == m && a2 < arg)) { m = m2; arg = a2; }
+    }
+    if (lane == 0) out[u - 1] = (arg == 0x7fffffff) ? 0 : arg;
+  }
+}
+
 template <typename K>
 void allow_dyn_smem(K kernel, int bytes) {
   TB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -398,6 +642,57 @@ void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, con
   gamma_warp_kernel<<<d.B, kGammaThreads, smem, stream>>>(arcs, alphasS, g.ld, g.stride, inLens,
                                                           labLens, stayS, stepS, pBlank, pLabel,
                                                           d.maxT, d.maxU, status);
+  TB200_CHECK_LAUNCH();
+}
+
+bool viterbi_warp_supported(Dims d) { return d.maxU >= 1 && d.maxU <= 256; }
+
+size_t viterbi_warp_decbits_words(Dims d) {
+  return viterbi_warp_supported(d)
+             ? (size_t)d.B * (size_t)d.maxU * (size_t)viterbi_words_d(d.maxT, d.maxU)
+             : 0;
+}
+
+size_t viterbi_warp_nodes(Dims d) {
+  const SkewGeom g = skew_geom(d);
+  return viterbi_warp_supported(d) ? (size_t)d.B * (size_t)g.stride : 0;
+}
+
+void launch_viterbi_warp(const float* E, const float* P, const float* LN, const float* best,
+                         float4* nodes, uint32_t* decBits, int* labels, const int* inLens,
+                         const int* labLens, Dims d, int* status, cudaStream_t stream) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  const SkewGeom g = skew_geom(d);
+  {
+    dim3 grid(div_up(d.maxU, 32), div_up(d.maxT, 32), d.B);
+    ScopedKernel sk("viterbi_prep", stream);
+    viterbi_fill_kernel<<<148 * 8, 256, 0, stream>>>(nodes, (i64)d.B * g.stride);
+    viterbi_prep_kernel<<<grid, 256, 0, stream>>>(E, LN, best, nodes, inLens, labLens, d.maxT,
+                                                  d.maxU, d.V, d.blank, g.ld, g.stride);
+    TB200_CHECK_LAUNCH();
+  }
+  const int slotBytes = kDiag * g.ld * 16;
+  const int ringDepth = std::max(2, std::min(kRing, (200 * 1024) / slotBytes));
+  const int smem = ringDepth * slotBytes;
+  ScopedKernel sk("viterbi_warp", stream);
+#define CALL(NPL)                                                                              \
+  do {                                                                                         \
+    allow_dyn_smem(viterbi_warp_kernel<NPL>, smem);                                            \
+    viterbi_warp_kernel<NPL><<<d.B, 256, smem, stream>>>(                                      \
+        E, P, nodes, g.ld, g.stride, g.nDiag, ringDepth, decBits, labels, inLens, labLens,     \
+        d.maxT, d.maxU, d.V, d.blank, status);                                                 \
+  } while (0)
+  switch (g.ld / 32) {
+    case 1: CALL(1); break;
+    case 2: CALL(2); break;
+    case 3: CALL(3); break;
+    case 4: CALL(4); break;
+    case 5: CALL(5); break;
+    case 6: CALL(6); break;
+    case 7: CALL(7); break;
+    default: CALL(8); break;
+  }
+#undef CALL
   TB200_CHECK_LAUNCH();
 }
 
