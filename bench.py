@@ -242,10 +242,12 @@ def main():
         step()
     barrier()
 
-    # The step only enqueues kernels, memsets and (N > 1) one NCCL all-reduce: capture it once in
-    # a CUDA graph and replay it, which removes the host-side launch gaps between the kernels.
+    # The step only enqueues kernels and memsets: capture it once in a CUDA graph and replay it,
+    # which removes the host-side launch gaps between the kernels.
+    # (Single-GPU runs only: with N > 1 the step contains an NCCL collective, and ranks that
+    # disagree on whether their capture succeeded would wait for each other forever.)
     eager_step, graphed = step, False
-    if not args.no_graph:
+    if not args.no_graph and not distributed:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
