@@ -224,14 +224,19 @@ def main():
     E.requires_grad_(True)
     P.requires_grad_(True)
 
-    def step():
+    def local_step():
+        """Forward + backward on this rank's shard; returns the shard's loss sum (device)."""
         E.grad = None
         P.grad = None
         costs = crit(E, P, labels, il, ll)
-        if distributed:
-            dist.all_reduce(crit.last_loss_sum)
         costs.backward(deltas)
         return crit.last_loss_sum
+
+    def step():
+        loss_sum = local_step()
+        if distributed:
+            dist.all_reduce(loss_sum)   # the path's one collective: 4 bytes
+        return loss_sum
 
     def barrier():
         if distributed:
@@ -242,33 +247,36 @@ def main():
         step()
     barrier()
 
-    # The step only enqueues kernels and memsets: capture it once in a CUDA graph and replay it,
-    # which removes the host-side launch gaps between the kernels.
-    # (Single-GPU runs only: with N > 1 the step contains an NCCL collective, and ranks that
-    # disagree on whether their capture succeeded would wait for each other forever.)
+    # The local part of the step only enqueues kernels and memsets: capture it once in a CUDA
+    # graph and replay it, which removes the host-side launch gaps between the kernels.  The NCCL
+    # all-reduce stays outside the graph and is issued by every rank on every step, whether or
+    # not its own capture succeeded, so ranks cannot end up waiting for each other.
     eager_step, graphed = step, False
-    if not args.no_graph and not distributed:
+    if not args.no_graph:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             graph = torch.cuda.CUDAGraph()
             n0 = _lib.lib.tb200_launch_count()
             with torch.cuda.graph(graph, stream=side):
-                captured_sum = eager_step()
+                captured_sum = local_step()
             kernels_per_step = _lib.lib.tb200_launch_count() - n0  # kernel nodes of the graph
             torch.cuda.current_stream().wait_stream(side)
 
             def step():
                 graph.replay()
+                if distributed:
+                    dist.all_reduce(captured_sum)
                 return captured_sum
             graphed = True
-            for _ in range(2):
-                step()
-            barrier()
         except Exception as exc:  # capture is an optimisation; the eager step is always valid
             print("bench.py: CUDA graph capture failed (%s); running eagerly" % exc, file=sys.stderr)
             step = eager_step
             torch.cuda.synchronize()
+        # (the same calls on every rank, whichever way its capture went)
+        for _ in range(2):
+            step()
+        barrier()
 
     # ---- timed region: K steps, device-timed, max over ranks -----------------------
     launches0 = _lib.lib.tb200_launch_count()
