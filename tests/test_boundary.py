@@ -117,3 +117,12 @@ def test_workspace_queries_are_pure_and_monotone():
     assert f(0, 0, 1, 8) >= 0
     assert f(2, 50, 11, 30) <= f(4, 50, 11, 30) <= f(4, 100, 11, 30)
     assert _lib.lib.tb200_viterbi_decode_workspace_bytes(2, 50, 11, 30) > 0
+
+
+def test_host_pipeline_needs_a_gpu_and_host_tensors():
+    """The host-buffer pipeline is part of the product path: no CUDA device, no result."""
+    import torch
+    from transducer_b200 import HostLossPipeline
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            HostLossPipeline()
