@@ -376,13 +376,13 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the
 # named kernel; see the summaries under profiles/.  Keyed by (workload, kernel).
 NCU_TRAFFIC_BYTES = {
-    ("c3", "grads_umma"): 2450743552 + 2682491136,     # profiles/launch_list_bench_c3.md
-    ("c3", "lognorm_umma"): 2604641792 + 14880512,
-    ("c3", "alpha_warp"): 59774208 + 2307072,          # profiles/lattice_sweeps_c3.md
-    ("c3", "gamma_warp"): 90813184 + 11543040,
-    ("c3", "lattice_prep"): 532794368 + 42867200,
-    ("c3", "expp_split"): 147243264 + 231990016,
-    ("c3", "lattice_unskew_round"): 64985856 + 17259264,
+    ("c3", "grads_umma"): 2466260480 + 2679300608,     # profiles/launch_list_bench_c3.md
+    ("c3", "lognorm_umma"): 2625806848 + 14500608,
+    ("c3", "alpha_warp"): 60119296 + 1955328,          # profiles/lattice_sweeps_c3.md
+    ("c3", "gamma_warp"): 91227136 + 11807488,
+    ("c3", "lattice_prep"): 532158720 + 43793664,
+    ("c3", "expp_split"): 144711680 + 230021888,
+    ("c3", "lattice_unskew_round"): 65938432 + 18867200,
 }
 
 
