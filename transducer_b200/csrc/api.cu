@@ -262,21 +262,32 @@ int tb200_viterbi(const float* E, const float* P, const float* LN, int* labels,
     check_dims(d);
     if (B == 0 || maxT == 0 || maxU == 0) return;
     const size_t cells = (size_t)B * maxT * maxU;
+    const bool warp = viterbi_warp_supported(d);  // label axis <= 256: single-warp sweep
     float* best = nullptr;
     uint32_t* dec = nullptr;
+    float4* nodes = nullptr;
+    const size_t decWords = warp ? viterbi_warp_decbits_words(d) : viterbi_decbits_words(d);
     TB200_CUDA_CHECK(cudaMallocAsync((void**)&best, sizeof(float) * cells, g_stream));
-    TB200_CUDA_CHECK(cudaMallocAsync((void**)&dec, sizeof(uint32_t) * viterbi_decbits_words(d),
-                                     g_stream));
-    try {
-      launch_maxplus(E, P, best, inLens, labLens, d, g_stream);
-      launch_viterbi_lattice(E, P, LN, best, dec, labels, inLens, labLens, d, g_stream);
-    } catch (...) {
+    TB200_CUDA_CHECK(cudaMallocAsync((void**)&dec, sizeof(uint32_t) * decWords, g_stream));
+    if (warp)
+      TB200_CUDA_CHECK(cudaMallocAsync((void**)&nodes, sizeof(float4) * viterbi_warp_nodes(d), g_stream));
+    auto release = [&] {
       cudaFreeAsync(best, g_stream);
       cudaFreeAsync(dec, g_stream);
+      if (nodes) cudaFreeAsync(nodes, g_stream);
+    };
+    try {
+      launch_maxplus(E, P, best, inLens, labLens, d, g_stream);
+      if (warp)
+        launch_viterbi_warp(E, P, LN, best, nodes, dec, labels, inLens, labLens, d, nullptr,
+                            g_stream);
+      else
+        launch_viterbi_lattice(E, P, LN, best, dec, labels, inLens, labLens, d, g_stream);
+    } catch (...) {
+      release();
       throw;
     }
-    TB200_CUDA_CHECK(cudaFreeAsync(best, g_stream));
-    TB200_CUDA_CHECK(cudaFreeAsync(dec, g_stream));
+    release();
   });
 }
 
