@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Benchmark of the RNN-T loss hot path (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3]
+                    [--impl reference | reference-cuda]
 
 One step = one forward + backward pass of the loss over one batch of the synthetic
 workload (default "c3": B=32 per GPU, T=2000, U=100, V=10000, N(0,2) scores,
@@ -13,7 +14,9 @@ Rank 0 prints ONE JSON line.  `value` is utterances/s over all ranks with inputs
 resident in HBM; `e2e` is the same through TransducerLoss with HOST (pinned) buffers,
 host<->device copies inside the timed region; `roofline` describes the dominant
 kernel; `cpu_baseline` is the reference's CPU path timed on this host on a bounded
-sample.  `--impl reference` times only that CPU path.
+sample.  `--impl reference` times only that CPU path; `--impl reference-cuda` times the
+reference's own GPU path (its CUDA backend rebuilt unchanged for sm_100a) on the same
+workload, for the speed-up over the GPU incumbent.
 """
 import argparse
 import json
@@ -167,6 +170,57 @@ def run_reference_arm(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda_arm(args, w):
+    """The reference's own GPU path on this GPU: its CUDA backend compiled unchanged for
+    sm_100a plus the torch CUDA ops of its wrapper (transducer/torch_binding.py:25-90), the
+    whole batch of `w`, forward + backward, timed with CUDA events on the default stream (where
+    that backend launches).  Rank 0 only; a comparison line, not the product."""
+    if env_int("RANK", 0) != 0:
+        return
+    from oracle import oracle as O
+    from transducer_b200 import workloads
+    if not O.have_reference_cuda():
+        print(json.dumps({"impl": "reference-cuda",
+                          "unavailable": "oracle/_ref/libref_transducer_cuda.so was not built"}))
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "no CUDA device"}))
+        return
+    dev = torch.device("cuda", env_int("LOCAL_RANK", 0))
+    torch.cuda.set_device(dev)
+    B = args.batch if args.batch > 0 else w.B
+    E, P, labels, il, ll = workloads.generate(w, dev, first=0, count=B)
+    deltas = torch.ones(B, device=dev)
+    steps = max(1, args.steps)
+
+    def step():
+        out = O.loss_and_grads_cuda(E, P, labels, il, ll, blank=w.blank, deltas=deltas)
+        return out["costs"]
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        ev0.record()
+        for _ in range(steps):
+            costs = step()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / steps
+    line = {
+        "impl": "reference-cuda",
+        "metric": "rnnt_loss_fwd_bwd_utterances_per_s", "value": B / (ms * 1e-3),
+        "unit": "utterances/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(w, 1, B),
+        "clocks": clocks.summary(),
+        "note": "reference CUDA backend (transducer_cuda.cu, unchanged, sm_100a) + torch CUDA ops "
+                "of its wrapper; inputs resident in HBM; loss sum %.6g" % float(costs.sum()),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def workload_config(w, n_gpus, per_rank_batch):
     return {"workload": "%s: B=%d per GPU, T=%d, U=%d, V=%d, N(0,%g) fp32, ragged lengths %s/%s"
                         % (w.name, per_rank_batch, w.T, w.U, w.V, w.std, w.t_range, w.u_range),
@@ -187,7 +241,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3")
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--batch", type=int, default=0,
@@ -203,6 +257,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, w)
+        return
+    if args.impl == "reference-cuda":
+        run_reference_cuda_arm(args, w)
         return
 
     from transducer_b200 import TransducerLoss, _lib

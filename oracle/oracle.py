@@ -12,6 +12,11 @@ Two backends sit behind the same functions:
   ``forward``/``backward``/``viterbi`` have C++ linkage, transducer/transducer.h:3-49,
   so they are bound by their mangled names).
 
+A third library, ``_ref/libref_transducer_cuda.so``, is the reference's own CUDA backend
+(transducer/transducer_cuda.cu) compiled unchanged for sm_100a; ``loss_and_grads_cuda``
+runs the reference's whole GPU path with it: the GPU incumbent that bench.py can time and
+a second checker for the GPU parity tests.
+
 The arithmetic the reference does in torch ops around those three calls
 (transducer/torch_binding.py:35-40 for the log-normalisers, :85-89 for the dense
 part of the gradient, :162-167 for Viterbi) is restated here with the same torch
@@ -28,6 +33,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _PORT_SO = os.path.join(_HERE, "liboracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libref_transducer.so")
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libref_transducer_cuda.so")
 
 _f = ctypes.POINTER(ctypes.c_float)
 _i = ctypes.POINTER(ctypes.c_int)
@@ -313,3 +319,89 @@ def truth64(E, P, labels, in_lens, lab_lens, blank=0):
             eg[b, :T, lab[u]] -= occ_step[:, u]
             pg[b, u, lab[u]] -= occ_step[:, u].sum()
     return {"costs": costs, "egrads": eg, "pgrads": pg, "log_norms": LN}
+
+
+# ----------------------------------------------------------------------------
+# the reference's GPU path (its CUDA backend + the torch CUDA ops of its wrapper)
+# ----------------------------------------------------------------------------
+
+def have_reference_cuda():
+    return os.path.exists(_REF_CUDA_SO)
+
+
+def _ref_cuda():
+    if "ref_cuda" not in _libs:
+        if not have_reference_cuda():
+            raise RuntimeError("reference CUDA backend not built: run `make -C oracle` "
+                               "where the reference sources and nvcc are present")
+        lib = ctypes.CDLL(_REF_CUDA_SO)
+        v, b = ctypes.c_void_p, ctypes.c_bool
+        fw = getattr(lib, _REF_FORWARD)
+        fw.argtypes = [v] * 8 + [_c] * 5 + [b]
+        bw = getattr(lib, _REF_BACKWARD)
+        bw.argtypes = [v] * 10 + [_c] * 5 + [b]
+        vt = getattr(lib, _REF_VITERBI)
+        vt.argtypes = [v] * 6 + [_c] * 5 + [b]
+        for fn in (fw, bw, vt):
+            fn.restype = None
+        _libs["ref_cuda"] = (fw, bw, vt)
+    return _libs["ref_cuda"]
+
+
+def loss_and_grads_cuda(E, P, labels, in_lens, lab_lens, blank=0, deltas=None,
+                        want_grads=True):
+    """``TransducerLoss`` of the reference on CUDA tensors (torch_binding.py:25-90):
+    the same torch ops in the same order, on the device, around the reference's own
+    forward/backward kernels (transducer_cuda.cu:280-348).  Those kernels are launched on
+    the legacy default stream (transducer_cuda.cu:294,334), so the torch ops are put there
+    too.  float32 E [B,T,V], P [B,U',V]; int32 labels [B,U'-1], lengths [B]; all on one
+    CUDA device.  Returns a dict of device tensors."""
+    fw, bw, _ = _ref_cuda()
+    dev = E.device
+    B, T, V = E.shape
+    U = P.shape[1]
+    with torch.cuda.device(dev), torch.cuda.stream(torch.cuda.default_stream(dev)):
+        costs = torch.empty((B,), device=dev, dtype=torch.float32)
+        alphas = torch.empty((B, T, U), device=dev, dtype=torch.float32)
+        max_e = E.max(dim=2, keepdim=True)[0]
+        max_p = P.max(dim=2, keepdim=True)[0]
+        exp_e = torch.exp(E - max_e)
+        exp_p = torch.exp(P - max_p)
+        exp_ln = torch.bmm(exp_e, exp_p.transpose(1, 2))
+        ln = torch.log(exp_ln) + max_e + max_p.transpose(1, 2)
+        fw(E.data_ptr(), P.data_ptr(), costs.data_ptr(), alphas.data_ptr(), ln.data_ptr(),
+           labels.data_ptr(), in_lens.data_ptr(), lab_lens.data_ptr(), B, T, U, V, blank, True)
+        out = {"costs": costs, "alphas": alphas, "log_norms": ln}
+        if not want_grads:
+            return out
+        eg = torch.empty((B, T, V), device=dev, dtype=torch.float32)
+        pg = torch.empty((B, U, V), device=dev, dtype=torch.float32)
+        lg = torch.empty((B, T, U), device=dev, dtype=torch.float32)
+        bw(E.data_ptr(), P.data_ptr(), eg.data_ptr(), pg.data_ptr(), lg.data_ptr(),
+           alphas.data_ptr(), ln.data_ptr(), labels.data_ptr(), in_lens.data_ptr(),
+           lab_lens.data_ptr(), B, T, U, V, blank, True)
+        d = torch.ones((B,), device=dev) if deltas is None else deltas
+        lg = lg * exp_ln.reciprocal()
+        eg += exp_e * torch.bmm(lg, exp_p)
+        pg += exp_p * torch.bmm(lg.transpose(1, 2), exp_e)
+        out["egrads"] = d[:, None, None] * eg
+        out["pgrads"] = d[:, None, None] * pg
+    return out
+
+
+def viterbi_cuda(E, P, in_lens, lab_lens, blank=0, fill=-1):
+    """``TransducerLoss.viterbi`` of the reference on CUDA tensors
+    (torch_binding.py:130-177, transducer_cuda.cu:350-388)."""
+    _, _, vt = _ref_cuda()
+    dev = E.device
+    B, T, V = E.shape
+    U = P.shape[1]
+    with torch.cuda.device(dev), torch.cuda.stream(torch.cuda.default_stream(dev)):
+        max_e = E.max(dim=2, keepdim=True)[0]
+        max_p = P.max(dim=2, keepdim=True)[0]
+        exp_ln = torch.bmm(torch.exp(E - max_e), torch.exp(P - max_p).transpose(1, 2))
+        ln = torch.log(exp_ln) + max_e + max_p.transpose(1, 2)
+        labels = torch.full((B, max(U - 1, 0)), fill, device=dev, dtype=torch.int32)
+        vt(E.data_ptr(), P.data_ptr(), ln.data_ptr(), labels.data_ptr(), in_lens.data_ptr(),
+           lab_lens.data_ptr(), B, T, U, V, blank, True)
+    return labels

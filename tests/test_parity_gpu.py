@@ -192,6 +192,47 @@ def test_stress_grid_against_oracle():
 
 
 # ---------------------------------------------------------------------------
+# the reference's own GPU path (its CUDA backend rebuilt for sm_100a) as a second checker
+# ---------------------------------------------------------------------------
+
+@pytest.mark.skipif(not O.have_reference_cuda(), reason="reference CUDA backend not built")
+@pytest.mark.parametrize("shape", [(3, 40, 9, 30), (4, 300, 41, 512), (2, 700, 101, 2048)])
+def test_against_reference_cuda_path(shape):
+    """Same device tensors through TransducerLoss-as-the-reference-runs-it-on-CUDA
+    (transducer/torch_binding.py:25-90 + transducer_cuda.cu) and through this library."""
+    B, T, U1, V = shape
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + T)
+    E = torch.empty((B, T, V), device="cuda").normal_(0, 1.0, generator=g)
+    P = torch.empty((B, U1, V), device="cuda").normal_(0, 1.0, generator=g)
+    labels = torch.randint(1, V, (B, U1 - 1), generator=g, device="cuda", dtype=torch.int32)
+    il = torch.randint(T // 2, T + 1, (B,), generator=g, device="cuda", dtype=torch.int32)
+    ll = torch.randint(1, U1, (B,), generator=g, device="cuda", dtype=torch.int32)
+    il[0], ll[0] = T, U1 - 1
+    deltas = torch.rand((B,), generator=g, device="cuda") + 0.5
+    want = O.loss_and_grads_cuda(E, P, labels, il, ll, deltas=deltas)
+    torch.cuda.synchronize()
+    fwd = abi.loss_forward(E, P, labels, il, ll)
+    eg, pg = abi.loss_backward(E, P, labels, il, ll, fwd, deltas=deltas)
+    assert close_ref(npy(fwd["costs"]), npy(want["costs"]), LOSS_RTOL, 1e-5), shape
+    # Both paths are fp32 recursions with their own rounding noise (the reference's kernels
+    # land 1.5e-3 of the gradient maximum away from a float64 evaluation at the largest shape
+    # here): the bar applies to the distance to the float64 result, and the distance between
+    # the two fp32 paths may exceed it only by the reference path's own error.
+    tr = O.truth64(npy(E), npy(P), npy(labels), npy(il), npy(ll))
+    d64 = npy(deltas).astype(np.float64)[:, None, None]
+    for got, ref, truth in ((eg, want["egrads"], tr["egrads"] * d64),
+                            (pg, want["pgrads"], tr["pgrads"] * d64)):
+        ours = abi.rel_to_max(npy(got), truth)
+        theirs = abi.rel_to_max(npy(ref), truth)
+        assert ours <= GRAD_TOL, (shape, ours)
+        assert abi.rel_to_max(npy(got), npy(ref)) <= GRAD_TOL + theirs, (shape, ours, theirs)
+    got = npy(abi.viterbi_decode(E, P, il, ll))
+    wv = npy(O.viterbi_cuda(E, P, il, ll))
+    for b, n in enumerate(npy(ll)):
+        assert np.array_equal(got[b, :n], wv[b, :n]), (shape, b)
+
+
+# ---------------------------------------------------------------------------
 # benchmark-sized inputs: a slice against the oracle + size-independent properties
 # ---------------------------------------------------------------------------
 
