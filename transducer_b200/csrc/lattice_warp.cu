@@ -63,6 +63,14 @@ __device__ __forceinline__ void finish_cost_w(float* costs, int b, float cost, i
 // stored in log2 units too: the reverse sweep must form a(t,u) + arc with the very same
 // rounding as here, or the occupancies stop being a conserved flow (the rounding of an alpha
 // of magnitude 1e4 is 1e-3, and such errors would compound along the 2000 steps of a path).
+// Lane l owns the label positions u = 4l + r, r = 0..3: the value crossing from u-1 is the
+// lane's own for r > 0 and comes from lane l-1 by ONE shuffle per diagonal for r = 0; the four
+// arc pairs and the four alphas of a lane are contiguous (two 16-byte loads, one store).  The
+// pace is set by the dependent chain of a diagonal -- the four ex2 and then the four lg2 queue
+// in the quarter-rate special-function unit -- so the loop holds nothing else: no validity
+// tests, no address arithmetic beyond an increment, the final cost read after the loop.
+// (Cutting the label axis over two or four warps that run a block apart, with one or two
+// positions per lane, was measured and is slower: every node then waits for a shuffle.)
 __global__ void __launch_bounds__(32) alpha_warp_kernel(
     const float2* __restrict__ arcs, float* __restrict__ costs, float* __restrict__ alphas, int ld,
     i64 latStride, int nDiag, const int* __restrict__ inLens, const int* __restrict__ labLens,
@@ -82,6 +90,8 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   const int S = T + U - 1;
   const int nBlocks = (S + kDiag - 1) / kDiag;
   const int slot = kDiag * ld;  // float2 elements per ring slot
+  // large negative and finite: the identity of the recursion without -inf arithmetic
+  const float kNone = __uint_as_float(kNoArcBits);
 
   if (lane == 0) {
     for (int s = 0; s < kRing; ++s) mbar_init(&bar[s], 1);
@@ -89,32 +99,28 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
     fence_mbar_init();
   }
   __syncwarp();
+  int issuedN = 0;  // lane 0: blocks whose copies were issued
   auto issue = [&](int k) {  // lane 0: rows [16k, 16k+16) of arcs -> ring slot k % kRing
     if (k < nBlocks) {
       const int rows = min(kDiag, nDiag - k * kDiag);
       const uint32_t bytes = (uint32_t)(rows * ld) * 8u;
       mbar_arrive_expect_tx(&bar[k % kRing], bytes);
       bulk_load_1d(ring + (size_t)(k % kRing) * slot, ar + (size_t)k * slot, bytes, &bar[k % kRing]);
+      issuedN = k + 1;
     }
   };
   if (lane == 0)
     for (int k = 0; k < kRing - 1; ++k) issue(k);
 
-  // large negative and finite: the identity of the recursion without -inf arithmetic
-  const float kNone = __uint_as_float(kNoArcBits);
-  // Lane l owns the label positions u = 4l + r, r = 0..3: the value crossing from u-1 is the
-  // lane's own for r > 0 and comes from lane l-1 by ONE shuffle per diagonal for r = 0; the
-  // four arc pairs and the four alphas of a lane are contiguous (two 16-byte loads, one store).
-  const int u0 = 4 * lane;
-  const bool act = u0 < ld;  // rows are ld <= 128 wide
+  // lanes past the row (ld is a multiple of 4, at most 128) compute on a clamped column: finite
+  // values that are never stored and never reach a lane below them
+  const int u0 = 4 * lane, uc = min(u0, ld - 4);
+  const bool act = u0 < ld;
   float stayIn[4], stepOut[4];
 #pragma unroll
   for (int r = 0; r < 4; ++r) stayIn[r] = stepOut[r] = kNone;
   if (lane == 0) stayIn[0] = 0.0f;  // alpha(0,0) = 0
-  float cost = 0.0f;
-  bool owner = false, ok = true;
-
-  int kFail = 0;
+  bool ok = true;
   for (int k = 0; k < nBlocks; ++k) {
     if (lane == 0) {
       fence_proxy_async_smem();  // the slot refilled next was read by this warp one block ago
@@ -122,21 +128,13 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
     }
     ok = mbar_wait(&bar[k % kRing], (k / kRing) & 1, &abortFlag, status, kStatusTimeoutTma);
     ok = __all_sync(0xffffffffu, ok);
-    if (!ok) {
-      kFail = k;
-      break;
-    }
-    const float2* blk = ring + (size_t)(k % kRing) * slot;
-    const int nd = min(kDiag, S - k * kDiag);
+    if (!ok) break;
+    const float4* blk = reinterpret_cast<const float4*>(ring + (size_t)(k % kRing) * slot + uc);
+    const int d0 = k * kDiag, nd = min(kDiag, S - d0), ld4 = ld / 2;  // float4 per diagonal
+    float* out = al + (size_t)d0 * ld + u0;
 #pragma unroll 2
     for (int dd = 0; dd < nd; ++dd) {
-      const int d = k * kDiag + dd;
-      float4 f01 = make_float4(kNone, kNone, kNone, kNone), f23 = f01;
-      if (act) {
-        const float4* src = reinterpret_cast<const float4*>(blk + dd * ld + u0);
-        f01 = src[0];
-        f23 = src[1];
-      }
+      const float4 f01 = blk[dd * ld4], f23 = blk[dd * ld4 + 1];
       const float fx[4] = {f01.x, f01.z, f23.x, f23.z}, fy[4] = {f01.y, f01.w, f23.y, f23.w};
       const float up = __shfl_up_sync(0xffffffffu, stepOut[3], 1);
       float left[4], m[4], e[4], a[4];
@@ -155,30 +153,25 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
         stayIn[r] = a[r] + fx[r];
         stepOut[r] = a[r] + fy[r];
       }
-      if (act) *reinterpret_cast<float4*>(al + d * ld + u0) = make_float4(a[0], a[1], a[2], a[3]);
-      if (d == S - 1) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-          if (u0 + r == U - 1) {
-            cost = -stayIn[r] * kLn2F;
-            owner = true;
-          }
-      }
+      if (act) *reinterpret_cast<float4*>(out + dd * ld) = make_float4(a[0], a[1], a[2], a[3]);
     }
   }
   if (!ok) {  // a copy never landed: make the failure visible in the result
     if (lane == 0) {  // give the copies still in flight a bounded time to land
-      for (int j = kFail; j < min(kFail + kRing, nBlocks); ++j) {
+      for (int j = max(0, issuedN - kRing); j < issuedN; ++j) {
         const unsigned long long t1 = global_timer_ns();
         while (!mbar_try_wait(&bar[j % kRing], (j / kRing) & 1) &&
                global_timer_ns() - t1 < 50000000ull) {
         }
       }
+      finish_cost_w(costs, b, __int_as_float(0x7fc00000), B, lossSum, ticket);
     }
-    cost = __int_as_float(0x7fc00000);
-    owner = (lane == 0);
+    return;
   }
-  if (owner) finish_cost_w(costs, b, cost, B, lossSum, ticket);
+  // the last diagonal holds only the terminal node (T-1, U-1); its blank arc ends the path
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+    if (u0 + r == U - 1) finish_cost_w(costs, b, -stayIn[r] * kLn2F, B, lossSum, ticket);
 }
 
 // ---------------------------------------------------------------------------
