@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   for (int r = 0; r < 4; ++r) stayIn[r] = stepOut[r] = kNone;
   if (lane == 0) stayIn[0] = 0.0f;  // alpha(0,0) = 0
   bool ok = true;
+  float up = kNone;  // stepOut[3] of the lane below, one diagonal back
   for (int k = 0; k < nBlocks; ++k) {
     if (lane == 0) {
       fence_proxy_async_smem();  // the slot refilled next was read by this warp one block ago
@@ -136,22 +137,23 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
     for (int dd = 0; dd < nd; ++dd) {
       const float4 f01 = blk[dd * ld4], f23 = blk[dd * ld4 + 1];
       const float fx[4] = {f01.x, f01.z, f23.x, f23.z}, fy[4] = {f01.y, f01.w, f23.y, f23.w};
-      const float up = __shfl_up_sync(0xffffffffu, stepOut[3], 1);
+      // Position 3 first: its result feeds the shuffle of the next diagonal; position 0 last: it
+      // waits for the shuffle of this one.  (A warp issues in order.)
       float left[4], m[4], e[4], a[4];
       left[0] = lane ? up : kNone;
 #pragma unroll
       for (int r = 1; r < 4; ++r) left[r] = stepOut[r - 1];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
+      for (int r = 3; r >= 0; --r) {
         m[r] = fmaxf(left[r], stayIn[r]);
         e[r] = ex2_approx(-fabsf(left[r] - stayIn[r]));
       }
 #pragma unroll
-      for (int r = 0; r < 4; ++r) a[r] = m[r] + lg2_approx(1.0f + e[r]);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
+      for (int r = 3; r >= 0; --r) {
+        a[r] = m[r] + lg2_approx(1.0f + e[r]);
         stayIn[r] = a[r] + fx[r];
         stepOut[r] = a[r] + fy[r];
+        if (r == 3) up = __shfl_up_sync(0xffffffffu, stepOut[3], 1);
       }
       if (act) *reinterpret_cast<float4*>(out + dd * ld) = make_float4(a[0], a[1], a[2], a[3]);
     }
