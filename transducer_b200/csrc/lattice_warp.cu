@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
     const float4* blk = reinterpret_cast<const float4*>(ring + (size_t)(k % kRing) * slot + uc);
     const int d0 = k * kDiag, nd = min(kDiag, S - d0), ld4 = ld / 2;  // float4 per diagonal
     float* out = al + (size_t)d0 * ld + u0;
-#pragma unroll 2
+#pragma unroll 4
     for (int dd = 0; dd < nd; ++dd) {
       const float4 f01 = blk[dd * ld4], f23 = blk[dd * ld4 + 1];
       const float fx[4] = {f01.x, f01.z, f23.x, f23.z}, fy[4] = {f01.y, f01.w, f23.y, f23.w};
@@ -316,8 +316,9 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
       for (int dd = 0; dd < nd; ++dd) {
         const float4* src = reinterpret_cast<const float4*>(&F[k & 1][dd][u0]);
         const float4 f01 = src[0], f23 = src[1];
-        const float dn = __shfl_down_sync(0xffffffffu, g[0], 1);
-        const float right3 = (lane < 31) ? dn : 0.0f;
+        // (lane 31 gets its own g[0] back: harmless, the label arc of position 127 never
+        // exists, its factor f23.w is 0)
+        const float right3 = __shfl_down_sync(0xffffffffu, g[0], 1);
         float4 o01, o23;
         o01.x = g[0] * f01.x;  o01.y = g[1] * f01.y;       // u0:   stay, step
         o01.z = g[1] * f01.z;  o01.w = g[2] * f01.w;       // u0+1
