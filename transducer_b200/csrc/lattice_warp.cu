@@ -187,15 +187,18 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 //   g(t,u) = stay + step,            g(T-1,U-1) = 1 (the terminating blank, booked as stay)
 // Warp 0 runs the recursion on (FB, FL) pairs staged in shared memory and hands (stay, step)
 // back the same way.  The helper warps (kHelperGroups groups of four, thread <-> label position
-// u, the diagonals of a block dealt round-robin to the groups): one thread issues the bulk
-// copies of the arc terms and the alphas, kRing-1 blocks ahead; all of them turn the block
+// u, the diagonals of a block dealt round-robin to the groups) turn the block
 // after the current one into (FB, FL), write the (stay, step) of the block before it to the
 // skewed lattices stayS / stepS, and accumulate per label position sum_t stay -> pBlank[u],
 // sum_t step -> pLabel[u] in a fixed order (per group, the groups' partial sums added in
-// group order at the end).
+// group order at the end).  One thread of a last warp issues the bulk copies of the arc terms
+// and the alphas, kRing-1 blocks ahead (the proxy fence and the copy issue cost ~500 cycles,
+// which no helper warp should carry).
 // Block k holds the diagonals dTop(k) = S-1-16k down to dLo(k) = max(dTop-15, 0).
 constexpr int kHelperGroups = 4;  // helper group j takes the diagonals dd = j (mod 4) of a block
-constexpr int kGammaThreads = 32 + 128 * kHelperGroups;
+constexpr int kPerHelper = kDiag / kHelperGroups;  // diagonals of a block per helper thread
+constexpr int kCopyTid = 32 + 128 * kHelperGroups;  // first thread of the copy warp
+constexpr int kGammaThreads = kCopyTid + 32;
 
 __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     const float2* __restrict__ arcs, const float* __restrict__ alphas, int ld, i64 latStride,
@@ -257,41 +260,53 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     const uint8_t* src = smemG + (size_t)(k % kRing) * slotBytes;
     const float2* tb = reinterpret_cast<const float2*>(src);
     const float* aa = reinterpret_cast<const float*>(src + arcBytes);
-#pragma unroll 4
-    for (int dd = hg; dd < nd; dd += kHelperGroups) {
-      const int row = dTop - dd - dLo, t = dTop - dd - hu;
-      const float2 arc = tb[row * ld + hu];
-      const float a = aa[row * ld + hu], adn = aa[(row + 1) * ld + hu];
-      const float art = aa[(row + 1) * ld + hu + 1];
+    // all operands of the thread's diagonals first (clamped, unconditional), then the arithmetic:
+    // the shared-memory latency is paid once per block, not once per diagonal
+    float2 arc[kPerHelper];
+    float a[kPerHelper], adn[kPerHelper], art[kPerHelper];
+#pragma unroll
+    for (int j = 0; j < kPerHelper; ++j) {
+      const int row = dTop - min(hg + j * kHelperGroups, nd - 1) - dLo;
+      arc[j] = tb[row * ld + hu];
+      a[j] = aa[row * ld + hu];
+      adn[j] = aa[(row + 1) * ld + hu];
+      art[j] = aa[(row + 1) * ld + hu + 1];
+    }
+#pragma unroll
+    for (int j = 0; j < kPerHelper; ++j) {
+      const int dd = hg + j * kHelperGroups, t = dTop - dd - hu;
       const bool valid = hu < U && t >= 0 && t < T;
       float2 f;
-      f.x = (valid && t < T - 1) ? ex2_approx((a + arc.x) - adn) : 0.0f;
+      f.x = (valid && t < T - 1) ? ex2_approx((a[j] + arc[j].x) - adn[j]) : 0.0f;
       if (t == T - 1 && hu == U - 1) f.x = 1.0f;  // terminating blank, fed by g(T,U-1) := 1
-      f.y = (valid && hu < U - 1) ? ex2_approx((a + arc.y) - art) : 0.0f;
-      F[k & 1][dd][hu] = f;
+      f.y = (valid && hu < U - 1) ? ex2_approx((a[j] + arc[j].y) - art[j]) : 0.0f;
+      if (dd < nd) F[k & 1][dd][hu] = f;
     }
     return ok;
   };
   auto post = [&](int k) {  // helpers: (stay, step) of block k -> global, running sums
     if (hu >= U) return;
     const int dTop = S - 1 - k * kDiag, nd = min(kDiag, dTop + 1);
-#pragma unroll 4
-    for (int dd = hg; dd < nd; dd += kHelperGroups) {
-      const int d = dTop - dd, t = d - hu;
-      if (t >= 0 && t < T) {
-        const float2 g = G[k & 1][dd][hu];
-        sS[d * ld + hu] = g.x;
-        pS[d * ld + hu] = g.y;
-        accB += g.x;
-        accL += g.y;
+    float2 g[kPerHelper];
+#pragma unroll
+    for (int j = 0; j < kPerHelper; ++j) g[j] = G[k & 1][min(hg + j * kHelperGroups, nd - 1)][hu];
+#pragma unroll
+    for (int j = 0; j < kPerHelper; ++j) {
+      const int dd = hg + j * kHelperGroups, d = dTop - dd, t = d - hu;
+      if (dd < nd && t >= 0 && t < T) {
+        sS[d * ld + hu] = g[j].x;
+        pS[d * ld + hu] = g[j].y;
+        accB += g[j].x;
+        accL += g[j].y;
       }
     }
   };
 
-  int issuedN = 0;  // thread 32: blocks whose copies were issued
-  if (tid == 32)
+  const bool helper = tid >= 32 && tid < kCopyTid;
+  int issuedN = 0;  // copy thread: blocks whose copies were issued
+  if (tid == kCopyTid)
     for (; issuedN < kRing - 1; ++issuedN) issue(issuedN);
-  if (warp > 0) stage(0);
+  if (helper) stage(0);
   __syncthreads();
 
   // recursion warp: lane l owns u = 4l + r; the value crossing from u+1 is the lane's own
@@ -303,14 +318,13 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
 
   bool ok = true;
   for (int k = 0; k < nBlocks && ok; ++k) {
-    if (warp > 0) {
-      if (tid == 32) {
-        fence_proxy_async_smem();  // the slot refilled next was read two blocks ago
-        issue(issuedN++);
-      }
+    if (helper) {
       if (k > 0) post(k - 1);
       if (k + 1 < nBlocks) stage(k + 1);
-    } else {
+    } else if (tid == kCopyTid) {
+      fence_proxy_async_smem();  // the slot refilled next was read two blocks ago
+      issue(issuedN++);
+    } else if (warp == 0) {
       const int nd = min(kDiag, S - k * kDiag);
 #pragma unroll 4
       for (int dd = 0; dd < nd; ++dd) {
@@ -336,13 +350,13 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     __syncthreads();
     ok = (*(volatile int*)&abortFlag) == 0;
   }
-  if (warp > 0) {
+  if (helper) {
     if (ok) post(nBlocks - 1);
     sAcc[hg][0][hu] = accB;
     sAcc[hg][1][hu] = accL;
   }
   __syncthreads();
-  if (warp > 0 && hg == 0 && hu < U) {
+  if (helper && hg == 0 && hu < U) {
     float sb = 0.0f, sl = 0.0f;
 #pragma unroll
     for (int j = 0; j < kHelperGroups; ++j) {
@@ -353,7 +367,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     pBlank[(i64)b * maxU + hu] = ok ? sb : bad;
     pLabel[(i64)b * maxU + hu] = ok ? ((hu < U - 1) ? sl : 0.0f) : bad;
   }
-  if (!ok && tid == 32) {  // give the copies still in flight a bounded time to land
+  if (!ok && tid == kCopyTid) {  // give the copies still in flight a bounded time to land
     for (int j = max(0, min(issuedN, nBlocks) - kRing); j < min(issuedN, nBlocks); ++j) {
       const unsigned long long t1 = global_timer_ns();
       while (!mbar_try_wait(&bar[j % kRing], (j / kRing) & 1) &&
