@@ -192,6 +192,36 @@ def test_stress_grid_against_oracle():
 
 
 # ---------------------------------------------------------------------------
+# label-axis lengths around the limits of the single-warp sweeps (rows of 32/64/96/128 positions,
+# the hand-over to the block-wide kernels above 128) and of the warp Viterbi (256)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("U1", [2, 31, 32, 33, 64, 65, 96, 97, 127, 128, 129, 255, 256, 257])
+def test_label_axis_edges(U1):
+    rng = np.random.default_rng(700 + U1)
+    for T in (1, 37, 300):
+        B, V = 3, 64
+        E = rng.normal(0, 1.5, (B, T, V)).astype(np.float32)
+        P = rng.normal(0, 1.5, (B, U1, V)).astype(np.float32)
+        il = rng.integers(max(1, T // 2), T + 1, B).astype(np.int32)
+        ll = rng.integers(0, U1, B).astype(np.int32)
+        il[0], ll[0] = T, U1 - 1                      # one utterance fills the padded shape
+        labels = rng.integers(1, V, (B, U1 - 1)).astype(np.int32)
+        d = abi.case_to_device(dict(E=E, P=P, labels=labels, in_lens=il, lab_lens=ll))
+        want = O.loss_and_grads(E, P, labels, il, ll)
+        fwd = abi.loss_forward(d["E"], d["P"], d["labels"], d["il"], d["ll"])
+        eg, pg = abi.loss_backward(d["E"], d["P"], d["labels"], d["il"], d["ll"], fwd)
+        tag = (U1, T)
+        assert close_ref(npy(fwd["costs"]), want["costs"], LOSS_RTOL, 1e-4), tag
+        assert abi.rel_to_max(npy(eg), want["egrads"]) <= GRAD_TOL, tag
+        assert abi.rel_to_max(npy(pg), want["pgrads"]) <= GRAD_TOL, tag
+        got = npy(abi.viterbi_decode(d["E"], d["P"], d["il"], d["ll"]))
+        wv = O.viterbi(E, P, il, ll)
+        for b, n in enumerate(ll):
+            assert np.array_equal(got[b, :n], wv[b, :n]), tag
+
+
+# ---------------------------------------------------------------------------
 # the reference's own GPU path (its CUDA backend rebuilt for sm_100a) as a second checker
 # ---------------------------------------------------------------------------
 
