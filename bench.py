@@ -128,7 +128,15 @@ def time_cpu_path(w, budget_s, steps, warmup):
     from transducer_b200 import workloads
     impl = "reference" if O.have_reference() else "port"
     kind = "reference" if impl == "reference" else "port"
-    cores = torch.get_num_threads()
+    # all the host cores this process may use, also under torch.distributed.run, which sets
+    # OMP_NUM_THREADS=1 for its workers: torch's pool and the OpenMP runtime of the backend
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    try:
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
     probe = [t.numpy() for t in workloads.generate(w, "cpu", first=0, count=1)]
     cpu_path_step(O, probe, impl)
     t0 = time.perf_counter()
