@@ -610,7 +610,7 @@ int pow2_cols(int x) {
 // occupancies row-major [B,maxT,maxU] (through emT), the row sums with row length maxT
 // (through ebl), no nref.
 template <bool TC>
-__global__ void __launch_bounds__(1024) unskew_round_kernel(
+__global__ void __launch_bounds__(1024, 2) unskew_round_kernel(
     const float* __restrict__ stayS, const float* __restrict__ stepS,
     const float* __restrict__ LNs, const float* __restrict__ rowRef,
     const float* __restrict__ maxP, const float* __restrict__ deltas, float* __restrict__ W,
