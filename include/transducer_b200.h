@@ -71,6 +71,25 @@ int tb200_profile_enable(int on);
 int tb200_profile_reset(void);
 size_t tb200_profile_report(char* buf, size_t bufBytes);
 
+/* Device-side failure detection.  Every wait inside the kernels (on a TMA / bulk copy, an MMA
+ * completion, a pipeline stage) is bounded; a wait that runs out makes its kernel record a code
+ * in a per-device status word, poison its outputs (NaN costs, log-normalisers and gradients,
+ * labels of -1) and return normally, so the CUDA context stays usable.  tb200_check_status
+ * SYNCHRONISES the calling thread's stream, reads the word of the current device, clears it,
+ * and returns TB200_ERR_DEVICE_STATUS (message with the code in tb200_last_error()) if any
+ * kernel of this library on this device gave up since the last check, else 0.  The word is
+ * shared by all streams and threads using the device.  tb200_status_name: text for a code.
+ * tb200_selftest_wait_timeout enqueues one tiny kernel that waits, for at most the given
+ * number of microseconds, on a barrier that nothing ever completes: the next
+ * tb200_check_status must then report code 5 -- the supported way of exercising this path
+ * (it neither faults nor hangs the GPU).  The first call on a device looks up the word's
+ * address (make it outside stream capture).
+ * The reference has no device-side waits; its counterpart on the host is
+ * cudaCheck -> std::runtime_error (transducer/transducer_cuda.cu:271-278). */
+int tb200_check_status(void);
+const char* tb200_status_name(int code);
+int tb200_selftest_wait_timeout(unsigned limitMicroseconds);
+
 /* ---- the reference's three entry points ------------------------------------ */
 
 /* transducer/transducer.h:3-17 (`forward`, useCuda=true): alpha recursion.
@@ -112,9 +131,13 @@ int tb200_viterbi(const float* emissions, const float* predictions,
  * ends), so the lattice is limited to tb200_viterbi_static_max_nodes() =
  * 4 Mi nodes of batchSize*maxInputLength*maxLabelLength (and 160 Ki back-pointer words,
  * batchSize*maxLabelLength*ceil(maxInputLength/32)); larger calls return
- * TB200_ERR_WORKSPACE without touching anything.  The call performs no allocation of any
- * kind.  The first call on each device looks up the array's device address and caches it:
- * make that first call with the device current and before any stream capture begins.
+ * TB200_ERR_WORKSPACE without touching anything.  The call itself requests no memory from
+ * any allocator (no cudaMalloc / cudaMallocAsync / cudaFree, no library routine that would).
+ * The first call on each device looks up the array's device address and caches it; with the
+ * CUDA runtime's lazy module loading that first call is also when the driver brings this
+ * library's kernels and the array itself onto the device.  So make the first call per device
+ * at start-up -- with the device current, before another allocator claims the rest of the
+ * card, and before any stream capture begins -- a call with batchSize = 0 will do.
  * All calls share the one array and it keeps whatever the last call left (nothing in it
  * needs to be zero on entry), so two calls whose GPU work may overlap -- different streams,
  * different host threads -- race with each other: serialise them. */

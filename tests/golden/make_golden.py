@@ -1,7 +1,7 @@
 """Generates the committed fixtures in this folder.  Run where the reference
 checkout is available (it is NOT available where the GPU tests run):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 1. reference_kats.json -- the literal known-answer vectors of the reference's own
    tests, read as text from transducer/test.cpp (smallTest :132-165, bigTest :167-226,
@@ -135,7 +135,9 @@ def reference_runs():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference/checkout")
+    ref_root = sys.argv[1]
     kats = kats_from_reference(ref_root)
     with open(os.path.join(HERE, "reference_kats.json"), "w") as f:
         json.dump(kats, f, indent=1)

@@ -37,6 +37,31 @@ def test_reference_cpp_symbols_exported():
         assert getattr(lib, sym) is not None
 
 
+def test_reference_cuda_namespace_exported():
+    # transducer/transducer_cuda.h:7-59: cuda::cudaCheck (behind the CUDA_CHECK macro that the
+    # reference's test_cuda.cu / benchmark_cuda.cu use) and cuda::forward/backward/viterbi
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for sym in ("_ZN4cuda9cudaCheckE9cudaErrorPKci",
+                "_ZN4cuda7forwardEPKfS1_PfS2_S1_PKiS4_S4_iiiii",
+                "_ZN4cuda8backwardEPKfS1_PfS2_S2_S1_S1_PKiS4_S4_iiiii",
+                "_ZN4cuda7viterbiEPKfS1_S1_PiPKiS4_iiiii"):
+        assert getattr(lib, sym) is not None
+    hdr = open(os.path.join(ROOT, "include", "transducer_cuda.h")).read()
+    assert "#define CUDA_CHECK(err)" in hdr and "namespace cuda" in hdr
+
+
+def test_package_import_does_not_load_the_native_library():
+    """Helper modules (workloads, distributed, errors) must be importable by a process that
+    must not load the CUDA library: bench.py's CPU reference arm is such a process."""
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); import transducer_b200; "
+            "from transducer_b200 import workloads, distributed, errors; "
+            "bad = [m for m in sys.modules if m.endswith('_transducer') or m.endswith('._lib')]; "
+            "assert not bad, bad" % ROOT)
+    subprocess.run([sys.executable, "-c", code], check=True)
+
+
 def test_version_and_options_roundtrip():
     assert _lib.lib.tb200_version() >= 100
     v = ctypes.c_int(-1)

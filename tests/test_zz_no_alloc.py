@@ -10,6 +10,7 @@ import pytest
 import torch
 
 import abi
+from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +45,11 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         got = _static(E, P, LN, il, ll)
         torch.cuda.synchronize()
         assert torch.equal(got, want), (B, T, U, V)   # bit-exact, padding entries untouched in both
+        # and against the CPU oracle's `viterbi` (transducer/transducer.h:37-49) fed with the
+        # same log-normalisers: an independent implementation, not another kernel of this library
+        cpu = lambda t: t.cpu().numpy()
+        ref = O.viterbi_abi(cpu(E), cpu(P), cpu(LN), cpu(il), cpu(ll))
+        assert np.array_equal(cpu(got), ref), (B, T, U, V)
         for b in range(B):
             n = int(ll[b])
             assert (got[b, :n] > 0).all() and (got[b, n:] == -1).all()
@@ -58,5 +64,5 @@ def test_sizes_beyond_the_built_in_scratch_are_refused():
     assert rc == 3
     msg = abi.lib.tb200_last_error().decode()
     assert "exceeds the built-in scratch" in msg and "tb200_viterbi" in msg
-    # empty problems are fine and touch nothing
+    # an empty problem decodes nothing (it only performs the per-device set-up)
     assert abi.lib.tb200_viterbi_static(None, None, None, None, None, None, 0, 10, 3, 8, 0) == 0

@@ -5,6 +5,8 @@ been built, importing this module raises."""
 import ctypes
 import os
 
+from .errors import DeviceStatusError, Tb200Error, raise_for_status  # noqa: F401
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtransducer_b200.so")
 
@@ -31,6 +33,9 @@ SIGNATURES = {
     "tb200_profile_enable": (_i, [_i]),
     "tb200_profile_reset": (_i, []),
     "tb200_profile_report": (_z, [ctypes.c_char_p, _z]),
+    "tb200_check_status": (_i, []),
+    "tb200_status_name": (ctypes.c_char_p, [_i]),
+    "tb200_selftest_wait_timeout": (_i, [ctypes.c_uint]),
     "tb200_forward": (_i, [_p] * 8 + [_i] * 5),
     "tb200_backward": (_i, [_p] * 10 + [_i] * 5),
     "tb200_viterbi": (_i, [_p] * 6 + [_i] * 5),
@@ -53,17 +58,10 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn.argtypes = _args
 
 
-class Tb200Error(RuntimeError):
-    pass
-
-
 def check(rc):
     """Raise with the library's message when a C-ABI call did not return 0."""
     if rc != 0:
-        msg = lib.tb200_last_error().decode()
-        if rc in (1, 3):
-            raise ValueError(msg)
-        raise Tb200Error("tb200 error %d: %s" % (rc, msg))
+        raise_for_status(rc, lib.tb200_last_error().decode())
 
 
 def profile_report():

@@ -10,6 +10,7 @@
 
 #include <cstdint>
 #include <stdexcept>
+#include <string>
 
 #include "../../include/transducer.h"
 #include "../../include/transducer_b200.h"
@@ -134,6 +135,15 @@ PYBIND11_MODULE(_transducer, m) {
         "emissions"_a, "predictions"_a, "input_lengths"_a, "label_lengths"_a, "labels"_a,
         "batch_size"_a, "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a,
         "blank"_a, "workspace"_a, "workspace_bytes"_a);
+
+  // ---- device status (bounded waits that ran out) -----------------------------------
+  // Returns the code of tb200_check_status (0, or 5 = a kernel gave up) without throwing, so the
+  // Python layer can raise its own exception type; the text is in last_error().
+  m.def("check_status", []() { return tb200_check_status(); });
+  m.def("last_error", []() { return std::string(tb200_last_error()); });
+  m.def("status_name", [](int code) { return std::string(tb200_status_name(code)); }, "code"_a);
+  m.def("selftest_wait_timeout",
+        [](unsigned us) { check(tb200_selftest_wait_timeout(us)); }, "limit_microseconds"_a);
 
   m.attr("__version__") = "b200-" + std::to_string(tb200_version());
 }

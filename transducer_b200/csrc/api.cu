@@ -1,10 +1,13 @@
 // C ABI (include/transducer_b200.h) and the reference-compatible C++-linkage entry
 // points (include/transducer.h) on top of the kernel launchers.
+#include <atomic>
 #include <cstring>
+#include <sstream>
 #include <string>
 
 #include "../../include/transducer.h"
 #include "../../include/transducer_b200.h"
+#include "../../include/transducer_cuda.h"
 #include "api_internal.h"
 #include "kernels.h"
 #include "profile.h"
@@ -15,10 +18,12 @@ namespace {
 thread_local cudaStream_t g_stream = nullptr;
 thread_local std::string g_error;
 
+// Process-wide switches (tb200_set_option); atomics, because the stream and the error
+// message are per thread but these are shared.
 struct Options {
-  int lognorm_path = 0;
-  int grads_path = 0;
-  int grad_passes = 2;
+  std::atomic<int> lognorm_path{0};
+  std::atomic<int> grads_path{0};
+  std::atomic<int> grad_passes{2};
 };
 Options g_opt;
 
@@ -67,12 +72,10 @@ int ld_w(const Dims& d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
 
 struct LogNormWs {
   unsigned* ticket;  // alpha kernel's completion counter
-  int* status;       // [0] device error code, [1] nodes recomputed exactly
   float* split;      // exp(P) hi/lo operand of the tensor-core path
   float* maxPScratch;
   LogNormWs(Carver& c, const Dims& d) {
     ticket = c.take<unsigned>(16);
-    status = c.take<int>(16);
     maxPScratch = c.take<float>((size_t)d.B * d.maxU);
     split = c.take<float>(lognorm_umma_workspace_floats(d));
   }
@@ -103,11 +106,9 @@ struct ForwardWs {
 
 struct BackwardWs {
   float *expP, *Ws, *EMs, *W, *em, *emT, *nref, *ebl, *eBlank, *pBlank, *pLabel, *maxPScratch;
-  int* status;
   BackwardWs(Carver& c, const Dims& d) {
     const SkewGeom g = skew_geom(d);
     const size_t B = d.B, T = d.maxT, U = d.maxU, V = d.V;
-    status = c.take<int>(16);
     expP = c.take<float>(B * U * V);  // SIMT path only
     Ws = c.take<float>(B * g.stride);
     EMs = c.take<float>(B * g.stride);
@@ -150,7 +151,6 @@ void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
                     const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws,
                     bool fixup = true) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
-  TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
   const bool can = lognorm_umma_supported(E, P, d);
   if (g_opt.lognorm_path == 2 && !can)
     throw std::invalid_argument(
@@ -160,8 +160,8 @@ void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
     // the kernel needs somewhere to put the row shifts even if the caller does not want them
     float* mp = maxP ? maxP : ws.maxPScratch;
     if (!rowRef) throw std::invalid_argument("rowRef must not be null");
-    launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split, ws.status, fixup,
-                        g_stream);
+    launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split,
+                        device_status_word(), fixup, g_stream);
     return;
   }
   launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
@@ -263,31 +263,32 @@ int tb200_viterbi(const float* E, const float* P, const float* LN, int* labels,
     if (B == 0 || maxT == 0 || maxU == 0) return;
     const size_t cells = (size_t)B * maxT * maxU;
     const bool warp = viterbi_warp_supported(d);  // label axis <= 256: single-warp sweep
-    float* best = nullptr;
-    uint32_t* dec = nullptr;
-    float4* nodes = nullptr;
     const size_t decWords = warp ? viterbi_warp_decbits_words(d) : viterbi_decbits_words(d);
-    TB200_CUDA_CHECK(cudaMallocAsync((void**)&best, sizeof(float) * cells, g_stream));
-    TB200_CUDA_CHECK(cudaMallocAsync((void**)&dec, sizeof(uint32_t) * decWords, g_stream));
+    // Temporaries from the stream-ordered allocator, as the reference takes them
+    // (transducer_cuda.cu:364-369); released in stream order on every way out.
+    struct Temporaries {
+      float* best = nullptr;
+      uint32_t* dec = nullptr;
+      float4* nodes = nullptr;
+      cudaStream_t stream;
+      ~Temporaries() {
+        if (best) cudaFreeAsync(best, stream);
+        if (dec) cudaFreeAsync(dec, stream);
+        if (nodes) cudaFreeAsync(nodes, stream);
+      }
+    } tmp;
+    tmp.stream = g_stream;
+    TB200_CUDA_CHECK(cudaMallocAsync((void**)&tmp.best, sizeof(float) * cells, g_stream));
+    TB200_CUDA_CHECK(cudaMallocAsync((void**)&tmp.dec, sizeof(uint32_t) * decWords, g_stream));
     if (warp)
-      TB200_CUDA_CHECK(cudaMallocAsync((void**)&nodes, sizeof(float4) * viterbi_warp_nodes(d), g_stream));
-    auto release = [&] {
-      cudaFreeAsync(best, g_stream);
-      cudaFreeAsync(dec, g_stream);
-      if (nodes) cudaFreeAsync(nodes, g_stream);
-    };
-    try {
-      launch_maxplus(E, P, best, inLens, labLens, d, g_stream);
-      if (warp)
-        launch_viterbi_warp(E, P, LN, best, nodes, dec, labels, inLens, labLens, d, nullptr,
-                            g_stream);
-      else
-        launch_viterbi_lattice(E, P, LN, best, dec, labels, inLens, labLens, d, g_stream);
-    } catch (...) {
-      release();
-      throw;
-    }
-    release();
+      TB200_CUDA_CHECK(cudaMallocAsync((void**)&tmp.nodes, sizeof(float4) * viterbi_warp_nodes(d),
+                                       g_stream));
+    launch_maxplus(E, P, tmp.best, inLens, labLens, d, g_stream);
+    if (warp)
+      launch_viterbi_warp(E, P, LN, tmp.best, tmp.nodes, tmp.dec, labels, inLens, labLens, d,
+                          device_status_word(), g_stream);
+    else
+      launch_viterbi_lattice(E, P, LN, tmp.best, tmp.dec, labels, inLens, labLens, d, g_stream);
   });
 }
 
@@ -353,7 +354,7 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
     // reverse sweep that matches the format of the saved alphas).
     if (lattice_warp_supported(d))
       launch_alpha_warp(st.arcs, costs, st.alphasS, g, inLens, labLens, d, lossSum,
-                        lossSum ? ws.ticket : nullptr, ws.status, g_stream);
+                        lossSum ? ws.ticket : nullptr, device_status_word(), g_stream);
     else
       launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
                         d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
@@ -384,7 +385,7 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
     const SkewGeom g = skew_geom(d);
     const int ldW = ld_w(d);
     const int passes = g_opt.grad_passes;
-    const bool can = grads_umma_supported(E, egrads, d, passes);
+    const bool can = grads_umma_supported(E, P, egrads, pgrads, d, passes);
     if (g_opt.grads_path == 2 && !can)
       throw std::invalid_argument(
           "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
@@ -393,14 +394,14 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
     if (lattice_warp_supported(d)) {
       // single-warp reverse sweep: blank/label arc occupancies to the skewed lattices
       // ws.Ws / ws.EMs, then re-laid out for whichever gradient kernels follow
-      TB200_CUDA_CHECK(cudaMemsetAsync(ws.status, 0, 2 * sizeof(int), g_stream));
+      int* status = device_status_word();
       launch_gamma_warp(st.arcs, st.alphasS, g, inLens, labLens, ws.Ws, ws.EMs, ws.pBlank,
-                        ws.pLabel, d, ws.status, g_stream);
+                        ws.pLabel, d, status, g_stream);
       if (tensorCore) {
         launch_unskew_round(ws.Ws, ws.EMs, st.LNs, st.rowRef, st.maxP, deltas, ws.W, ws.emT,
                             ws.nref, ws.ebl, inLens, labLens, g, d, true, g_stream);
         launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
-                          labels, deltas, egrads, pgrads, inLens, labLens, d, passes, ws.status,
+                          labels, deltas, egrads, pgrads, inLens, labLens, d, passes, status,
                           g_stream);
         return;
       }
@@ -443,7 +444,7 @@ int tb200_viterbi_decode(const float* E, const float* P, const int* inLens,
     launch_maxplus(E, P, ws.best, inLens, labLens, d, g_stream);
     if (viterbi_warp_supported(d))
       launch_viterbi_warp(E, P, ws.LN, ws.best, ws.nodes, ws.decBits, labels, inLens, labLens, d,
-                          lw.status, g_stream);
+                          device_status_word(), g_stream);
     else
       launch_viterbi_lattice(E, P, ws.LN, ws.best, ws.decBits, labels, inLens, labLens, d,
                              g_stream);
@@ -494,3 +495,42 @@ void viterbi(const float* emissions, const float* predictions, const float* logN
   rethrow(tb200_viterbi(emissions, predictions, logNorms, labels, inputLengths, labelLengths,
                         batchSize, maxInputLength, maxLabelLength, alphabetSize, blank));
 }
+
+// ---- transducer_cuda.h-compatible namespace (transducer/transducer_cuda.h:7-59) ----------
+
+namespace cuda {
+
+void cudaCheck(cudaError_t err, const char* file, int line) {
+  if (err != cudaSuccess) {
+    std::ostringstream ess;
+    ess << '[' << file << ':' << line << "] CUDA error: " << cudaGetErrorString(err);
+    throw std::runtime_error(ess.str());
+  }
+}
+
+void forward(const float* emissions, const float* predictions, float* costs, float* alphas,
+             const float* logNorms, const int* labels, const int* inputLengths,
+             const int* labelLengths, int batchSize, int maxInputLength, int maxLabelLength,
+             int alphabetSize, int blank) {
+  rethrow(tb200_forward(emissions, predictions, costs, alphas, logNorms, labels, inputLengths,
+                        labelLengths, batchSize, maxInputLength, maxLabelLength, alphabetSize,
+                        blank));
+}
+
+void backward(const float* emissions, const float* predictions, float* egrads, float* pgrads,
+              float* lngrads, const float* alphas, const float* logNorms, const int* labels,
+              const int* inputLengths, const int* labelLengths, int batchSize,
+              int maxInputLength, int maxLabelLength, int alphabetSize, int blank) {
+  rethrow(tb200_backward(emissions, predictions, egrads, pgrads, lngrads, alphas, logNorms,
+                         labels, inputLengths, labelLengths, batchSize, maxInputLength,
+                         maxLabelLength, alphabetSize, blank));
+}
+
+void viterbi(const float* emissions, const float* predictions, const float* logNorms, int* labels,
+             const int* inputLengths, const int* labelLengths, int batchSize, int maxInputLength,
+             int maxLabelLength, int alphabetSize, int blank) {
+  rethrow(tb200_viterbi(emissions, predictions, logNorms, labels, inputLengths, labelLengths,
+                        batchSize, maxInputLength, maxLabelLength, alphabetSize, blank));
+}
+
+}  // namespace cuda

@@ -12,4 +12,10 @@ int api_fail(int code, const std::string& msg);
 // Stream selected with tb200_set_stream on the calling thread.
 cudaStream_t api_stream();
 
+// Device address, on the current device, of the library's status word (status.cu): int[4],
+// [0] first code recorded by a bounded wait that ran out since the last tb200_check_status,
+// [1] lattice nodes recomputed exactly since then.  Throws CudaError.
+int* device_status_word();
+const char* status_name(int code);
+
 }  // namespace tb200

@@ -584,6 +584,14 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   __syncthreads();
   tc_fence_after();
   if (warp == kWarpMma1) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
+  if (*abortp && threadIdx.x < kVBlock && v0 + (int)threadIdx.x < p.V) {
+    // a wait ran out (recorded in the status word): whatever this CTA wrote is incomplete, so
+    // its whole slice of both gradients becomes NaN rather than a plausible-looking number
+    const float bad = __int_as_float(0x7fc00000);
+    const int v = v0 + threadIdx.x;
+    for (int t = 0; t < p.maxT; ++t) eg[(i64)t * p.V + v] = bad;
+    for (int u = 0; u < p.maxU; ++u) pg[(i64)u * p.V + v] = bad;
+  }
 }
 
 int pow2_cols(int x) {
@@ -756,10 +764,14 @@ constexpr int kStaticSmemBound = 3 * 1024;  // barriers + per-position tables of
 int grads_umma_ld_w(Dims d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
 int grads_umma_ld_t(Dims d) { return (int)round_up64(d.maxT > 0 ? d.maxT : 1, 4); }
 
-bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes) {
+bool grads_umma_supported(const float* E, const float* P, const float* egrads,
+                          const float* pgrads, Dims d, int passes) {
   if (d.V % 4 != 0 || d.V < 32 || d.maxU < 1 || d.maxU > 128 || d.B > 65535) return false;
-  if ((reinterpret_cast<uintptr_t>(E) & 15) != 0 || (reinterpret_cast<uintptr_t>(egrads) & 15) != 0)
-    return false;
+  // E and egrads are TMA operands (16-byte base); the column owners read P and write pgrads
+  // with plain 4-byte accesses, but a caller whose P / pgrads are offset by a few bytes gets
+  // the same routing as for E: the SIMT kernels
+  for (const float* ptr : {E, P, egrads, pgrads})
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return false;
   const int Ku = (int)round_up64(d.maxU, 8);
   return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound).TB > 0;
 }
@@ -774,14 +786,10 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
   dim3 grid(div_up(ldT, 32), d.B);
   ScopedKernel sk("lattice_unskew_round", stream);
   const int smem = 12 * 32 * 33 * (int)sizeof(float);
-  static bool attrSet = false;
-  if (!attrSet) {
-    TB200_CUDA_CHECK(cudaFuncSetAttribute(unskew_round_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    TB200_CUDA_CHECK(cudaFuncSetAttribute(unskew_round_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attrSet = true;
-  }
+  // (a function attribute belongs to the device that is current when it is set: set it on every
+  // launch, it is a host-side table update)
+  TB200_CUDA_CHECK(cudaFuncSetAttribute(tensorCore ? unskew_round_kernel<true> : unskew_round_kernel<false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   if (tensorCore)
     unskew_round_kernel<true><<<grid, 1024, smem, stream>>>(stayS, stepS, LNs, rowRef, maxP, deltas, W,
                                                         emT, nref, ebl, inLens, labLens, d.maxT,

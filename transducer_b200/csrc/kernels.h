@@ -105,8 +105,8 @@ void launch_exp_rows(const float* P, float* expP, float* maxP, const int* labLen
 
 // ---- lognorm_umma.cu ----------------------------------------------------------
 // Tensor-core log-normalisers (one pass over E).  Usable when lognorm_umma_supported();
-// splitWs holds lognorm_umma_workspace_floats(d) floats, status two ints (zeroed by the
-// caller): [0] first device-side error code (0 = none), [1] nodes recomputed exactly.
+// splitWs holds lognorm_umma_workspace_floats(d) floats; status is the device status word
+// (api_internal.h): [0] first device-side error code (0 = none), [1] nodes recomputed exactly.
 bool lognorm_umma_supported(const float* E, const float* P, Dims d);
 size_t lognorm_umma_workspace_floats(Dims d);
 // Nodes whose factored sum left the fp32 range come out of the kernel as NaN; with `fixup` a
@@ -120,7 +120,8 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
 // grads_umma_supported(); passes = 1..3 selects the operand precision (see grads_umma.cu).
 int grads_umma_ld_w(Dims d);  // row length of W: maxU rounded up to 32
 int grads_umma_ld_t(Dims d);  // row length of nref / ebl / emT: maxT rounded up to 4
-bool grads_umma_supported(const float* E, const float* egrads, Dims d, int passes);
+bool grads_umma_supported(const float* E, const float* P, const float* egrads,
+                          const float* pgrads, Dims d, int passes);
 // After the reverse sweep of lattice_warp.cu: stayS/stepS/LNs (skewed) ->
 //   tensorCore: W [B,maxT,ldW] rounded to TF32, emT [B,maxU,ldT], ebl [B,ldT] (row sums of
 //               stay); rowRef -> nref = -rowRef*log2(e) [B,ldT].  W, emT and ebl are scaled by

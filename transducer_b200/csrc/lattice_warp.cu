@@ -123,8 +123,11 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   bool ok = true;
   float up = kNone;  // stepOut[3] of the lane below, one diagonal back
   for (int k = 0; k < nBlocks; ++k) {
+    // The slot refilled next was read by ALL lanes one block ago: the warp barrier orders those
+    // reads before lane 0's proxy fence and copy issue.
+    __syncwarp();
     if (lane == 0) {
-      fence_proxy_async_smem();  // the slot refilled next was read by this warp one block ago
+      fence_proxy_async_smem();
       issue(k + kRing - 1);
     }
     ok = mbar_wait(&bar[k % kRing], (k / kRing) & 1, &abortFlag, status, kStatusTimeoutTma);
@@ -491,6 +494,7 @@ __global__ void __launch_bounds__(256) viterbi_warp_kernel(
     bool ok = true;
     int kFail = 0;
     for (int k = 0; k < nBlocks; ++k) {
+      __syncwarp();  // all lanes have read the slot that is refilled next
       if (lane == 0) {
         fence_proxy_async_smem();
         issue(k + ringDepth - 1);
@@ -544,7 +548,10 @@ __global__ void __launch_bounds__(256) viterbi_warp_kernel(
     __threadfence_block();
   }
   __syncthreads();
-  if (abortFlag) return;
+  if (abortFlag) {  // a copy never landed (recorded in the status word): no path, labels = -1
+    for (int u = i; u < U - 1; u += 256) labelsOut[(i64)b * (maxU - 1) + u] = -1;
+    return;
+  }
 
   // Backtrack from (T-1,U-1) along row u in diagonal coordinates d = t + u.  Each iteration
   // consumes either one label or one 32-diagonal word of blanks, so it ends within

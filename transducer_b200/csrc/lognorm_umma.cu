@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "kernels.h"
 #include "profile.h"
@@ -41,14 +42,16 @@ namespace tb200 {
 
 namespace sm100 {
 
-CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
-                             bool atom32) {
-  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeFn encode = nullptr;
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                             const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, resolved through the runtime once per process (a pure host function
+// of the driver; the same pointer serves every device).
+static EncodeFn tensor_map_encoder() {
+  static std::atomic<EncodeFn> cached{nullptr};
+  EncodeFn encode = cached.load(std::memory_order_acquire);
   if (!encode) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -56,7 +59,15 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
     if (q != cudaDriverEntryPointSuccess || !fn)
       throw CudaError("cuTensorMapEncodeTiled is not available from this driver");
     encode = reinterpret_cast<EncodeFn>(fn);
+    cached.store(encode, std::memory_order_release);
   }
+  return encode;
+}
+
+CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                             uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
+                             bool atom32) {
+  const EncodeFn encode = tensor_map_encoder();
   CUtensorMap m;
   const cuuint64_t dims[3] = {d0, d1, d2};
   const cuuint64_t strides[2] = {stride1Bytes, stride2Bytes};
@@ -74,22 +85,13 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
 
 CUtensorMap make_tmap_f32_rows(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0) {
-  // same encoder as above; resolved once there
-  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  TB200_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-  if (q != cudaDriverEntryPointSuccess || !fn)
-    throw CudaError("cuTensorMapEncodeTiled is not available from this driver");
+  const EncodeFn encode = tensor_map_encoder();
   CUtensorMap m;
   const cuuint64_t dims[3] = {d0, d1, d2};
   const cuuint64_t strides[2] = {stride1Bytes, stride2Bytes};
   const cuuint32_t box[3] = {box0, 1, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult rc = reinterpret_cast<EncodeFn>(fn)(
+  const CUresult rc = encode(
       &m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -516,15 +518,21 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     }
     if (ok) ok = mbar_wait(&barRef, 0, abortp, p.status, kStatusTimeoutOperand);
     ok = __all_sync(0xffffffffu, ok);
+    // A warp that gave up (ok == false; the cause is in the status word) turns its sums into
+    // NaN: the nodes then carry the "recompute exactly" marker instead of stale memory.
+    const float bad = __int_as_float(0x7fc00000);
+    if (!ok) {
+#pragma unroll
+      for (int j = 0; j < kDrainCols; ++j) sum[j] = bad;
+    }
+    bool writer = true;  // does this CTA write the tile's log-normalisers?
     if (parts > 1) {
       // split tile: park the partial sums; the part that finishes last adds all of them in
       // part order (so the result does not depend on which part that is) and goes on
       float* mine = p.partial + ((size_t)(splitIdx * parts + part) * kTileM + r) * p.nPad + c0;
-      if (ok) {
 #pragma unroll
-        for (int j = 0; j < kDrainCols; ++j)
-          if (c0 + j < c1) mine[j] = sum[j];
-      }
+      for (int j = 0; j < kDrainCols; ++j)
+        if (c0 + j < c1) mine[j] = sum[j];
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
       if (warp == kDrainWarp0 && lane == 0) {
@@ -533,8 +541,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         if (sLast) p.tickets[splitIdx] = 0u;  // ready for the next launch
       }
       asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
-      if (!sLast) ok = false;  // nothing more to do here
-      if (ok) {
+      writer = sLast != 0;
+      if (writer) {
         __threadfence();
 #pragma unroll
         for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
@@ -546,9 +554,9 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         }
       }
     }
-    if (ok) {
+    if (writer) {
       const int t = t0 + r;
-      const float ref = sRef[r];
+      const float ref = ok ? sRef[r] : 0.0f;
       int flagged = 0;
       if (t < T) {
         float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
@@ -559,7 +567,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
             const float acc = sum[j];
             float ln = (logf(acc) + ref) + sMaxP[u];
             if (!(acc >= kSumLo && acc <= kSumHi)) {
-              ln = __int_as_float(0x7fc00000);  // marker: recompute exactly
+              ln = bad;  // marker: recompute exactly
               ++flagged;
             }
             out[u] = ln;

@@ -22,7 +22,8 @@ enum : int {
   kStatusTimeoutTma = 1,       // tile never landed
   kStatusTimeoutOperand = 2,   // operand stage never produced
   kStatusTimeoutMma = 3,       // MMA completion never signalled
-  kStatusTimeoutStageFree = 4  // stage never released
+  kStatusTimeoutStageFree = 4, // stage never released
+  kStatusTimeoutSelfTest = 5   // the wait of tb200_selftest_wait_timeout (never satisfied)
 };
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
@@ -70,16 +71,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false (after raising *abortFlag and recording `code`) if the
-// barrier did not flip within kWaitLimitNs or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abortFlag, int* status, int code) {
+// barrier did not flip within `limitNs` or another role already aborted.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity,
+                                                volatile int* abortFlag, int* status, int code,
+                                                unsigned long long limitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*abortFlag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limitNs) {
         *abortFlag = 1;
         if (status) atomicCAS(status, kStatusOk, code);
         return false;
@@ -87,6 +89,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   return true;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          volatile int* abortFlag, int* status, int code) {
+  return mbar_wait_limit(bar, parity, abortFlag, status, code, kWaitLimitNs);
 }
 
 // ---- TMA ------------------------------------------------------------------------

@@ -53,6 +53,7 @@ unsigned char* scratch_for_current_device(std::string* err) {
     void* p = nullptr;
     rc = cudaGetSymbolAddress(&p, g_viterbi_scratch);
     if (rc != cudaSuccess || p == nullptr) {
+      cudaGetLastError();  // consume it: the next launch check must not report this failure
       *err = std::string("cudaGetSymbolAddress(static Viterbi scratch): ") + cudaGetErrorString(rc);
       return nullptr;
     }
@@ -77,7 +78,12 @@ int tb200_viterbi_static(const float* emissions, const float* predictions, const
   Dims d{batchSize, maxInputLength, maxLabelLength, alphabetSize, blank};
   if (d.B < 0 || d.maxT < 0 || d.maxU < 0 || d.V <= 0 || blank < 0 || blank >= d.V)
     return api_fail(kErrInvalidArgument, "bad batch/length/alphabet/blank argument");
-  if (d.B == 0 || d.maxT == 0 || d.maxU == 0) return kOk;
+  if (d.B == 0 || d.maxT == 0 || d.maxU == 0) {
+    // nothing to decode, but do the per-device set-up: an empty call at start-up is how a host
+    // brings the array onto the device before its own allocator takes the rest of the card
+    std::string e0;
+    return scratch_for_current_device(&e0) ? kOk : api_fail(kErrCuda, e0);
+  }
   const size_t nodes = (size_t)d.B * d.maxT * d.maxU;
   const size_t words = viterbi_decbits_words(d);
   if (nodes > kStaticBestFloats || words > kStaticDecWords)

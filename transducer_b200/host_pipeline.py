@@ -24,8 +24,8 @@ class _Slot(object):
         self.stream = torch.cuda.Stream(device=device)
         self.shape = None
 
-    def fit(self, n, T, U, V, device):
-        if self.shape == (n, T, U, V):
+    def fit(self, n, T, U, V, device, forward_only=False):
+        if self.shape == (n, T, U, V, forward_only):
             return
         f32 = dict(device=device, dtype=torch.float32)
         i32 = dict(device=device, dtype=torch.int32)
@@ -37,14 +37,14 @@ class _Slot(object):
         self.ll = torch.empty((n,), **i32)
         self.deltas = torch.empty((n,), **f32)
         self.costs = torch.empty((n,), **f32)
-        self.eg = torch.empty((n, T, V), **f32)
-        self.pg = torch.empty((n, U, V), **f32)
+        self.eg = None if forward_only else torch.empty((n, T, V), **f32)
+        self.pg = None if forward_only else torch.empty((n, U, V), **f32)
         self.saved_bytes = _transducer.loss_saved_bytes(n, T, U, V)
         self.saved = torch.empty(max(self.saved_bytes, 1), **u8)
         self.fwd_bytes = _transducer.loss_forward_workspace_bytes(n, T, U, V)
-        self.bwd_bytes = _transducer.loss_backward_workspace_bytes(n, T, U, V)
+        self.bwd_bytes = 0 if forward_only else _transducer.loss_backward_workspace_bytes(n, T, U, V)
         self.ws = torch.empty(max(self.fwd_bytes, self.bwd_bytes, 1), **u8)
-        self.shape = (n, T, U, V)
+        self.shape = (n, T, U, V, forward_only)
 
 
 class HostLossPipeline(object):
@@ -56,6 +56,8 @@ class HostLossPipeline(object):
         slots (int): chunks in flight; 3 keeps one copying in, one computing and one
             copying out.
         device: CUDA device (default: the current one).
+        forward_only (bool): compute the costs only (no gradients; pass None for egrads and
+            pgrads).
 
     Call with host tensors (pinned memory, or the copies will not overlap):
         emissions float32 [B,T,V], predictions float32 [B,U+1,V], labels int32 [B,U],
@@ -66,7 +68,7 @@ class HostLossPipeline(object):
     to wait for the pipeline) has been synchronised.
     """
 
-    def __init__(self, blank=0, chunk=8, slots=3, device=None):
+    def __init__(self, blank=0, chunk=8, slots=3, device=None, forward_only=False):
         if not torch.cuda.is_available():
             raise RuntimeError("transducer_b200 runs on CUDA devices only")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
@@ -75,20 +77,23 @@ class HostLossPipeline(object):
         self.chunk = int(chunk)
         self.slots = [_Slot(self.device) for _ in range(int(slots))]
         self.loss_parts = None
+        self.forward_only = bool(forward_only)
 
     def __call__(self, emissions, predictions, labels, input_lengths, label_lengths,
                  costs, egrads, pgrads, deltas=None):
+        outs = (("costs", costs),) if self.forward_only else \
+            (("costs", costs), ("egrads", egrads), ("pgrads", pgrads))
         for name, t in (("emissions", emissions), ("predictions", predictions),
                         ("labels", labels), ("input_lengths", input_lengths),
-                        ("label_lengths", label_lengths), ("costs", costs),
-                        ("egrads", egrads), ("pgrads", pgrads)):
+                        ("label_lengths", label_lengths)) + outs:
             if t.device.type != "cpu":
                 raise ValueError("%s must be a host tensor" % name)
             if not t.is_contiguous():
                 raise ValueError("%s must be contiguous" % name)
         B, T, V = emissions.shape
         U = predictions.shape[1]
-        if egrads.shape != emissions.shape or pgrads.shape != predictions.shape:
+        if not self.forward_only and (egrads.shape != emissions.shape or
+                                      pgrads.shape != predictions.shape):
             raise ValueError("gradient buffers must have the shapes of their inputs")
         dev = self.device
         n_chunks = (B + self.chunk - 1) // self.chunk
@@ -104,7 +109,7 @@ class HostLossPipeline(object):
                 slot = self.slots[i % len(self.slots)]
                 slot.stream.wait_event(start)
                 with torch.cuda.stream(slot.stream):
-                    slot.fit(self.chunk, T, U, V, dev)  # views of n <= chunk rows below
+                    slot.fit(self.chunk, T, U, V, dev, self.forward_only)  # views of n <= chunk rows below
                     slot.E[:n].copy_(emissions[lo:hi], non_blocking=True)
                     slot.P[:n].copy_(predictions[lo:hi], non_blocking=True)
                     slot.labels[:n].copy_(labels[lo:hi], non_blocking=True)
@@ -120,15 +125,16 @@ class HostLossPipeline(object):
                         slot.il.data_ptr(), slot.ll.data_ptr(), slot.costs.data_ptr(),
                         self.loss_parts[i:].data_ptr(), slot.saved.data_ptr(), slot.saved_bytes,
                         n, T, U, V, self.blank, slot.ws.data_ptr(), slot.fwd_bytes)
-                    _transducer.loss_backward(
-                        slot.E.data_ptr(), slot.P.data_ptr(), slot.labels.data_ptr(),
-                        slot.il.data_ptr(), slot.ll.data_ptr(), slot.saved.data_ptr(),
-                        slot.saved_bytes, slot.deltas.data_ptr(), slot.eg.data_ptr(),
-                        slot.pg.data_ptr(), n, T, U, V, self.blank, slot.ws.data_ptr(),
-                        slot.bwd_bytes)
                     costs[lo:hi].copy_(slot.costs[:n], non_blocking=True)
-                    egrads[lo:hi].copy_(slot.eg[:n], non_blocking=True)
-                    pgrads[lo:hi].copy_(slot.pg[:n], non_blocking=True)
+                    if not self.forward_only:
+                        _transducer.loss_backward(
+                            slot.E.data_ptr(), slot.P.data_ptr(), slot.labels.data_ptr(),
+                            slot.il.data_ptr(), slot.ll.data_ptr(), slot.saved.data_ptr(),
+                            slot.saved_bytes, slot.deltas.data_ptr(), slot.eg.data_ptr(),
+                            slot.pg.data_ptr(), n, T, U, V, self.blank, slot.ws.data_ptr(),
+                            slot.bwd_bytes)
+                        egrads[lo:hi].copy_(slot.eg[:n], non_blocking=True)
+                        pgrads[lo:hi].copy_(slot.pg[:n], non_blocking=True)
             for slot in self.slots:
                 done = torch.cuda.Event()
                 done.record(slot.stream)

@@ -7,6 +7,18 @@ CUDA tensors only: there is no CPU backend and no PyTorch fallback."""
 import torch
 
 from . import _transducer
+from .errors import DeviceStatusError, raise_for_status  # noqa: F401
+
+
+def check_device_status(device=None):
+    """Synchronise torch's current stream on `device` and raise DeviceStatusError if a kernel
+    of this library gave up on one of its bounded waits there since the last check (its
+    outputs are then NaN / -1).  No counterpart in the reference, whose kernels never wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+        else torch.device(device)
+    with DeviceManager(device):
+        rc = _transducer.check_status()
+        raise_for_status(rc, _transducer.last_error() if rc else "")
 
 
 class DeviceManager(object):
@@ -37,7 +49,7 @@ class Transducer(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, emissions, predictions, labels, input_lengths, label_lengths, blank=0,
-                validate_lengths=True):
+                validate_lengths=True, check_status=False):
         certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
                        validate_lengths)
         device = emissions.device
@@ -58,11 +70,15 @@ class Transducer(torch.autograd.Function):
                 input_lengths.data_ptr(), label_lengths.data_ptr(), costs.data_ptr(),
                 loss_sum.data_ptr(), saved.data_ptr(), saved_bytes, B, T, U, V, blank,
                 ws.data_ptr(), nbytes)
+            if check_status:
+                rc = _transducer.check_status()
+                raise_for_status(rc, _transducer.last_error() if rc else "")
         # `saved` replaces the reference's saved alphas/log_norms/expEs/expPs/expLNs
         # (torch_binding.py:52-55); exp(emissions) is recomputed, never stored
         ctx.save_for_backward(emissions, predictions, saved, labels, input_lengths,
                               label_lengths)
         ctx.blank = blank
+        ctx.check_status = check_status
         ctx.mark_non_differentiable(loss_sum)
         return costs, loss_sum
 
@@ -83,7 +99,10 @@ class Transducer(torch.autograd.Function):
                 input_lengths.data_ptr(), label_lengths.data_ptr(), saved.data_ptr(),
                 saved.numel(), deltas.data_ptr(), egrads.data_ptr(), pgrads.data_ptr(),
                 B, T, U, V, ctx.blank, ws.data_ptr(), nbytes)
-        return egrads, pgrads, None, None, None, None, None
+            if ctx.check_status:
+                rc = _transducer.check_status()
+                raise_for_status(rc, _transducer.last_error() if rc else "")
+        return egrads, pgrads, None, None, None, None, None, None
 
 
 class TransducerLoss(torch.nn.Module):
@@ -101,16 +120,26 @@ class TransducerLoss(torch.nn.Module):
             pass False to skip it when the lengths are known to fit -- the call then only
             enqueues work (and can be captured in a CUDA graph).  No counterpart in the
             reference.
+        check_status (bool, optional): after the forward and the backward kernels, wait for
+            them and raise DeviceStatusError if one of them gave up on a bounded wait (see
+            check_device_status).  Default: the value of validate_lengths -- the reference-style
+            call synchronises once per call anyway; the enqueue-only call never does.
+        reduction (str, optional): "none" (default; the reference returns the per-utterance
+            costs, transducer/torch_binding.py:108-128), "sum" or "mean" over the batch.
 
     After each call ``last_loss_sum`` holds a detached 1-element device tensor with
     sum_b costs[b], produced by the kernel itself; a data-parallel caller can
     all-reduce it without launching a reduction.
     """
 
-    def __init__(self, blank=0, validate_lengths=True):
+    def __init__(self, blank=0, validate_lengths=True, check_status=None, reduction="none"):
         super(TransducerLoss, self).__init__()
+        if reduction not in ("none", "sum", "mean"):
+            raise ValueError("reduction must be 'none', 'sum' or 'mean'")
         self.blank = blank
         self.validate_lengths = validate_lengths
+        self.check_status = validate_lengths if check_status is None else bool(check_status)
+        self.reduction = reduction
         self.last_loss_sum = None
 
     def forward(self, emissions, predictions, labels, input_lengths, label_lengths):
@@ -124,8 +153,12 @@ class TransducerLoss(torch.nn.Module):
         """
         costs, loss_sum = Transducer.apply(
             emissions, predictions, labels, input_lengths, label_lengths, self.blank,
-            self.validate_lengths)
+            self.validate_lengths, self.check_status)
         self.last_loss_sum = loss_sum
+        if self.reduction == "sum":
+            return costs.sum()
+        if self.reduction == "mean":
+            return costs.mean()
         return costs
 
     @torch.no_grad()
@@ -137,7 +170,8 @@ class TransducerLoss(torch.nn.Module):
         B, T, V = emissions.shape
         U = predictions.shape[1]
         labels = torch.empty((B, U - 1), device=device, dtype=torch.int32)
-        certify_inputs(emissions, predictions, labels, input_lengths, label_lengths)
+        certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
+                       self.validate_lengths)
         emissions = emissions.contiguous()
         predictions = predictions.contiguous()
         with DeviceManager(device):
@@ -147,6 +181,9 @@ class TransducerLoss(torch.nn.Module):
                 emissions.data_ptr(), predictions.data_ptr(), input_lengths.data_ptr(),
                 label_lengths.data_ptr(), labels.data_ptr(), B, T, U, V, self.blank,
                 ws.data_ptr(), nbytes)
+            if self.check_status:
+                rc = _transducer.check_status()
+                raise_for_status(rc, _transducer.last_error() if rc else "")
         return labels
 
 
