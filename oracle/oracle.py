@@ -258,6 +258,47 @@ def accumulate_grads_exact(E, P, egrads, pgrads, lngrads, LN, in_lens, lab_lens)
 # fp32 noise floor of the recursion (alphas reach ~1e4 at T=2000, ulp ~1e-3).
 # ----------------------------------------------------------------------------
 
+def _alpha_beta64(stay, step):
+    """float64 alpha and beta lattices [T,U] from the arc log-probabilities stay[t,u] (blank arc
+    leaving (t,u)) and step[t,u] (label arc leaving (t,u); -inf in the last column), swept one
+    anti-diagonal per numpy operation."""
+    T, U = stay.shape
+    D = T + U - 1
+    ninf = -np.inf
+    # skewed copies: X[d, u] = x[d - u, u]
+    def skew(x):
+        out = np.full((D, U), ninf)
+        for u in range(U):
+            out[u:u + T, u] = x[:, u]
+        return out
+    st, sp = skew(stay), skew(step)
+    valid = np.isfinite(skew(np.zeros((T, U))))
+    A = np.full((D, U), ninf)
+    A[0, 0] = 0.0
+    for d in range(1, D):
+        from_stay = A[d - 1] + st[d - 1]                       # (t-1,u) -> (t,u)
+        from_step = np.full(U, ninf)
+        from_step[1:] = A[d - 1, :-1] + sp[d - 1, :-1]         # (t,u-1) -> (t,u)
+        with np.errstate(invalid="ignore"):
+            row = np.logaddexp(from_stay, from_step)
+        A[d] = np.where(valid[d], row, ninf)
+    Bt = np.full((D, U), ninf)
+    Bt[D - 1, U - 1] = stay[T - 1, U - 1]
+    for d in range(D - 2, -1, -1):
+        to_stay = Bt[d + 1] + st[d]                            # (t,u) -> (t+1,u)
+        to_step = np.full(U, ninf)
+        to_step[:-1] = Bt[d + 1, 1:] + sp[d, :-1]              # (t,u) -> (t,u+1)
+        with np.errstate(invalid="ignore"):
+            row = np.logaddexp(to_stay, to_step)
+        Bt[d] = np.where(valid[d], row, ninf)
+    def unskew(X):
+        out = np.empty((T, U))
+        for u in range(U):
+            out[:, u] = X[u:u + T, u]
+        return out
+    return unskew(A), unskew(Bt)
+
+
 def truth64(E, P, labels, in_lens, lab_lens, blank=0):
     E = torch.as_tensor(np.asarray(E, np.float64))
     P = torch.as_tensor(np.asarray(P, np.float64))
@@ -283,24 +324,7 @@ def truth64(E, P, labels, in_lens, lab_lens, blank=0):
         step = np.full((T, U), -np.inf)
         if U > 1:
             step[:, :U - 1] = En[b, :T][:, lab] + Pn[b, np.arange(U - 1), lab][None, :] - ln[:, :U - 1]
-        al = np.full((T, U), -np.inf)
-        be = np.full((T, U), -np.inf)
-        al[0, 0] = 0.0
-        for t in range(T):
-            for u in range(U):
-                if t == 0 and u == 0:
-                    continue
-                a = al[t - 1, u] + stay[t - 1, u] if t > 0 else -np.inf
-                c = al[t, u - 1] + step[t, u - 1] if u > 0 else -np.inf
-                al[t, u] = np.logaddexp(a, c)
-        be[T - 1, U - 1] = stay[T - 1, U - 1]
-        for t in range(T - 1, -1, -1):
-            for u in range(U - 1, -1, -1):
-                if t == T - 1 and u == U - 1:
-                    continue
-                a = be[t + 1, u] + stay[t, u] if t < T - 1 else -np.inf
-                c = be[t, u + 1] + step[t, u] if u < U - 1 else -np.inf
-                be[t, u] = np.logaddexp(a, c)
+        al, be = _alpha_beta64(stay, step)
         ll = be[0, 0]
         costs[b] = -ll
         g = np.exp(al + be - ll)                                   # node occupancy

@@ -4,11 +4,20 @@ every utterance of every configuration goes through the C ABI and is compared wi
 oracle (the reference's own CPU backend where it was built, else its restatement).
 
 Bars: per-utterance losses within 1e-4 relative, gradients within 1e-3 of the gradient's largest
-magnitude, Viterbi labels bit-exact.  The oracle's own fp32 recursion is noisy at T = 2000 (its
-distance to a float64 evaluation is measured here for one utterance per configuration and
-reported beside ours): where our distance to the oracle exceeds 1e-3 but stays within twice
-that floor, the test reports XFAIL instead of FAIL; beyond that it fails.
+magnitude, Viterbi labels bit-exact.
 
+The gradient bar needs a third party.  The reference carries its alphas in fp32 at a magnitude
+of 1e4 after 2000 frames (one ulp = 1e-3), and its gradients are measurably noisy there: its CPU
+backend sits 1e-3 .. 6e-3 (of the gradient's maximum) away from a float64 evaluation of the same
+formulas, and its own CUDA backend sits up to 2.5e-3 away from its CPU backend.  No
+implementation can be within 1e-3 of a result that is itself 5e-3 from the exact value, except
+by reproducing its rounding errors bit for bit.  So every utterance is also evaluated in float64
+(oracle.truth64) and the tests assert
+  * strictly: this library is within 1e-3 of the float64 gradients (it is ~1e-4: its alphas are
+    stored relative to per-block offsets), and its losses within 1e-4 of the oracle's;
+  * the bar itself against the oracle: where the distance exceeds 1e-3 but stays within 1.5x the
+    oracle's OWN distance to float64 on the same utterances, the test reports XFAIL with the
+    numbers; beyond that it fails.
 Set TB200_PARITY_REPORT=<path> to have the measured distances written there as JSON."""
 import json
 import os
@@ -47,17 +56,6 @@ def report(row):
         json.dump(rows, f, indent=1)
 
 
-def device_distance(got, want_np):
-    """(max|got - want|, max|want|) in float64, evaluated on the device one utterance at a
-    time (the arrays are gigabytes)."""
-    diff, mag = 0.0, 0.0
-    for b in range(got.shape[0]):
-        w = torch.from_numpy(np.ascontiguousarray(want_np[b])).cuda().double()
-        diff = max(diff, float((got[b].double() - w).abs().max()))
-        mag = max(mag, float(w.abs().max()))
-    return diff, mag
-
-
 def loss_rel(got, want):
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     inf = np.isinf(want)
@@ -65,8 +63,9 @@ def loss_rel(got, want):
     return float((np.abs(got[~inf] - want[~inf]) / np.maximum(np.abs(want[~inf]), 1e-30)).max())
 
 
-def fwd_bwd_against_oracle(w, floor_utt=1):
-    """Whole configuration `w` (forward + backward, one call each) against the oracle."""
+def fwd_bwd_against_oracle(w):
+    """Whole configuration `w` (forward + backward, one call each) against the oracle, the
+    float64 evaluation and, where it was built, the reference's own CUDA backend."""
     torch.cuda.empty_cache()
     E, P, labels, il, ll = workloads.generate(w, "cuda")
     fwd = abi.loss_forward(E, P, labels, il, ll, blank=w.blank)
@@ -74,26 +73,37 @@ def fwd_bwd_against_oracle(w, floor_utt=1):
     torch.cuda.synchronize()
     abi.check(abi.lib.tb200_check_status())
     costs = npy(fwd["costs"])
-    l_err, e_diff, e_mag, p_diff, p_mag = 0.0, 0.0, 0.0, 0.0, 0.0
+    have_cuda_ref = O.have_reference_cuda() and E.numel() < 2 ** 31
+    names = ("ours_vs_oracle", "ours_vs_fp64", "oracle_vs_fp64", "refcuda_vs_oracle")
+    dist = {n: {"e": 0.0, "p": 0.0} for n in names}
+    l_err, l_err64, l_oracle64 = 0.0, 0.0, 0.0
+
+    def rel(got, want):   # one utterance, on the device, float64
+        w64 = torch.as_tensor(np.ascontiguousarray(want)).cuda().double()
+        return float((got.double() - w64).abs().max() / w64.abs().max())
+
     step = 8
     for lo in range(0, w.B, step):
         sl = slice(lo, min(w.B, lo + step))
-        want = O.loss_and_grads(npy(E[sl]), npy(P[sl]), npy(labels[sl]), npy(il[sl]), npy(ll[sl]),
-                                blank=w.blank, impl=IMPL)
+        host = [npy(t[sl]) for t in (E, P, labels, il, ll)]
+        want = O.loss_and_grads(*host, blank=w.blank, impl=IMPL)
         l_err = max(l_err, loss_rel(costs[sl], want["costs"]))
-        d, m = device_distance(eg[sl], want["egrads"])
-        e_diff, e_mag = max(e_diff, d), max(e_mag, m)
-        d, m = device_distance(pg[sl], want["pgrads"])
-        p_diff, p_mag = max(p_diff, d), max(p_mag, m)
-        if lo <= floor_utt < lo + step:
-            k = floor_utt - lo
-            one = slice(floor_utt, floor_utt + 1)
-            truth = O.truth64(npy(E[one]), npy(P[one]), npy(labels[one]), npy(il[one]), npy(ll[one]),
-                              blank=w.blank)
-            e_floor = abi.rel_to_max(want["egrads"][k:k + 1], truth["egrads"])
-            p_floor = abi.rel_to_max(want["pgrads"][k:k + 1], truth["pgrads"])
-            e_ours64 = abi.rel_to_max(npy(eg[one]), truth["egrads"])
-            p_ours64 = abi.rel_to_max(npy(pg[one]), truth["pgrads"])
+        rc = O.loss_and_grads_cuda(E[sl], P[sl], labels[sl], il[sl], ll[sl], blank=w.blank) \
+            if have_cuda_ref else None
+        for k in range(sl.stop - lo):
+            b = lo + k
+            tr = O.truth64(*[h[k:k + 1] for h in host], blank=w.blank)
+            for key, ours, theirs, truth, ref in (("e", eg, want["egrads"], tr["egrads"], "egrads"),
+                                                  ("p", pg, want["pgrads"], tr["pgrads"], "pgrads")):
+                o_dev = torch.as_tensor(np.ascontiguousarray(theirs[k])).cuda()
+                dist["ours_vs_oracle"][key] = max(dist["ours_vs_oracle"][key], rel(ours[b], theirs[k]))
+                dist["ours_vs_fp64"][key] = max(dist["ours_vs_fp64"][key], rel(ours[b], truth[0]))
+                dist["oracle_vs_fp64"][key] = max(dist["oracle_vs_fp64"][key], rel(o_dev, truth[0]))
+                if rc is not None:
+                    dist["refcuda_vs_oracle"][key] = max(dist["refcuda_vs_oracle"][key],
+                                                         rel(rc[ref][k], theirs[k]))
+            l_err64 = max(l_err64, abs(float(costs[b]) - tr["costs"][0]) / tr["costs"][0])
+            l_oracle64 = max(l_oracle64, abs(float(want["costs"][k]) - tr["costs"][0]) / tr["costs"][0])
     # size-independent properties on the full batch
     assert np.isclose(npy(fwd["loss_sum"])[0], costs.sum(), rtol=1e-5)
     for b in range(w.B):   # padding exactly zero
@@ -101,17 +111,24 @@ def fwd_bwd_against_oracle(w, floor_utt=1):
             assert float(eg[b, int(il[b]):].abs().max()) == 0.0
         if int(ll[b]) + 1 < w.U + 1:
             assert float(pg[b, int(ll[b]) + 1:].abs().max()) == 0.0
-    row = {"config": w.name, "utterances": w.B, "oracle": IMPL, "loss_rel_max": l_err,
-           "egrad_rel_to_max": e_diff / e_mag, "pgrad_rel_to_max": p_diff / p_mag,
-           "oracle_vs_fp64_egrad": e_floor, "oracle_vs_fp64_pgrad": p_floor,
-           "ours_vs_fp64_egrad": e_ours64, "ours_vs_fp64_pgrad": p_ours64, "floor_utterance": floor_utt}
+    row = {"config": w.name, "utterances": w.B, "oracle": IMPL, "loss_rel_max_vs_oracle": l_err,
+           "loss_rel_max_vs_fp64": l_err64, "oracle_loss_rel_max_vs_fp64": l_oracle64}
+    for n in names:
+        if n != "refcuda_vs_oracle" or have_cuda_ref:
+            row[n + "_egrad"], row[n + "_pgrad"] = dist[n]["e"], dist[n]["p"]
     report(row)
     assert l_err <= LOSS_RTOL, row
-    for err, floor in ((row["egrad_rel_to_max"], e_floor), (row["pgrad_rel_to_max"], p_floor)):
+    assert dist["ours_vs_fp64"]["e"] <= GRAD_TOL and dist["ours_vs_fp64"]["p"] <= GRAD_TOL, row
+    for key in ("e", "p"):
+        err, floor = dist["ours_vs_oracle"][key], dist["oracle_vs_fp64"][key]
         if err > GRAD_TOL:
-            assert err <= 2 * floor, row   # beyond the oracle's own noise: a real failure
-            pytest.xfail("gradient distance %.2e above 1e-3 but within twice the oracle's own "
-                         "distance to float64 (%.2e)" % (err, floor))
+            assert err <= 1.5 * floor, row   # more than the oracle's own noise: a real failure
+    worst = max(dist["ours_vs_oracle"].values())
+    if worst > GRAD_TOL:
+        pytest.xfail("distance to the oracle %.2e above 1e-3, within the oracle's own distance to "
+                     "float64 (%.2e / %.2e); ours to float64: %.2e / %.2e"
+                     % (worst, dist["oracle_vs_fp64"]["e"], dist["oracle_vs_fp64"]["p"],
+                        dist["ours_vs_fp64"]["e"], dist["ours_vs_fp64"]["p"]))
 
 
 @pytest.mark.parametrize("name", ["c2_v100", "c2_v1000", "c2_v2000", "c2_v10000"])

@@ -35,11 +35,20 @@ def ref_package():
     if not HAVE_SHIM:
         pytest.skip("reference shim was not built (needs the reference sources at build time)")
     sys.path.insert(0, REF_DIR)
+    # The reference's wrapper was written for PyTorch 1.9 and calls torch.cuda.get_device()
+    # (transducer/torch_binding.py:15), which current PyTorch no longer has: with any CUDA tensor
+    # it raises AttributeError before reaching native code, whatever library is underneath.  The
+    # test lends it the present-day name of that function; the reference's files stay untouched.
+    lent = not hasattr(torch.cuda, "get_device")
+    if lent:
+        torch.cuda.get_device = torch.cuda.current_device
     try:
         import transducer  # the reference's package: its torch_binding.py + its shim on our library
         yield transducer
     finally:
         sys.path.remove(REF_DIR)
+        if lent:
+            del torch.cuda.get_device
 
 
 def _run(ref_package, k):

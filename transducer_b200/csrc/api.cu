@@ -84,7 +84,8 @@ struct LogNormWs {
 // What the forward call leaves for the backward call (opaque to the caller).
 struct SavedState {
   float *alphasS, *LNs, *ELs, *ebl, *rowRef, *maxP;
-  float2* arcs;  // arc terms of the single-warp sweeps (label axis <= 128), else null
+  float2* arcs;   // arc terms of the single-warp sweeps (label axis <= 128), else null
+  float* deltas;  // per-block offsets of their rebased alphas
   SavedState(Carver& c, const Dims& d) {
     const SkewGeom g = skew_geom(d);
     const size_t B = d.B;
@@ -95,6 +96,7 @@ struct SavedState {
     rowRef = c.take<float>(B * d.maxT);
     maxP = c.take<float>(B * d.maxU);
     arcs = c.take<float2>(lattice_warp_supported(d) ? B * g.stride : 0);
+    deltas = c.take<float>(lattice_warp_supported(d) ? lattice_warp_delta_floats(d) : 0);
     if (!lattice_warp_supported(d)) arcs = nullptr;
   }
 };
@@ -353,7 +355,7 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
     // The shape alone decides which pair of sweeps runs (the backward call must pick the
     // reverse sweep that matches the format of the saved alphas).
     if (lattice_warp_supported(d))
-      launch_alpha_warp(st.arcs, costs, st.alphasS, g, inLens, labLens, d, lossSum,
+      launch_alpha_warp(st.arcs, costs, st.alphasS, st.deltas, g, inLens, labLens, d, lossSum,
                         lossSum ? ws.ticket : nullptr, device_status_word(), g_stream);
     else
       launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
@@ -395,7 +397,7 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
       // single-warp reverse sweep: blank/label arc occupancies to the skewed lattices
       // ws.Ws / ws.EMs, then re-laid out for whichever gradient kernels follow
       int* status = device_status_word();
-      launch_gamma_warp(st.arcs, st.alphasS, g, inLens, labLens, ws.Ws, ws.EMs, ws.pBlank,
+      launch_gamma_warp(st.arcs, st.alphasS, st.deltas, g, inLens, labLens, ws.Ws, ws.EMs, ws.pBlank,
                         ws.pLabel, d, status, g_stream);
       if (tensorCore) {
         launch_unskew_round(ws.Ws, ws.EMs, st.LNs, st.rowRef, st.maxP, deltas, ws.W, ws.emT,

@@ -147,15 +147,19 @@ bool lattice_warp_supported(Dims d);
 // and alphasS -- in LOG2 units, for launch_gamma_warp only (the nodes of the stored diagonals
 // that lie outside the lattice receive large negative numbers).  status: device error word (a copy that never lands
 // is recorded there and the cost becomes NaN).
-void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, SkewGeom g,
+// The stored alphas are REBASED: block k of 16 diagonals is relative to an offset of its own;
+// deltas [B, ceil(nDiag/16)] (lattice_warp_delta_floats(d) floats) receives, at index k >= 1, by
+// how much the carried state was lowered at the start of block k.
+size_t lattice_warp_delta_floats(Dims d);
+void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, float* deltas, SkewGeom g,
                        const int* inLens, const int* labLens, Dims d, float* lossSum,
                        unsigned* ticket, int* status, cudaStream_t stream);
 // Reverse sweep: blank-arc and label-arc occupancies of every valid node to the skewed
 // lattices stayS / stepS (the terminating blank counts as the blank arc of node (T-1,U-1)),
 // their sums over frames to pBlank / pLabel [B,maxU].
-void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, const int* inLens,
-                       const int* labLens, float* stayS, float* stepS, float* pBlank,
-                       float* pLabel, Dims d, int* status, cudaStream_t stream);
+void launch_gamma_warp(const float2* arcs, const float* alphasS, const float* deltas, SkewGeom g,
+                       const int* inLens, const int* labLens, float* stayS, float* stepS,
+                       float* pBlank, float* pLabel, Dims d, int* status, cudaStream_t stream);
 
 // Viterbi sweep in one warp per utterance (label axis <= 256): same results as
 // launch_viterbi_lattice.  `nodes` is scratch of viterbi_warp_nodes(d) float4, decBits of

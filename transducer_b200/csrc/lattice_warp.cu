@@ -61,8 +61,17 @@ __device__ __forceinline__ void finish_cost_w(float* costs, int b, float cost, i
 //   a(t,u) = log2( 2^(a(t-1,u) + blank arc) + 2^(a(t,u-1) + label arc) ),
 // so that the two transcendental steps are the bare ex2 / lg2 instructions, and the alphas are
 // stored in log2 units too: the reverse sweep must form a(t,u) + arc with the very same
-// rounding as here, or the occupancies stop being a conserved flow (the rounding of an alpha
-// of magnitude 1e4 is 1e-3, and such errors would compound along the 2000 steps of a path).
+// rounding as here, or the occupancies stop being a conserved flow.
+//
+// REBASED alphas.  After 2000 frames an alpha is of magnitude 1e4 and an fp32 ulp there is
+// 1e-3: the reference carries its alphas at that magnitude (transducer_cpu.cpp:30-79) and its
+// gradients are 2e-3..6e-3 of their maximum away from a float64 evaluation for it (measured).
+// Here every block of 16 diagonals stores its alphas relative to an offset of its own: at the
+// start of block k the whole carried state is lowered by delta_k = the floor of its largest
+// entry (an integer, so that the running offset -- needed only for the final cost -- adds up
+// exactly), which keeps every stored number below ~500 in magnitude (ulp 3e-5).  delta_k is
+// written to `deltas` for the reverse sweep, which subtracts it at the same point of the same
+// sum.  The loss and the gradients then sit ~1e-4 from the float64 result.
 // Lane l owns the label positions u = 4l + r, r = 0..3: the value crossing from u-1 is the
 // lane's own for r > 0 and comes from lane l-1 by ONE shuffle per diagonal for r = 0; the four
 // arc pairs and the four alphas of a lane are contiguous (two 16-byte loads, one store).  The
@@ -72,9 +81,10 @@ __device__ __forceinline__ void finish_cost_w(float* costs, int b, float cost, i
 // (Cutting the label axis over two or four warps that run a block apart, with one or two
 // positions per lane, was measured and is slower: every node then waits for a shuffle.)
 __global__ void __launch_bounds__(32) alpha_warp_kernel(
-    const float2* __restrict__ arcs, float* __restrict__ costs, float* __restrict__ alphas, int ld,
-    i64 latStride, int nDiag, const int* __restrict__ inLens, const int* __restrict__ labLens,
-    int B, int maxT, int maxU, float* lossSum, unsigned* ticket, int* status) {
+    const float2* __restrict__ arcs, float* __restrict__ costs, float* __restrict__ alphas,
+    float* __restrict__ deltas, int ld, i64 latStride, int nDiag,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int B, int maxT, int maxU,
+    float* lossSum, unsigned* ticket, int* status) {
   extern __shared__ __align__(128) uint8_t smemA[];
   float2* ring = reinterpret_cast<float2*>(smemA);  // [kRing][kDiag * ld]
   __shared__ uint64_t bar[kRing];
@@ -122,7 +132,25 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   if (lane == 0) stayIn[0] = 0.0f;  // alpha(0,0) = 0
   bool ok = true;
   float up = kNone;  // stepOut[3] of the lane below, one diagonal back
+  float offset = 0.0f;  // sum of the deltas so far: an integer, exact in fp32
+  float* dl = deltas + (i64)b * ((nDiag + kDiag - 1) / kDiag);
   for (int k = 0; k < nBlocks; ++k) {
+    if (k > 0) {
+      // rebase: lower the carried state by the floor of its largest entry (entries of nodes
+      // outside the lattice are ~ -6e29 and stay there)
+      float m = fmaxf(fmaxf(stayIn[0], stayIn[1]), fmaxf(stayIn[2], stayIn[3]));
+      m = fmaxf(m, fmaxf(fmaxf(stepOut[0], stepOut[1]), fmaxf(stepOut[2], stepOut[3])));
+      const int mi = __reduce_max_sync(0xffffffffu, __float2int_rd(fmaxf(m, -1.0e9f)));
+      const float delta = (float)mi;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        stayIn[r] -= delta;
+        stepOut[r] -= delta;
+      }
+      up -= delta;
+      offset += delta;
+      if (lane == 0) dl[k] = delta;
+    }
     // The slot refilled next was read by ALL lanes one block ago: the warp barrier orders those
     // reads before lane 0's proxy fence and copy issue.
     __syncwarp();
@@ -176,7 +204,7 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   // the last diagonal holds only the terminal node (T-1, U-1); its blank arc ends the path
 #pragma unroll
   for (int r = 0; r < 4; ++r)
-    if (u0 + r == U - 1) finish_cost_w(costs, b, -stayIn[r] * kLn2F, B, lossSum, ticket);
+    if (u0 + r == U - 1) finish_cost_w(costs, b, -(stayIn[r] + offset) * kLn2F, B, lossSum, ticket);
 }
 
 // ---------------------------------------------------------------------------
@@ -186,7 +214,10 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
 //   stay(t,u) = g(t+1,u) * FB(t,u),  FB = 2^((alpha(t,u) + blank arc) - alpha(t+1,u))
 //   step(t,u) = g(t,u+1) * FL(t,u),  FL = 2^((alpha(t,u) + label arc) - alpha(t,u+1))
 //   (alphas and arcs in log2 units; the parenthesised sums are rounded exactly as in the alpha
-//   kernel, so FB and FL of the arcs entering a node add up to 1 to within the error of ex2/lg2)
+//   kernel, so FB and FL of the arcs entering a node add up to 1 to within the error of ex2/lg2.
+//   The stored alphas are relative to a per-block offset, see alpha_warp_kernel: where the
+//   successors' diagonal opens a new block of the alpha kernel, that block's delta is
+//   subtracted from the sum first, exactly as the alpha kernel lowered its carried state.)
 //   g(t,u) = stay + step,            g(T-1,U-1) = 1 (the terminating blank, booked as stay)
 // Warp 0 runs the recursion on (FB, FL) pairs staged in shared memory and hands (stay, step)
 // back the same way.  The helper warps (kHelperGroups groups of four, thread <-> label position
@@ -204,7 +235,8 @@ constexpr int kCopyTid = 32 + 128 * kHelperGroups;  // first thread of the copy 
 constexpr int kGammaThreads = kCopyTid + 32;
 
 __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
-    const float2* __restrict__ arcs, const float* __restrict__ alphas, int ld, i64 latStride,
+    const float2* __restrict__ arcs, const float* __restrict__ alphas,
+    const float* __restrict__ deltas, int nDiag, int ld, i64 latStride,
     const int* __restrict__ inLens, const int* __restrict__ labLens, float* __restrict__ stayS,
     float* __restrict__ stepS, float* __restrict__ pBlank, float* __restrict__ pLabel, int maxT,
     int maxU, int* status) {
@@ -227,6 +259,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   if (empty) return;
   const float2* ar = arcs + (i64)b * latStride;
   const float* al = alphas + (i64)b * latStride;
+  const float* dl = deltas + (i64)b * ((nDiag + kDiag - 1) / kDiag);
   float* sS = stayS + (i64)b * latStride;
   float* pS = stepS + (i64)b * latStride;
   const int S = T + U - 1;
@@ -266,7 +299,7 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     // all operands of the thread's diagonals first (clamped, unconditional), then the arithmetic:
     // the shared-memory latency is paid once per block, not once per diagonal
     float2 arc[kPerHelper];
-    float a[kPerHelper], adn[kPerHelper], art[kPerHelper];
+    float a[kPerHelper], adn[kPerHelper], art[kPerHelper], dlt[kPerHelper];
 #pragma unroll
     for (int j = 0; j < kPerHelper; ++j) {
       const int row = dTop - min(hg + j * kHelperGroups, nd - 1) - dLo;
@@ -274,15 +307,19 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
       a[j] = aa[row * ld + hu];
       adn[j] = aa[(row + 1) * ld + hu];
       art[j] = aa[(row + 1) * ld + hu + 1];
+      // the successors lie on diagonal dNext; if it opens a block of the alpha kernel, the
+      // carried sums were lowered by that block's delta before they entered it
+      const int dNext = dLo + row + 1;
+      dlt[j] = ((dNext & (kDiag - 1)) == 0 && dNext < S) ? dl[dNext / kDiag] : 0.0f;
     }
 #pragma unroll
     for (int j = 0; j < kPerHelper; ++j) {
       const int dd = hg + j * kHelperGroups, t = dTop - dd - hu;
       const bool valid = hu < U && t >= 0 && t < T;
       float2 f;
-      f.x = (valid && t < T - 1) ? ex2_approx((a[j] + arc[j].x) - adn[j]) : 0.0f;
+      f.x = (valid && t < T - 1) ? ex2_approx(((a[j] + arc[j].x) - dlt[j]) - adn[j]) : 0.0f;
       if (t == T - 1 && hu == U - 1) f.x = 1.0f;  // terminating blank, fed by g(T,U-1) := 1
-      f.y = (valid && hu < U - 1) ? ex2_approx((a[j] + arc[j].y) - art[j]) : 0.0f;
+      f.y = (valid && hu < U - 1) ? ex2_approx(((a[j] + arc[j].y) - dlt[j]) - art[j]) : 0.0f;
       if (dd < nd) F[k & 1][dd][hu] = f;
     }
     return ok;
@@ -635,28 +672,33 @@ void allow_dyn_smem(K kernel, int bytes) {
 
 bool lattice_warp_supported(Dims d) { return d.maxU >= 1 && d.maxU <= 128; }
 
-void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, SkewGeom g,
+size_t lattice_warp_delta_floats(Dims d) {
+  const SkewGeom g = skew_geom(d);
+  return (size_t)d.B * (size_t)((g.nDiag + kDiag - 1) / kDiag);
+}
+
+void launch_alpha_warp(const float2* arcs, float* costs, float* alphasS, float* deltas, SkewGeom g,
                        const int* inLens, const int* labLens, Dims d, float* lossSum,
                        unsigned* ticket, int* status, cudaStream_t stream) {
   if (d.B <= 0) return;
   const int smem = kRing * kDiag * g.ld * 8;
   ScopedKernel sk("alpha_warp", stream);
   allow_dyn_smem(alpha_warp_kernel, smem);
-  alpha_warp_kernel<<<d.B, 32, smem, stream>>>(arcs, costs, alphasS, g.ld, g.stride, g.nDiag,
+  alpha_warp_kernel<<<d.B, 32, smem, stream>>>(arcs, costs, alphasS, deltas, g.ld, g.stride, g.nDiag,
                                                inLens, labLens, d.B, d.maxT, d.maxU, lossSum,
                                                ticket, status);
   TB200_CHECK_LAUNCH();
 }
 
-void launch_gamma_warp(const float2* arcs, const float* alphasS, SkewGeom g, const int* inLens,
-                       const int* labLens, float* stayS, float* stepS, float* pBlank,
+void launch_gamma_warp(const float2* arcs, const float* alphasS, const float* deltas, SkewGeom g,
+                       const int* inLens, const int* labLens, float* stayS, float* stepS, float* pBlank,
                        float* pLabel, Dims d, int* status, cudaStream_t stream) {
   if (d.B <= 0) return;
   const int slotBytes = kDiag * g.ld * 8 + (kDiag + 2) * g.ld * 4;
   const int smem = kRing * slotBytes + 4 * kDiag * 128 * (int)sizeof(float2);
   ScopedKernel sk("gamma_warp", stream);
   allow_dyn_smem(gamma_warp_kernel, smem);
-  gamma_warp_kernel<<<d.B, kGammaThreads, smem, stream>>>(arcs, alphasS, g.ld, g.stride, inLens,
+  gamma_warp_kernel<<<d.B, kGammaThreads, smem, stream>>>(arcs, alphasS, deltas, g.nDiag, g.ld, g.stride, inLens,
                                                           labLens, stayS, stepS, pBlank, pLabel,
                                                           d.maxT, d.maxU, status);
   TB200_CHECK_LAUNCH();
