@@ -380,7 +380,7 @@ def main():
         else:
             with torch.no_grad():
                 costs = crit(E, P, labels, il, ll)
-        state["costs"] = costs
+        state["costs"] = costs.detach()   # (a reference to `costs` would keep its autograd graph alive)
         return crit.last_loss_sum
 
     # The path's one collective (4 bytes) runs on a side stream: the main stream copies the loss

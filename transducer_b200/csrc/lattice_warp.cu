@@ -134,22 +134,18 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
   float up = kNone;  // stepOut[3] of the lane below, one diagonal back
   float offset = 0.0f;  // sum of the deltas so far: an integer, exact in fp32
   float* dl = deltas + (i64)b * ((nDiag + kDiag - 1) / kDiag);
+  float nextDelta = 0.0f;  // by how much the state is lowered at the start of the next block
   for (int k = 0; k < nBlocks; ++k) {
     if (k > 0) {
-      // rebase: lower the carried state by the floor of its largest entry (entries of nodes
-      // outside the lattice are ~ -6e29 and stay there)
-      float m = fmaxf(fmaxf(stayIn[0], stayIn[1]), fmaxf(stayIn[2], stayIn[3]));
-      m = fmaxf(m, fmaxf(fmaxf(stepOut[0], stepOut[1]), fmaxf(stepOut[2], stepOut[3])));
-      const int mi = __reduce_max_sync(0xffffffffu, __float2int_rd(fmaxf(m, -1.0e9f)));
-      const float delta = (float)mi;
+      // rebase (entries of nodes outside the lattice are ~ -6e29 and stay there)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        stayIn[r] -= delta;
-        stepOut[r] -= delta;
+        stayIn[r] -= nextDelta;
+        stepOut[r] -= nextDelta;
       }
-      up -= delta;
-      offset += delta;
-      if (lane == 0) dl[k] = delta;
+      up -= nextDelta;
+      offset += nextDelta;
+      if (lane == 0) dl[k] = nextDelta;
     }
     // The slot refilled next was read by ALL lanes one block ago: the warp barrier orders those
     // reads before lane 0's proxy fence and copy issue.
@@ -164,6 +160,15 @@ __global__ void __launch_bounds__(32) alpha_warp_kernel(
     const float4* blk = reinterpret_cast<const float4*>(ring + (size_t)(k % kRing) * slot + uc);
     const int d0 = k * kDiag, nd = min(kDiag, S - d0), ld4 = ld / 2;  // float4 per diagonal
     float* out = al + (size_t)d0 * ld + u0;
+    // The delta applied at the start of the NEXT block is the floor of the largest entry of
+    // the state now, at the start of this one: the warp-wide maximum then has a whole block to
+    // arrive, off the dependent chain.  (By then the state has sunk by another ~16 arcs; all
+    // that matters is that the stored numbers stay small: below ~1000, ulp 6e-5.)
+    {
+      float m = fmaxf(fmaxf(stayIn[0], stayIn[1]), fmaxf(stayIn[2], stayIn[3]));
+      m = fmaxf(m, fmaxf(fmaxf(stepOut[0], stepOut[1]), fmaxf(stepOut[2], stepOut[3])));
+      nextDelta = (float)__reduce_max_sync(0xffffffffu, __float2int_rd(fmaxf(m, -1.0e9f)));
+    }
 #pragma unroll 4
     for (int dd = 0; dd < nd; ++dd) {
       const float4 f01 = blk[dd * ld4], f23 = blk[dd * ld4 + 1];
@@ -259,7 +264,6 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
   if (empty) return;
   const float2* ar = arcs + (i64)b * latStride;
   const float* al = alphas + (i64)b * latStride;
-  const float* dl = deltas + (i64)b * ((nDiag + kDiag - 1) / kDiag);
   float* sS = stayS + (i64)b * latStride;
   float* pS = stepS + (i64)b * latStride;
   const int S = T + U - 1;
@@ -269,6 +273,12 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     for (int s = 0; s < kRing; ++s) mbar_init(&bar[s], 1);
     abortFlag = 0;
     fence_mbar_init();
+  }
+  // the alpha kernel's per-block deltas of this utterance, staged once (after the F/G buffers)
+  float* dl = reinterpret_cast<float*>(G + 2);
+  {
+    const float* src = deltas + (i64)b * ((nDiag + kDiag - 1) / kDiag);
+    for (int k = 1 + tid; k < nBlocks; k += kGammaThreads) dl[k] = src[k];
   }
   __syncthreads();
   auto issue = [&](int k) {  // one thread
@@ -299,7 +309,13 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
     // all operands of the thread's diagonals first (clamped, unconditional), then the arithmetic:
     // the shared-memory latency is paid once per block, not once per diagonal
     float2 arc[kPerHelper];
-    float a[kPerHelper], adn[kPerHelper], art[kPerHelper], dlt[kPerHelper];
+    float a[kPerHelper], adn[kPerHelper], art[kPerHelper];
+    // Exactly one diagonal of the block, ddB, has its successors on a diagonal that opens a block
+    // of the alpha kernel (dNext = dTop - ddB + 1 a multiple of 16): there the carried sums were
+    // lowered by that block's delta before they entered it.
+    const int ddB = (dTop + 1) & (kDiag - 1);
+    const int dNextB = dTop - ddB + 1;
+    const float deltaB = (dNextB >= kDiag && dNextB < S) ? dl[dNextB / kDiag] : 0.0f;
 #pragma unroll
     for (int j = 0; j < kPerHelper; ++j) {
       const int row = dTop - min(hg + j * kHelperGroups, nd - 1) - dLo;
@@ -307,19 +323,16 @@ __global__ void __launch_bounds__(kGammaThreads) gamma_warp_kernel(
       a[j] = aa[row * ld + hu];
       adn[j] = aa[(row + 1) * ld + hu];
       art[j] = aa[(row + 1) * ld + hu + 1];
-      // the successors lie on diagonal dNext; if it opens a block of the alpha kernel, the
-      // carried sums were lowered by that block's delta before they entered it
-      const int dNext = dLo + row + 1;
-      dlt[j] = ((dNext & (kDiag - 1)) == 0 && dNext < S) ? dl[dNext / kDiag] : 0.0f;
     }
 #pragma unroll
     for (int j = 0; j < kPerHelper; ++j) {
       const int dd = hg + j * kHelperGroups, t = dTop - dd - hu;
       const bool valid = hu < U && t >= 0 && t < T;
+      const float dlt = (dd == ddB) ? deltaB : 0.0f;
       float2 f;
-      f.x = (valid && t < T - 1) ? ex2_approx(((a[j] + arc[j].x) - dlt[j]) - adn[j]) : 0.0f;
+      f.x = (valid && t < T - 1) ? ex2_approx(((a[j] + arc[j].x) - dlt) - adn[j]) : 0.0f;
       if (t == T - 1 && hu == U - 1) f.x = 1.0f;  // terminating blank, fed by g(T,U-1) := 1
-      f.y = (valid && hu < U - 1) ? ex2_approx(((a[j] + arc[j].y) - dlt[j]) - art[j]) : 0.0f;
+      f.y = (valid && hu < U - 1) ? ex2_approx(((a[j] + arc[j].y) - dlt) - art[j]) : 0.0f;
       if (dd < nd) F[k & 1][dd][hu] = f;
     }
     return ok;
@@ -695,7 +708,9 @@ void launch_gamma_warp(const float2* arcs, const float* alphasS, const float* de
                        float* pLabel, Dims d, int* status, cudaStream_t stream) {
   if (d.B <= 0) return;
   const int slotBytes = kDiag * g.ld * 8 + (kDiag + 2) * g.ld * 4;
-  const int smem = kRing * slotBytes + 4 * kDiag * 128 * (int)sizeof(float2);
+  const int smem = kRing * slotBytes + 4 * kDiag * 128 * (int)sizeof(float2) +
+                   (int)sizeof(float) * ((g.nDiag + kDiag - 1) / kDiag + 1);
+  if (smem > 225 * 1024) throw std::invalid_argument("input too long for the single-warp reverse sweep");
   ScopedKernel sk("gamma_warp", stream);
   allow_dyn_smem(gamma_warp_kernel, smem);
   gamma_warp_kernel<<<d.B, kGammaThreads, smem, stream>>>(arcs, alphasS, deltas, g.nDiag, g.ld, g.stride, inLens,
