@@ -103,7 +103,11 @@ struct SavedState {
 
 struct ForwardWs {
   float* LN;  // row-major log-normalisers before the re-layout
-  ForwardWs(Carver& c, const Dims& d) { LN = c.take<float>((size_t)d.B * d.maxT * d.maxU); }
+  float* EL;  // row-major label emissions E[t,label_u] gathered by the log-normaliser pass
+  ForwardWs(Carver& c, const Dims& d) {
+    LN = c.take<float>((size_t)d.B * d.maxT * d.maxU);
+    EL = c.take<float>(lognorm_umma_gathers(d) ? (size_t)d.B * d.maxT * d.maxU : 0);
+  }
 };
 
 struct BackwardWs {
@@ -149,10 +153,12 @@ void need(size_t have, size_t want, const void* ws) {
 
 // Log-normalisers plus the row shifts.  With the exact path rowRef is the true row
 // maximum of E.
-void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+// Returns true if the pass also produced the label / blank emissions (EL, ebl) it was offered.
+bool log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
                     const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws,
-                    bool fixup = true) {
-  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+                    bool fixup = true, const int* labels = nullptr, float* EL = nullptr,
+                    float* ebl = nullptr) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return false;
   const bool can = lognorm_umma_supported(E, P, d);
   if (g_opt.lognorm_path == 2 && !can)
     throw std::invalid_argument(
@@ -162,13 +168,16 @@ void log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
     // the kernel needs somewhere to put the row shifts even if the caller does not want them
     float* mp = maxP ? maxP : ws.maxPScratch;
     if (!rowRef) throw std::invalid_argument("rowRef must not be null");
+    const bool gathers = labels && EL && ebl && lognorm_umma_gathers(d);
     launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split,
-                        device_status_word(), fixup, g_stream);
-    return;
+                        device_status_word(), fixup, g_stream, gathers ? labels : nullptr,
+                        gathers ? EL : nullptr, gathers ? ebl : nullptr);
+    return gathers;
   }
   launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
   if (rowRef) launch_row_max(E, rowRef, inLens, 0, d.B, d.maxT, d.V, g_stream);
   if (maxP) launch_row_max(P, maxP, labLens, 1, d.B, d.maxU, d.V, g_stream);
+  return false;
 }
 
 }  // namespace
@@ -345,9 +354,10 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
     LogNormWs ws(c, d);
     const SkewGeom g = skew_geom(d);
     // (nodes the tensor-core log-normaliser could not represent are recomputed by the re-layout)
-    log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws, /*fixup=*/false);
-    launch_lattice_prep(E, P, fw.LN, st.LNs, st.arcs ? nullptr : st.ELs, st.ebl, st.arcs, labels, inLens, labLens, g, d,
-                        g_stream);
+    const bool gathered = log_norms_impl(E, P, fw.LN, st.rowRef, st.maxP, inLens, labLens, d, ws,
+                                         /*fixup=*/false, labels, fw.EL, st.ebl);
+    launch_lattice_prep(E, P, fw.LN, st.LNs, st.arcs ? nullptr : st.ELs, st.ebl, st.arcs, labels,
+                        inLens, labLens, g, d, g_stream, gathered ? fw.EL : nullptr);
     if (lossSum) {
       TB200_CUDA_CHECK(cudaMemsetAsync(ws.ticket, 0, sizeof(unsigned), g_stream));
       if (B == 0) TB200_CUDA_CHECK(cudaMemsetAsync(lossSum, 0, sizeof(float), g_stream));

@@ -53,10 +53,12 @@ constexpr int kNoArcByte = 0xF0;
 // are recomputed here with the exact fp32 logsumexp.
 // If arcs is not null: arcs[t,u] (skewed, [B,nDiag,ld] float2) = log2-unit log-probabilities of
 // the blank arc and the label arc leaving node (t,u), kNoArcBits where there is none.
+// If ELrow is not null it holds E[t,label_u] row-major [B,maxT,maxU] and ebl is an INPUT
+// (both written by launch_lognorm_umma): nothing is gathered from E here.
 void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
                          float* ELs, float* ebl, float2* arcs, const int* labels,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const float* ELrow = nullptr);
 
 void launch_alpha_skew(const float* P, float* costs, float* alphasS, const float* LNs,
                        const float* ELs, const float* ebl, SkewGeom g, const int* labels,
@@ -111,9 +113,14 @@ bool lognorm_umma_supported(const float* E, const float* P, Dims d);
 size_t lognorm_umma_workspace_floats(Dims d);
 // Nodes whose factored sum left the fp32 range come out of the kernel as NaN; with `fixup` a
 // second kernel recomputes them exactly, without it the caller must (lattice_prep does).
+// With labels, EL [B,maxT,maxU] and ebl [B,maxT] (all three non-null) and lognorm_umma_gathers(d),
+// the kernel also writes EL[b,t,u] = E[b,t,labels[b,u]] (u < U_b - 1) and ebl[b,t] = E[b,t,blank]
+// for the valid frames, from the chunks it streams anyway.
+bool lognorm_umma_gathers(Dims d);
 void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
-                         int* status, bool fixup, cudaStream_t stream);
+                         int* status, bool fixup, cudaStream_t stream,
+                         const int* labels = nullptr, float* EL = nullptr, float* ebl = nullptr);
 
 // ---- grads_umma.cu --------------------------------------------------------------
 // Tensor-core gradients: one pass over E produces egrads and pgrads.  Usable when

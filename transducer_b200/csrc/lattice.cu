@@ -605,12 +605,15 @@ namespace {
 //   arcs[t,u].y = (E[t,label_u] + P[u,label_u] - LN[t,u]) * log2(e),  u < U-1
 // (the caller pre-fills the array with a large negative number: nodes outside the lattice and
 // the label arc of the last position keep it).
+// With ELrow (row-major [B,maxT,maxU], written by the tensor-core log-normaliser together with
+// ebl) the label and blank emissions are read from there, coalesced, instead of being gathered
+// from E one DRAM sector per node.
 __global__ void __launch_bounds__(256) lattice_prep_kernel(
     const float* __restrict__ E, const float* __restrict__ P, const float* __restrict__ LN,
     float* __restrict__ LNs, float* __restrict__ ELs, float* __restrict__ ebl,
-    float2* __restrict__ arcs, const int* __restrict__ labels, const int* __restrict__ inLens,
-    const int* __restrict__ labLens, int maxT, int maxU, int V, int blank, int ld,
-    i64 latStride) {
+    float2* __restrict__ arcs, const float* __restrict__ ELrow, const int* __restrict__ labels,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
+    int blank, int ld, i64 latStride) {
   __shared__ float tLn[32][33], tEl[32][33], tEb[32];
   const int b = blockIdx.z, t0 = blockIdx.y * 32, u0 = blockIdx.x * 32;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
@@ -618,6 +621,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const float* e = E + (i64)b * maxT * V;
   const float* ln = LN + (i64)b * maxT * maxU;
+  const float* elr = ELrow ? ELrow + (i64)b * maxT * maxU : nullptr;
   const int* lab = labels + (i64)b * (maxU - 1);
   const int u = u0 + lane;
   const int myLab = (u < U - 1) ? lab[u] : blank;
@@ -637,7 +641,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     for (int k = 0; k < 4; ++k) {
       const int tc = min(t0 + w * 4 + k, T - 1);
       va[k] = ln[(i64)tc * maxU + uc];
-      vc[k] = e[(i64)tc * V + labc];
+      vc[k] = elr ? ((uc < U - 1) ? elr[(i64)tc * maxU + uc] : 0.0f) : e[(i64)tc * V + labc];
     }
   }
 #pragma unroll
@@ -669,9 +673,10 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     tEl[tt][lane] = c;
   }
   if (threadIdx.x < 32) {
-    const float v = (t0 + lane < T) ? e[(i64)(t0 + lane) * V + blank] : 0.0f;
+    float v = 0.0f;
+    if (t0 + lane < T) v = elr ? ebl[(i64)b * maxT + t0 + lane] : e[(i64)(t0 + lane) * V + blank];
     tEb[lane] = v;
-    if (u0 == 0 && t0 + lane < T) ebl[(i64)b * maxT + t0 + lane] = v;
+    if (!elr && u0 == 0 && t0 + lane < T) ebl[(i64)b * maxT + t0 + lane] = v;
   }
   __syncthreads();
   // diagonal s = t + u of this tile: s - (t0+u0) in [0, 62]; lane <-> u
@@ -735,15 +740,15 @@ __global__ void __launch_bounds__(256) lattice_unskew_kernel(
 void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
                          float* ELs, float* ebl, float2* arcs, const int* labels,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const float* ELrow) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   if (arcs != nullptr)
     TB200_CUDA_CHECK(cudaMemsetAsync(arcs, kNoArcByte, sizeof(float2) * (size_t)d.B * g.stride, stream));
   dim3 grid(div_up(d.maxU, 32), div_up(d.maxT, 32), d.B);
   ScopedKernel sk("lattice_prep", stream);
-  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, P, LN, LNs, ELs, ebl, arcs, labels, inLens,
-                                                labLens, d.maxT, d.maxU, d.V, d.blank, g.ld,
-                                                g.stride);
+  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, P, LN, LNs, ELs, ebl, arcs, ELrow, labels,
+                                                inLens, labLens, d.maxT, d.maxU, d.V, d.blank,
+                                                g.ld, g.stride);
   TB200_CHECK_LAUNCH();
 }
 
