@@ -56,6 +56,8 @@ void* tb200_get_stream(void);
  *                   weights are always rounded once to TF32.  1: exp(E), exp(P) rounded
  *                   once too; 2 (default): exp(E) split hi+lo (exact products for
  *                   pgrads); 3: exp(P) split as well (smaller tiles, slower)
+ *   "fused_gather"  1 (default): the tensor-core log-normaliser also hands out E[t,label_u] and
+ *                   E[t,blank] from the rows it streams; 0: a separate gather pass fetches them
  * Unknown keys return TB200_ERR_INVALID_ARGUMENT.  No counterpart in the reference. */
 int tb200_set_option(const char* key, int value);
 int tb200_get_option(const char* key, int* value);

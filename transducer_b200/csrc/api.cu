@@ -24,6 +24,7 @@ struct Options {
   std::atomic<int> lognorm_path{0};
   std::atomic<int> grads_path{0};
   std::atomic<int> grad_passes{2};
+  std::atomic<int> fused_gather{1};
 };
 Options g_opt;
 
@@ -168,7 +169,7 @@ bool log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
     // the kernel needs somewhere to put the row shifts even if the caller does not want them
     float* mp = maxP ? maxP : ws.maxPScratch;
     if (!rowRef) throw std::invalid_argument("rowRef must not be null");
-    const bool gathers = labels && EL && ebl && lognorm_umma_gathers(d);
+    const bool gathers = labels && EL && ebl && lognorm_umma_gathers(d) && g_opt.fused_gather != 0;
     launch_lognorm_umma(E, P, LN, rowRef, mp, inLens, labLens, d, ws.split,
                         device_status_word(), fixup, g_stream, gathers ? labels : nullptr,
                         gathers ? EL : nullptr, gathers ? ebl : nullptr);
@@ -206,6 +207,7 @@ int tb200_set_option(const char* key, int value) {
   if (!strcmp(key, "lognorm_path") && value >= 0 && value <= 2) g_opt.lognorm_path = value;
   else if (!strcmp(key, "grads_path") && value >= 0 && value <= 2) g_opt.grads_path = value;
   else if (!strcmp(key, "grad_passes") && value >= 1 && value <= 3) g_opt.grad_passes = value;
+  else if (!strcmp(key, "fused_gather") && value >= 0 && value <= 1) g_opt.fused_gather = value;
   else return fail(kErrInvalidArgument, std::string("unknown option or bad value: ") + key);
   return kOk;
 }
@@ -215,6 +217,7 @@ int tb200_get_option(const char* key, int* value) {
   if (!strcmp(key, "lognorm_path")) *value = g_opt.lognorm_path;
   else if (!strcmp(key, "grads_path")) *value = g_opt.grads_path;
   else if (!strcmp(key, "grad_passes")) *value = g_opt.grad_passes;
+  else if (!strcmp(key, "fused_gather")) *value = g_opt.fused_gather;
   else return fail(kErrInvalidArgument, std::string("unknown option: ") + key);
   return kOk;
 }

@@ -53,8 +53,8 @@ constexpr int kNoArcByte = 0xF0;
 // are recomputed here with the exact fp32 logsumexp.
 // If arcs is not null: arcs[t,u] (skewed, [B,nDiag,ld] float2) = log2-unit log-probabilities of
 // the blank arc and the label arc leaving node (t,u), kNoArcBits where there is none.
-// If ELrow is not null it holds E[t,label_u] row-major [B,maxT,maxU] and ebl is an INPUT
-// (both written by launch_lognorm_umma): nothing is gathered from E here.
+// If ELrow is not null it holds E[t,label_u] as [B,maxU,maxT] (frames contiguous) and ebl is an
+// INPUT (both written by launch_lognorm_umma): nothing is gathered from E here.
 void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
                          float* ELs, float* ebl, float2* arcs, const int* labels,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
@@ -113,9 +113,9 @@ bool lognorm_umma_supported(const float* E, const float* P, Dims d);
 size_t lognorm_umma_workspace_floats(Dims d);
 // Nodes whose factored sum left the fp32 range come out of the kernel as NaN; with `fixup` a
 // second kernel recomputes them exactly, without it the caller must (lattice_prep does).
-// With labels, EL [B,maxT,maxU] and ebl [B,maxT] (all three non-null) and lognorm_umma_gathers(d),
-// the kernel also writes EL[b,t,u] = E[b,t,labels[b,u]] (u < U_b - 1) and ebl[b,t] = E[b,t,blank]
-// for the valid frames, from the chunks it streams anyway.
+// With labels, EL [B,maxU,maxT] (frames contiguous) and ebl [B,maxT] (all three non-null) and
+// lognorm_umma_gathers(d), the kernel also writes EL[b,u,t] = E[b,t,labels[b,u]] (u < U_b - 1)
+// and ebl[b,t] = E[b,t,blank] for the valid frames, from the chunks it streams anyway.
 bool lognorm_umma_gathers(Dims d);
 void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,

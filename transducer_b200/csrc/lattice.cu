@@ -605,9 +605,9 @@ namespace {
 //   arcs[t,u].y = (E[t,label_u] + P[u,label_u] - LN[t,u]) * log2(e),  u < U-1
 // (the caller pre-fills the array with a large negative number: nodes outside the lattice and
 // the label arc of the last position keep it).
-// With ELrow (row-major [B,maxT,maxU], written by the tensor-core log-normaliser together with
-// ebl) the label and blank emissions are read from there, coalesced, instead of being gathered
-// from E one DRAM sector per node.
+// With ELrow ([B,maxU,maxT], frames contiguous, written by the tensor-core log-normaliser
+// together with ebl) the label and blank emissions are read from there, coalesced, instead of
+// being gathered from E one DRAM sector per node.
 __global__ void __launch_bounds__(256) lattice_prep_kernel(
     const float* __restrict__ E, const float* __restrict__ P, const float* __restrict__ LN,
     float* __restrict__ LNs, float* __restrict__ ELs, float* __restrict__ ebl,
@@ -621,7 +621,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const float* e = E + (i64)b * maxT * V;
   const float* ln = LN + (i64)b * maxT * maxU;
-  const float* elr = ELrow ? ELrow + (i64)b * maxT * maxU : nullptr;
+  const float* elr = ELrow ? ELrow + (i64)b * maxU * maxT : nullptr;
   const int* lab = labels + (i64)b * (maxU - 1);
   const int u = u0 + lane;
   const int myLab = (u < U - 1) ? lab[u] : blank;
@@ -641,7 +641,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     for (int k = 0; k < 4; ++k) {
       const int tc = min(t0 + w * 4 + k, T - 1);
       va[k] = ln[(i64)tc * maxU + uc];
-      vc[k] = elr ? ((uc < U - 1) ? elr[(i64)tc * maxU + uc] : 0.0f) : e[(i64)tc * V + labc];
+      vc[k] = elr ? 0.0f : e[(i64)tc * V + labc];
     }
   }
 #pragma unroll
@@ -670,7 +670,15 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
       if (lane == src) a = logf(s) + m;
     }
     tLn[tt][lane] = a;
-    tEl[tt][lane] = c;
+    if (!elr) tEl[tt][lane] = c;
+  }
+  if (elr) {  // transposed tile load: lane <-> frame, row <-> label position
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int uu = u0 + w * 4 + k, tl = t0 + lane;
+      const float v = elr[(i64)min(uu, max(U - 2, 0)) * maxT + min(tl, T - 1)];
+      tEl[lane][w * 4 + k] = (uu < U - 1 && tl < T) ? v : 0.0f;
+    }
   }
   if (threadIdx.x < 32) {
     float v = 0.0f;

@@ -180,9 +180,9 @@ struct LnParams {
   int B, tilesX, nSM;
   float* partial;    // [nSM][kTileM][nPad] partial sums of split tiles
   unsigned* tickets; // [nSM] parts finished per split tile (zero on entry, zero again on exit)
-  // label / blank emissions gathered on the fly by lognorm_umma_v3_kernel (null: not wanted)
+  // label / blank emissions gathered on the fly (null: not wanted)
   const int* labels; // [B, maxU-1]
-  float* EL;         // [B, maxT, maxU] row-major: EL[b,t,u] = E[b,t,labels[b,u]] for u < U_b - 1
+  float* EL;         // [B, maxU, maxT], frames contiguous: EL[b,u,t] = E[b,t,labels[b,u]], u < U_b - 1
   float* ebl;        // [B, maxT]: E[b,t,blank]
   int blank;
 };
@@ -209,6 +209,7 @@ constexpr int kGroup = 2;
 // The grid is (tilesX * B + nSM) x 1; lengths are on the device, so every CTA derives the
 // schedule from them itself (B <= 1024; larger batches are not split).
 constexpr int kMaxParts = 8;
+constexpr int kMaxLabels = 256;
 template <int NTW, int NDRAIN, int DCOLS>
 __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
@@ -299,6 +300,12 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   __shared__ float sMaxP[256];
   __shared__ float sRef[kTileM];
   __shared__ int sLast;
+  // While a transform thread holds its frame's row of a chunk it also hands out the entries
+  // the lattice sweeps need: E[t, label_u] for the labels whose column lies in the chunk (the
+  // utterance's labels are sorted by column once per CTA) and E[t, blank].  That replaces a
+  // gather pass that fetched one DRAM sector per lattice node (transducer_cuda.cu:84 does that
+  // gather inside its wavefront).
+  __shared__ int sKey[kMaxLabels];      // (column << 8 | label position u), ascending
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // this part's chunks [cBegin, cEnd); iteration i of the pipeline handles chunk chunkOf(i)
@@ -325,6 +332,23 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   }
   for (int u = threadIdx.x; u < p.nPad; u += kThreads)
     sMaxP[u] = (u < U) ? p.maxP[(i64)b * p.maxU + u] : 0.0f;
+  const bool gather = p.EL != nullptr;
+  const int nLab = gather ? min(U - 1, kMaxLabels) : 0;
+  if (gather) {  // rank sort by column (from a shared-memory copy); ties keep position order
+    __shared__ int sLab[kMaxLabels];
+    const int* lab = p.labels + (i64)b * (p.maxU - 1);
+    for (int i = threadIdx.x; i < nLab; i += kThreads) sLab[i] = lab[i];
+    __syncthreads();
+    for (int i = threadIdx.x; i < nLab; i += kThreads) {
+      const int mine = sLab[i];
+      int rank = 0;
+      for (int j = 0; j < nLab; ++j) {
+        const int o = sLab[j];
+        rank += (o < mine || (o == mine && j < i)) ? 1 : 0;
+      }
+      sKey[rank] = (mine << 8) | i;
+    }
+  }
   if (warp == kMmaWarp) {
     tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
     tmem_relinquish();
@@ -418,6 +442,11 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
       ok = __all_sync(0xffffffffu, ok);
       ref = sRef[r];
     }
+    int cur = 0;  // cursor into the sorted label list (the same in every thread)
+    // column of the next entry that this group has not passed yet, kept in a register so that a
+    // chunk without any costs one comparison and no shared-memory access
+    int nextCol = (gather && nLab > 0) ? (sKey[0] >> 8) : 0x7fffffff;
+    float* elCol = gather ? p.EL + (i64)b * p.maxU * p.maxT + t0 + r : nullptr;  // my frame
     for (int c = grp; c < nChunks && ok; c += NTW) {
       const int s = c % S;
       ok = mbar_wait(&barFull[s], (c / S) & 1, abortp, p.status, kStatusTimeoutTma);
@@ -442,6 +471,27 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
         sRef[r] = ref;
         if (t0 + r < T && part == 0) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
+      }
+      const int col0 = chunkOf(c) * kChunkK;
+      if (gather && !refOnly && nextCol < col0 + kChunkK) {
+        // (uniform control flow: the list and the cursor are the same in all threads)
+        int key = sKey[cur];
+        while ((key >> 8) < col0 && ++cur < nLab) key = sKey[cur];   // the other group's chunks
+        while (cur < nLab && (key >> 8) < col0 + kChunkK) {
+          const int off = (key >> 8) - col0;
+          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
+          // (the 128 threads of the group write 128 consecutive floats of row u)
+          if (t0 + r < T) elCol[(i64)(key & 0xff) * p.maxT] = v;
+          if (++cur < nLab) key = sKey[cur];
+        }
+        nextCol = cur < nLab ? (key >> 8) : 0x7fffffff;
+      }
+      if (gather && !refOnly) {
+        if (p.blank >= col0 && p.blank < col0 + kChunkK) {
+          const int off = p.blank - col0;
+          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
+          if (t0 + r < T) p.ebl[(i64)b * p.maxT + t0 + r] = v;
+        }
       }
       const float nref = -ref * kLog2e;
       const uint32_t dst = tA + laneAddr + (uint32_t)(s * 64);
@@ -516,456 +566,6 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
 #pragma unroll
             for (int j = 0; j < 16; ++j) sum[(i0 + i) * 16 + j] += __uint_as_float(v[i][j]);
           }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&barAccEmpty[a]);
-    }
-    if (ok) ok = mbar_wait(&barRef, 0, abortp, p.status, kStatusTimeoutOperand);
-    ok = __all_sync(0xffffffffu, ok);
-    // A warp that gave up (ok == false; the cause is in the status word) turns its sums into
-    // NaN: the nodes then carry the "recompute exactly" marker instead of stale memory.
-    const float bad = __int_as_float(0x7fc00000);
-    if (!ok) {
-#pragma unroll
-      for (int j = 0; j < kDrainCols; ++j) sum[j] = bad;
-    }
-    bool writer = true;  // does this CTA write the tile's log-normalisers?
-    if (parts > 1) {
-      // split tile: park the partial sums; the part that finishes last adds all of them in
-      // part order (so the result does not depend on which part that is) and goes on
-      float* mine = p.partial + ((size_t)(splitIdx * parts + part) * kTileM + r) * p.nPad + c0;
-#pragma unroll
-      for (int j = 0; j < kDrainCols; ++j)
-        if (c0 + j < c1) mine[j] = sum[j];
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
-      if (warp == kDrainWarp0 && lane == 0) {
-        const unsigned done = atomicAdd(&p.tickets[splitIdx], 1u);
-        sLast = (done == (unsigned)(parts - 1)) ? 1 : 0;
-        if (sLast) p.tickets[splitIdx] = 0u;  // ready for the next launch
-      }
-      asm volatile("bar.sync 1, %0;" ::"r"(4 * NDRAIN * 32) : "memory");
-      writer = sLast != 0;
-      if (writer) {
-        __threadfence();
-#pragma unroll
-        for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
-        for (int z = 0; z < parts; ++z) {
-          const float* src = p.partial + ((size_t)(splitIdx * parts + z) * kTileM + r) * p.nPad + c0;
-#pragma unroll
-          for (int j = 0; j < kDrainCols; ++j)
-            if (c0 + j < c1) sum[j] += __ldcg(src + j);
-        }
-      }
-    }
-    if (writer) {
-      const int t = t0 + r;
-      const float ref = ok ? sRef[r] : 0.0f;
-      int flagged = 0;
-      if (t < T) {
-        float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
-#pragma unroll
-        for (int j = 0; j < kDrainCols; ++j) {
-          const int u = c0 + j;
-          if (u < U) {
-            const float acc = sum[j];
-            float ln = (logf(acc) + ref) + sMaxP[u];
-            if (!(acc >= kSumLo && acc <= kSumHi)) {
-              ln = bad;  // marker: recompute exactly
-              ++flagged;
-            }
-            out[u] = ln;
-          }
-        }
-      }
-      if (flagged) atomicAdd(&p.status[1], flagged);
-    }
-  }
-
-  // ---------------- teardown (all roles, also after an abort) ----------------
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (warp == kMmaWarp) tmem_dealloc(tBase, (uint32_t)p.tmemCols);
-}
-
-// ---------------------------------------------------------------------------------
-// main kernel for label axes of at most 128 positions
-// ---------------------------------------------------------------------------------
-// Same arithmetic, tile and work items as lognorm_umma_kernel, re-plumbed after a cycle-stamped
-// trace of that kernel at the benchmark shape: a stage (raw E chunk + exp(P) hi/lo chunks, 44 KB)
-// was held ~4700 cycles -- ~1750 for the copies to land, ~940 for the transform group that owned
-// the chunk, ~790 to issue its 12 MMAs, the rest hand-offs -- so four stages gave one chunk per
-// ~1175 cycles while the tensor pipe needs 672 and HBM 740 per chunk, and the transform groups
-// sat idle half of the time waiting for data.  Changes:
-//   * five shared-memory stages where they fit (the operand stages in tensor memory stay four:
-//     they are only held from the transform to the MMAs, so they are indexed separately);
-//   * all eight transform warps work on EVERY chunk (a thread owns half a frame row: 16 columns),
-//     which halves the transform latency inside the chain and keeps every barrier's waiters in
-//     program order, so the ring depth need not be a multiple of anything;
-//   * stage indices and phases are carried incrementally (no division by a run-time ring depth in
-//     the single-thread loops: such a thread issues one instruction every several cycles), and
-//     the MMA issuers build their operand descriptors once.
-// While a transform thread holds its part of a frame's row it also hands out the entries the
-// lattice sweeps need: E[t, label_u] for the labels whose column lies in the chunk (the
-// utterance's labels are sorted by column once per CTA) and E[t, blank].  That replaces a
-// gather pass that fetched one DRAM sector per lattice node (transducer_cuda.cu:84 does that
-// gather inside its wavefront).
-constexpr int kMaxLabels = 256;
-constexpr int kV3Threads = 19 * 32;  // 8 transform + 8 drain + producer + 2 MMA warps
-constexpr int kAStages = 4;          // operand stages in tensor memory
-
-__device__ __forceinline__ void ln_find_item(const LnParams& p, int* sItem) {
-  // (warp 0; same schedule as lognorm_umma_kernel, see the comment above kMaxParts)
-  const int lane0 = threadIdx.x;
-  const int nNatural = p.tilesX * p.B;
-  const bool worker = (int)blockIdx.x >= nNatural;
-  const int myB = worker ? -1 : (int)blockIdx.x / p.tilesX, myX = worker ? 0 : (int)blockIdx.x % p.tilesX;
-  auto liveTiles = [&](int bb) {
-    if (bb >= p.B) return 0;
-    const int Tb = min(p.inLens[bb], p.maxT), Ub = min(p.labLens[bb] + 1, p.maxU);
-    return (Tb > 0 && Ub > 0) ? (Tb + kTileM - 1) / kTileM : 0;
-  };
-  int n = 0, before = 0;
-  for (int b0 = 0; b0 < p.B; b0 += 32) {
-    const int v = liveTiles(b0 + lane0);
-    n += __reduce_add_sync(0xffffffffu, v);
-    before += __reduce_add_sync(0xffffffffu, (b0 + lane0 < myB) ? v : 0);
-  }
-  const int full = (n / p.nSM) * p.nSM, rem = n - full;
-  int k = (rem > 0 && p.B <= 1024) ? min(kMaxParts, p.nSM / rem) : 1;
-  k = min(k, ((p.V + kChunkK - 1) / kChunkK) / 16);
-  if (k < 2) k = 1;
-  int ib = -1, ix = 0, part = 0, parts = 1, split = 0, valid = 0;
-  if (!worker) {
-    if (myX < liveTiles(myB)) {
-      valid = 1; ib = myB; ix = myX;
-      const int r = before + myX;
-      if (k > 1 && r >= full) { parts = k; split = r - full; }
-    }
-  } else if (k > 1) {
-    const int w = (int)blockIdx.x - nNatural;
-    if (w < rem * (k - 1)) {
-      split = w / (k - 1);
-      part = 1 + w % (k - 1);
-      parts = k;
-      const int target = full + split;
-      int run = 0;
-      for (int b0 = 0; b0 < p.B && !valid; b0 += 32) {
-        const int v = liveTiles(b0 + lane0);
-        int incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int up = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane0 >= o) incl += up;
-        }
-        const int lo = run + incl - v, hi = run + incl;
-        const unsigned hit = __ballot_sync(0xffffffffu, target >= lo && target < hi);
-        if (hit) {
-          const int src = __ffs(hit) - 1;
-          ib = b0 + src;
-          ix = target - __shfl_sync(0xffffffffu, lo, src);
-          valid = 1;
-        }
-        run += __shfl_sync(0xffffffffu, incl, 31);
-      }
-    }
-  }
-  if (lane0 == 0) {
-    sItem[0] = ib; sItem[1] = ix; sItem[2] = part; sItem[3] = parts; sItem[4] = split; sItem[5] = valid;
-  }
-}
-
-// S: shared-memory stages (4 or 5)
-template <int S>
-__global__ void __launch_bounds__(kV3Threads, 1) lognorm_umma_v3_kernel(
-    const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
-    const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
-  constexpr int NDRAIN = 2, kDrainCols = 64;
-  constexpr int kDrainWarp0 = 8;
-  constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
-  __shared__ int sItem[6];
-  if (threadIdx.x < 32) ln_find_item(p, sItem);
-  __syncthreads();
-  if (!sItem[5]) return;
-  const int b = sItem[0], t0 = sItem[1] * kTileM;
-  const int part = sItem[2], parts = sItem[3], splitIdx = sItem[4];
-  const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
-
-  extern __shared__ uint8_t smemRaw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
-                                             ~uintptr_t(1023));
-  const int bBytes = p.nPad * kChunkK * 4;
-  const int stageBytes = kRawBytes + 2 * bBytes;
-  __shared__ uint64_t barFull[S], barDone[S], barReady[kAStages], barAccFull[2], barAccEmpty[2], barRef,
-      barHalf;
-  __shared__ uint32_t tmemBase;
-  __shared__ int abortFlag;
-  __shared__ float sMaxP[128];
-  __shared__ float sRef[kTileM];
-  __shared__ float sRefHalf[2][kTileM];
-  __shared__ int sLast;
-  __shared__ int sCol[kMaxLabels];      // label columns of this utterance, ascending
-  __shared__ short sPos[kMaxLabels];    // their label positions u
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nChunksAll = (p.V + kChunkK - 1) / kChunkK;
-  const int cBegin = (int)((i64)part * nChunksAll / parts), cEnd = (int)((i64)(part + 1) * nChunksAll / parts);
-  const bool refFirst = part > 0;  // iteration 0 fetches chunk 0 for the frames' shifts only
-  const int nChunks = cEnd - cBegin + (refFirst ? 1 : 0);
-  auto chunkOf = [&](int i) { return refFirst ? (i == 0 ? 0 : cBegin + i - 1) : cBegin + i; };
-  const int nGroups = (nChunks + kGroup - 1) / kGroup;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&barFull[s], 1);
-      mbar_init(&barDone[s], 1);
-    }
-    for (int s = 0; s < kAStages; ++s) mbar_init(&barReady[s], 8);   // the eight transform warps
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&barAccFull[a], 1);
-      mbar_init(&barAccEmpty[a], 4 * NDRAIN);
-    }
-    mbar_init(&barRef, 8);
-    mbar_init(&barHalf, 8);
-    abortFlag = 0;
-    fence_mbar_init();
-  }
-  for (int u = threadIdx.x; u < p.nPad; u += kV3Threads)
-    sMaxP[u] = (u < U) ? p.maxP[(i64)b * p.maxU + u] : 0.0f;
-  // labels of the utterance sorted by column (rank sort; ties keep position order)
-  const bool gather = p.EL != nullptr;
-  const int nLab = gather ? U - 1 : 0;
-  if (gather) {
-    const int* lab = p.labels + (i64)b * (p.maxU - 1);
-    for (int i = threadIdx.x; i < nLab; i += kV3Threads) {
-      const int mine = lab[i];
-      int rank = 0;
-      for (int j = 0; j < nLab; ++j) {
-        const int o = lab[j];
-        rank += (o < mine || (o == mine && j < i)) ? 1 : 0;
-      }
-      sCol[rank] = mine;
-      sPos[rank] = (short)i;
-    }
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(&tmemBase, (uint32_t)p.tmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tBase = tmemBase;                       // accumulators: 2 x nPad columns
-  const uint32_t tA = tBase + (uint32_t)(2 * p.nPad);    // operand stages: [hi 32 | lo 32] each
-  volatile int* abortp = &abortFlag;
-
-  if (warp == kProducerWarp) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tmE);
-      tma_prefetch_desc(&tmHi);
-      tma_prefetch_desc(&tmLo);
-      int issued = 0, s = 0;
-      uint32_t ph = 1;  // parity of the PREVIOUS use of the stage
-      for (int c = 0; c < nChunks; ++c) {
-        if (c >= S && !mbar_wait(&barDone[s], ph, abortp, p.status, kStatusTimeoutStageFree)) break;
-        uint8_t* st = smem + (size_t)s * stageBytes;
-        mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
-        const int col = chunkOf(c) * kChunkK;
-        tma_load_3d(st, &tmE, &barFull[s], col, t0, b);
-        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], col, 0, b);
-        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], col, 0, b);
-        issued = c + 1;
-        if (++s == S) { s = 0; ph ^= 1u; }
-      }
-      if (*abortp) {
-        // after an abort: give the copies still in flight a bounded time to land
-        // before the CTA's shared memory is released
-        for (int c = max(0, issued - S); c < issued; ++c) {
-          const unsigned long long t1 = global_timer_ns();
-          while (!mbar_try_wait(&barFull[c % S], (c / S) & 1) &&
-                 global_timer_ns() - t1 < 50000000ull) {
-          }
-        }
-      }
-    }
-  } else if (warp >= kMmaWarp) {
-    // ---------------- MMA issuers ----------------
-    // One elected thread in each of two warps.  Issuer m owns accumulator m and therefore the
-    // chunk groups g with g % 2 == m: while one issuer is blocked on its barrier waits and
-    // commits, the other keeps the tensor pipe fed.  The transform warps finish the chunks in
-    // order, so when an issuer looks at a barrier for chunk c every earlier phase of that
-    // barrier is complete: the parity it waits for cannot be mistaken for an older one.
-    const int m = warp - kMmaWarp;
-    if (lane == 0) {
-      const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
-      const uint64_t descBase = smem_desc_sw128(smem_u32(smem) + (uint32_t)kRawBytes, 16, 1024);
-      const uint32_t dAcc = tBase + (uint32_t)(m * p.nPad);
-      const uint32_t stepHi = (uint32_t)stageBytes >> 4, stepLo = (uint32_t)bBytes >> 4;
-      bool ok = true;
-      int s = 0;
-      for (int c = 0; c < nChunks && ok; ++c) {
-        const int g = c >> 1, j = c & 1;
-        if ((g & 1) == m) {
-          const int sa = c & 3;
-          if (j == 0 && g >= 2)
-            ok = mbar_wait(&barAccEmpty[m], ((g >> 1) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
-          // the transform warps arrive on barReady only after they saw barFull complete, so
-          // the copies of this stage (the exp(P) tiles among them) have landed as well
-          ok = ok && mbar_wait(&barReady[sa], (c >> 2) & 1, abortp, p.status, kStatusTimeoutOperand);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t dHi = descBase + (uint64_t)(stepHi * (uint32_t)s);  // address field, 16-byte units
-          const uint64_t dLo = dHi + stepLo;
-          const uint32_t aHi = tA + (uint32_t)(sa * 64), aLo = aHi + 32;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // (+2 in the descriptor's address field = +32 bytes: one 8-float k-step)
-            mma_tf32_ts(dAcc, aHi + k * 8, dHi + 2 * k, idesc, (j | k) ? 1u : 0u);
-            mma_tf32_ts(dAcc, aLo + k * 8, dHi + 2 * k, idesc, 1u);
-            mma_tf32_ts(dAcc, aHi + k * 8, dLo + 2 * k, idesc, 1u);
-          }
-          mma_commit(&barDone[s]);
-          if (j == 1 || c == nChunks - 1) mma_commit(&barAccFull[m]);
-        }
-        if (++s == S) s = 0;
-      }
-    }
-  } else if (warp < kDrainWarp0) {
-    // ---------------- operand transform ----------------
-    // Thread (q, lane, h): frame r = 32q + lane of the tile (= TMEM lane r), columns
-    // [16h, 16h + 16) of every chunk.
-    const int q = warp & 3, h = warp >> 2;
-    const int r = q * 32 + lane;
-    const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
-    const int t = t0 + r;
-    float ref = 0.0f;
-    bool ok = true;
-    int cur = 0;  // cursor into the sorted label list (same in every thread of a half)
-    float* elRow = gather ? p.EL + ((i64)b * p.maxT + t) * p.maxU : nullptr;
-    int s = 0, s4 = 0;          // stage of chunk c, stage of chunk c - 4
-    uint32_t ph = 0, ph4 = 0;   // and their phases
-    for (int c = 0; c < nChunks && ok; ++c) {
-      const int sa = c & 3;
-      ok = mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma);
-      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
-      if (!ok) break;
-      const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
-      const int col0 = chunkOf(c) * kChunkK + 16 * h;     // first column of my half
-      const int kLeft = p.V - col0;                       // valid columns in my half
-      const bool refOnly = refFirst && c == 0;            // its terms belong to part 0
-      float x[16];
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const float4 v4 = *reinterpret_cast<const float4*>(row + (((4 * h + jj) ^ (r & 7)) << 4));
-        x[4 * jj] = v4.x; x[4 * jj + 1] = v4.y; x[4 * jj + 2] = v4.z; x[4 * jj + 3] = v4.w;
-      }
-      if (c == 0) {
-        // the frame's shift: maximum of the first 32 entries of the row (both halves)
-        float mx = neg_inf();
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (j < kLeft) mx = fmaxf(mx, x[j]);
-        sRefHalf[h][r] = mx;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&barHalf);   // (release: the warp's partial maxima are visible)
-        ok = mbar_wait(&barHalf, 0, abortp, p.status, kStatusTimeoutOperand);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        mx = fmaxf(sRefHalf[0][r], sRefHalf[1][r]);
-        // a -inf/NaN prefix would poison every term; fall back to 0 and let the
-        // range check route the row to the exact path if needed
-        ref = (mx > -3.0e38f && mx < 3.0e38f) ? mx : 0.0f;
-        if (h == 0) {
-          sRef[r] = ref;
-          if (t < T && part == 0) p.rowRef[(i64)b * p.maxT + t] = ref;
-        }
-      }
-      if (gather && !refOnly) {
-        // entries of my half of the chunk that the lattice sweeps need (uniform control flow:
-        // the list and the cursor are the same in all threads of the warp)
-        while (cur < nLab && sCol[cur] < col0) ++cur;
-        for (int k = cur; k < nLab && sCol[k] < col0 + 16; ++k) {
-          const int off = sCol[k] - col0 + 16 * h;
-          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
-          if (t < T) elRow[sPos[k]] = v;
-        }
-        if (p.blank >= col0 && p.blank < col0 + 16) {
-          const int off = p.blank - col0 + 16 * h;
-          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
-          if (t < T) p.ebl[(i64)b * p.maxT + t] = v;
-        }
-      }
-      const float nref = -ref * kLog2e;
-      const int kLeftMine = refOnly ? 0 : kLeft;
-      uint32_t hi[16], lo[16];
-      if (kLeftMine >= 16) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float e = ex2_approx(fmaf(x[j], kLog2e, nref));
-          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = hbits;
-          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
-        }
-      } else {  // last chunk of a vocabulary that is not a multiple of 32, or shift-only chunk
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float e = (j < kLeftMine) ? ex2_approx(fmaf(x[j], kLog2e, nref)) : 0.0f;
-          const uint32_t hbits = __float_as_uint(e) & 0xffffe000u;
-          hi[j] = hbits;
-          lo[j] = __float_as_uint(e - __uint_as_float(hbits));
-        }
-      }
-      // the operand stage in tensor memory must have been released by the MMAs of the chunk
-      // four back (their commit is that chunk's barDone)
-      if (c >= kAStages) {
-        ok = mbar_wait(&barDone[s4], ph4, abortp, p.status, kStatusTimeoutMma);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (++s4 == S) { s4 = 0; ph4 ^= 1u; }
-      }
-      const uint32_t dst = tA + laneAddr + (uint32_t)(sa * 64 + 16 * h);
-      tmem_st16(dst, hi);
-      tmem_st16(dst + 32, lo);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&barReady[sa]);
-        if (c == 0) mbar_arrive(&barRef);
-      }
-      if (++s == S) { s = 0; ph ^= 1u; }
-    }
-  } else {
-    // ---------------- accumulator drain + epilogue ----------------
-    const int h = (warp - kDrainWarp0) >> 2;     // which column slice
-    const int q = warp & 3;                      // TMEM lane quarter this warp may touch
-    const int r = q * 32 + lane;
-    const uint32_t laneAddr = (uint32_t)(q * 32) << 16;
-    const int c0 = h * kDrainCols, c1 = min(p.nPad, c0 + kDrainCols);
-    float sum[kDrainCols];
-#pragma unroll
-    for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
-    bool ok = true;
-    for (int g = 0; g < nGroups && ok; ++g) {
-      const int a = g & 1;
-      ok = mbar_wait(&barAccFull[a], (g >> 1) & 1, abortp, p.status, kStatusTimeoutMma);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t src = tBase + laneAddr + (uint32_t)(a * p.nPad + c0);
-#pragma unroll
-      for (int i0 = 0; i0 < kDrainCols / 16; ++i0) {
-        uint32_t v[16];
-        if (c0 + i0 * 16 < c1) {
-          tmem_ld16(src + i0 * 16, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) sum[i0 * 16 + j] += __uint_as_float(v[j]);
-        }
       }
       tc_fence_before();
       __syncwarp();
@@ -1160,26 +760,13 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
     ScopedKernel sk("lognorm_umma", stream);
     // the two-group transform and the two MMA issuers rely on exactly four stages (each stage
     // then has one consumer of each kind, in program order)
-    if (nPad <= 128) {
-      // five stages where they fit beside the kernel's static shared memory (227 KB per CTA)
-      const bool five = (size_t)5 * stageBytes + 1024 + 4096 <= (size_t)227 * 1024;
-      p.stages = five ? 5 : 4;
-      p.nAcc = 2;
-      p.tmemCols = pow2_at_least(2 * nPad + kAStages * 64);
-      if (labels != nullptr && EL != nullptr && ebl != nullptr) {
-        p.labels = labels; p.EL = EL; p.ebl = ebl;
-      }
-      size_t smem3 = (size_t)p.stages * stageBytes + 1024;
-      if (smem3 < 120 * 1024) smem3 = 120 * 1024;  // one CTA per SM (it may hold all of tensor memory)
-      if (five) {
-        auto k = lognorm_umma_v3_kernel<5>;
-        TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
-        k<<<grid, kV3Threads, smem3, stream>>>(tmE, tmHi, tmLo, p);
-      } else {
-        auto k = lognorm_umma_v3_kernel<4>;
-        TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
-        k<<<grid, kV3Threads, smem3, stream>>>(tmE, tmHi, tmLo, p);
-      }
+    if (labels != nullptr && EL != nullptr && ebl != nullptr && lognorm_umma_gathers(d)) {
+      p.labels = labels; p.EL = EL; p.ebl = ebl;
+    }
+    if (nPad <= 128 && stages == 4 && nAcc == 2) {
+      auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     } else {
       auto k = lognorm_umma_kernel<1, 2, 128>;  // 4 transform + 8 drain (128 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
