@@ -236,47 +236,59 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     }
     const uint32_t bytes =
         (uint32_t)(kEBytes + kRowBytes + (blankHere ? kRowBytes : 0) + nStaged * kRowBytes);
-    const int myU = (lane >= 6 && lane - 6 < nStaged) ? sListU[lane - 6] : -1;
+    // What this lane copies for every tile -- all through ONE call site, so that the warp issues
+    // its copies together instead of one divergent branch after the other (a branch with a TMA
+    // issue costs a lone lane ~200 cycles): which tensor map, where in the stage, and the two
+    // tile-independent coordinates.
+    const CUtensorMap* myMap = nullptr;
+    int myDst = 0, myX = 0, myZ = 0;
+    bool yIsT0 = true;   // E: (x = column, y = t0, z = b); scalar rows: (x = t0, y, z)
+    if (lane < 4) {  // (a box beyond the vocabulary reads as zeros and still counts its bytes)
+      myMap = &tm.E; myDst = lane * kBoxBytes; myX = v0 + 32 * lane; myZ = b;
+    } else if (lane == 4) {
+      myMap = &tm.nref; myDst = kEBytes; myX = b; myZ = 0; yIsT0 = false;
+    } else if (lane == 5) {
+      if (blankHere) { myMap = &tm.ebl; myDst = kEBytes + kRowStride; myX = b; myZ = 0; yIsT0 = false; }
+    } else if (lane - 6 < nStaged) {
+      myMap = &tm.emT; myDst = kEBytes + (lane - 4) * kRowStride; myX = sListU[lane - 6]; myZ = b; yIsT0 = false;
+    }
+    int fs = 0;  // stage of the next fill
     auto fill = [&](int i) {
-      const int s = i % SE, t0 = i * TB;
-      uint8_t* st = smem + (size_t)s * kEStage;
-      uint8_t* rows = st + kEBytes;
-      if (lane == 0) mbar_arrive_expect_tx(&barEFull[s], bytes);
+      const int t0 = i * TB;
+      uint8_t* st = smem + (size_t)fs * kEStage;
+      if (lane == 0) mbar_arrive_expect_tx(&barEFull[fs], bytes);
       __syncwarp();
-      if (lane < 4) tma_load_3d(st + lane * kBoxBytes, &tm.E, &barEFull[s], v0 + 32 * lane, t0, b);
-      else if (lane == 4) tma_load_3d(rows, &tm.nref, &barEFull[s], t0, b, 0);
-      else if (lane == 5) {
-        if (blankHere) tma_load_3d(rows + kRowStride, &tm.ebl, &barEFull[s], t0, b, 0);
-      } else if (myU >= 0) {
-        tma_load_3d(rows + (lane - 4) * kRowStride, &tm.emT, &barEFull[s], t0, myU, b);
-      }
+      if (myMap != nullptr)
+        tma_load_3d(st + myDst, myMap, &barEFull[fs], yIsT0 ? myX : t0, yIsT0 ? t0 : myX, myZ);
+      if (++fs == SE) fs = 0;
     };
     int issued = 0;
     for (; issued < nTiles && issued < SE; ++issued) fill(issued);
+    int ss = 0;        // stage of the tile stored next
+    uint32_t sph = 0;  // its phase
     for (int i = 0; i < nTiles; ++i) {
-      const int s = i % SE;
-      const bool ok = mbar_wait(&barStore[s], (i / SE) & 1, abortp, p.status, kStatusTimeoutOperand);
+      const bool ok = mbar_wait(&barStore[ss], sph, abortp, p.status, kStatusTimeoutOperand);
       if (!__all_sync(0xffffffffu, ok)) break;
-      if (lane == 0) {
-        const uint8_t* st = smem + (size_t)s * kEStage;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (v0 + 32 * j < p.V) tma_store_3d(&tm.G, st + j * kBoxBytes, v0 + 32 * j, i * TB, b);
+      // lanes 0..3 store one 32-column box each (every lane has a bulk group of its own), and
+      // wait until the store engine has read their box before the stage is refilled
+      if (lane < 4 && v0 + 32 * lane < p.V) {
+        tma_store_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + 32 * lane, i * TB, b);
         tma_store_commit();
-        if (issued < nTiles) tma_store_wait_read();  // the stage is about to be overwritten
+        if (issued < nTiles) tma_store_wait_read();
       }
       __syncwarp();
       if (issued < nTiles) fill(issued++);
+      if (++ss == SE) { ss = 0; sph ^= 1u; }
     }
-    if (lane == 0) {
+    if (lane < 4) {
       // all stores complete (not only read) before the CTA ends
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      if (*abortp) {  // give copies still in flight a bounded time to land
-        for (int i = max(0, issued - SE); i < issued; ++i) {
-          const unsigned long long t1 = global_timer_ns();
-          while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
-                 global_timer_ns() - t1 < 50000000ull) {
-          }
+    }
+    if (lane == 0 && *abortp) {  // give copies still in flight a bounded time to land
+      for (int i = max(0, issued - SE); i < issued; ++i) {
+        const unsigned long long t1 = global_timer_ns();
+        while (!mbar_try_wait(&barEFull[i % SE], (i / SE) & 1) &&
+               global_timer_ns() - t1 < 50000000ull) {
         }
       }
     }
@@ -318,51 +330,63 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     if (lane == 0) {
       const uint32_t idesc1 = idesc_tf32(128, TB, 0, 0);  // B = W tile, K-major (K = u)
       const int kSteps1 = p.Ku / 8;
+      // operand descriptor of W stage 0, k-step 0; the address field counts 16-byte units
+      const uint64_t descW = smem_desc_sw128(smem_u32(smemW), 16, 1024);
+      int s = 0, db = 0;
+      uint32_t wph = 0, dph = 1;  // phase of the W stage; phase of the PREVIOUS use of the D1 copy
       // expP^T resident in TMEM.  (Its own barrier: a warp whose columns lie beyond the
       // vocabulary finishes the prologue early and must not be able to complete a per-tile
       // phase with that arrival.)
       bool ok = mbar_wait(&barPReady, 0, abortp, p.status, kStatusTimeoutOperand);
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int s = i % SW, db = i % DB;
-        ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma);
+        ok = mbar_wait(&barWFull[s], wph, abortp, p.status, kStatusTimeoutTma);
         if (ok && i >= DB)  // the gradient warps have read this copy of D1
-          ok = mbar_wait(&barD1Free[db], ((i / DB) - 1) & 1, abortp, p.status, kStatusTimeoutOperand);
+          ok = mbar_wait(&barD1Free[db], dph, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t wK = smem_u32(smemW + (size_t)s * wStage);
+        const uint64_t bW0 = descW + (uint64_t)((uint32_t)(s * wStage) >> 4);
         const uint32_t d1 = tBase + cD1 + db * TB;
-        for (int ks = 0; ks < kSteps1; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * kBoxBytes + (ks & 3) * 32);
-          const uint64_t bW = smem_desc_sw128(wK + off, 16, 1024);
-          mma_tf32_ts(d1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
-          if (PSPLIT) mma_tf32_ts(d1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {  // Ku <= 128: at most 16 k-steps, constants when unrolled
+          if (ks < kSteps1) {
+            const uint64_t bW = bW0 + (uint64_t)(((ks >> 2) * kBoxBytes + (ks & 3) * 32) >> 4);
+            mma_tf32_ts(d1, tBase + cPhi + ks * 8, bW, idesc1, ks ? 1u : 0u);
+            if (PSPLIT) mma_tf32_ts(d1, tBase + cPlo + ks * 8, bW, idesc1, 1u);
+          }
         }
         mma_commit(&barD1Full[db]);
         mma_commit(&barWFree[s]);
+        if (++s == SW) { s = 0; wph ^= 1u; }
+        if (++db == DB) { db = 0; dph ^= 1u; }
       }
     }
   } else if (warp == kWarpMma2) {
     // ---------------- MMA issuer 2: GEMM2, D2[v, u] += expE^T . W over all tiles ----------------
     if (lane == 0) {
       const uint32_t idesc2 = idesc_tf32(128, p.N2, 0, 1);  // B = W tile, MN-major (K = t)
+      // descriptor of the MN-major copy in W stage 0, frames 0..7: 8 frames = two 4-row atoms 512
+      // bytes apart; 32-column atoms one box apart
+      const uint64_t descW = smem_desc_sw128_base32(smem_u32(smemW) + (uint32_t)wBytes, (uint32_t)kBoxBytes, 512);
       bool ok = true;
+      int s = 0, eb = 0;
+      uint32_t wph = 0, eph = 0;
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int s = i % SW;
-        const int eb = i % EB;
         const uint32_t cEhi = cE + eb * kECols, cElo = cEhi + TB;
-        ok = mbar_wait(&barWFull[s], (i / SW) & 1, abortp, p.status, kStatusTimeoutTma) &&
-             mbar_wait(&barEReady[eb], (i / EB) & 1, abortp, p.status, kStatusTimeoutOperand);
+        ok = mbar_wait(&barWFull[s], wph, abortp, p.status, kStatusTimeoutTma) &&
+             mbar_wait(&barEReady[eb], eph, abortp, p.status, kStatusTimeoutOperand);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t wMn = smem_u32(smemW + (size_t)s * wStage) + (uint32_t)wBytes;
+        const uint64_t bW0 = descW + (uint64_t)((uint32_t)(s * wStage) >> 4);
+#pragma unroll
         for (int ks = 0; ks < TB / 8; ++ks) {
-          // 8 frames = two 4-row atoms 512 bytes apart; 32-column atoms one box apart
-          const uint64_t bW = smem_desc_sw128_base32(wMn + ks * 1024, (uint32_t)kBoxBytes, 512);
+          const uint64_t bW = bW0 + (uint64_t)((ks * 1024) >> 4);
           mma_tf32_ts(tBase + cD2, tBase + cEhi + ks * 8, bW, idesc2, (i | ks) ? 1u : 0u);
           if (ESPLIT) mma_tf32_ts(tBase + cD2, tBase + cElo + ks * 8, bW, idesc2, 1u);
         }
         mma_commit(&barE2Free[eb]);
         mma_commit(&barWFree[s]);
+        if (++s == SW) { s = 0; wph ^= 1u; }
+        if (++eb == EB) { eb = 0; eph ^= 1u; }
       }
       if (ok) mma_commit(&barD2Done);
     }
