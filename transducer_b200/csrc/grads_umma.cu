@@ -300,11 +300,12 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       tma_prefetch_desc(&tm.Wmn);
     }
     int issued = 0;
+    int s = 0;
+    uint32_t wph = 1;  // phase of the PREVIOUS release of the stage (no division by a run-time ring
+                       // depth in the per-tile loops: it costs a warp ~100 cycles each time)
     for (int i = 0; i < nTiles; ++i) {
-      const int s = i % SW;
       bool ok = true;
-      if (i >= SW)
-        ok = mbar_wait(&barWFree[s], ((i / SW) - 1) & 1, abortp, p.status, kStatusTimeoutStageFree);
+      if (i >= SW) ok = mbar_wait(&barWFree[s], wph, abortp, p.status, kStatusTimeoutStageFree);
       if (!__all_sync(0xffffffffu, ok)) break;
       uint8_t* st = smemW + (size_t)s * wStage;
       const int t0 = i * TB;
@@ -316,6 +317,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
       }
       issued = i + 1;
+      if (++s == SW) { s = 0; wph ^= 1u; }
     }
     if (lane == 0 && *abortp) {
       for (int i = max(0, issued - SW); i < issued; ++i) {
@@ -442,13 +444,15 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
     if (grp == 0) {
       // ---- exp group: raw E -> exp(E - ref), in place, and into TMEM as GEMM2's A operand ----
+      int se = 0, eb = 0;          // E stage and expE^T copy of tile i
+      uint32_t sph = 0, eph = 0;   // and their phases
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int se = i % SE, eb = i % EB, t0 = i * TB;
+        const int t0 = i * TB;
         // live frames in my half (may be <= 0); none for a column beyond the vocabulary
         const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
-        ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma);
+        ok = mbar_wait(&barEFull[se], sph, abortp, p.status, kStatusTimeoutTma);
         if (ok && i >= EB)  // this copy of expE^T must have been consumed by GEMM2
-          ok = mbar_wait(&barE2Free[eb], ((i / EB) - 1) & 1, abortp, p.status, kStatusTimeoutMma);
+          ok = mbar_wait(&barE2Free[eb], eph ^ 1u, abortp, p.status, kStatusTimeoutMma);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -491,6 +495,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         __syncwarp();
         // exp(E - ref) of the tile is in TMEM and the raw tile in shared memory is dead
         if (lane == 0) mbar_arrive(&barEReady[eb]);
+        if (++se == SE) { se = 0; sph ^= 1u; }
+        if (++eb == EB) { eb = 0; eph ^= 1u; }
       }
     } else {
       // ---- gradient group: egrads tile = expE * D1 - sparse (delta_b is inside W and the rows) ----
@@ -504,13 +510,14 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
           else extraMine = true;
         }
       }
+      int se = 0, eb = 0, db = 0;            // E stage, expE^T copy and D1 copy of tile i
+      uint32_t sph = 0, eph = 0, dph = 0;    // and their phases
       for (int i = 0; i < nTiles && ok; ++i) {
-        const int se = i % SE, t0 = i * TB;
+        const int t0 = i * TB;
         const int tValid = vOk ? min(TB, T - t0) - h * TBH : 0;
-        const int eb = i % EB, db = i % DB;
-        ok = mbar_wait(&barEFull[se], (i / SE) & 1, abortp, p.status, kStatusTimeoutTma) &&
-             mbar_wait(&barD1Full[db], (i / DB) & 1, abortp, p.status, kStatusTimeoutMma) &&
-             mbar_wait(&barEReady[eb], (i / EB) & 1, abortp, p.status, kStatusTimeoutOperand);
+        ok = mbar_wait(&barEFull[se], sph, abortp, p.status, kStatusTimeoutTma) &&
+             mbar_wait(&barD1Full[db], dph, abortp, p.status, kStatusTimeoutMma) &&
+             mbar_wait(&barEReady[eb], eph, abortp, p.status, kStatusTimeoutOperand);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -566,6 +573,9 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         fence_proxy_async_smem();  // the tile is read next by TMA stores
         __syncwarp();
         if (lane == 0) mbar_arrive(&barStore[se]);  // my part of the gradient tile is in place
+        if (++se == SE) { se = 0; sph ^= 1u; }
+        if (++eb == EB) { eb = 0; eph ^= 1u; }
+        if (++db == DB) { db = 0; dph ^= 1u; }
       }
     }
 

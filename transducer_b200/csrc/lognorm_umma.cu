@@ -366,12 +366,11 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
       tma_prefetch_desc(&tmE);
       tma_prefetch_desc(&tmHi);
       tma_prefetch_desc(&tmLo);
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t ph = 1;  // phase of the PREVIOUS release of the stage (stage and phase are carried
+                        // along: a division by the run-time ring depth costs a lone thread ~100 cycles)
       for (int c = 0; c < nChunks; ++c) {
-        const int s = c % S;
-        if (c >= S && !mbar_wait(&barDone[s], ((c / S) - 1) & 1, abortp, p.status,
-                                 kStatusTimeoutStageFree))
-          break;
+        if (c >= S && !mbar_wait(&barDone[s], ph, abortp, p.status, kStatusTimeoutStageFree)) break;
         uint8_t* st = smem + (size_t)s * stageBytes;
         mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
         const int col = chunkOf(c) * kChunkK;
@@ -379,6 +378,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], col, 0, b);
         tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], col, 0, b);
         issued = c + 1;
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
       if (*abortp) {
         // after an abort: give the copies still in flight a bounded time to land
@@ -402,12 +402,16 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     if (lane == 0 && m < nAcc) {
       const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
       bool ok = true;
+      int s = -1;
+      uint32_t ph = 1;
       for (int c = 0; c < nChunks && ok; ++c) {
-        const int s = c % S, g = c / kGroup, a = g % nAcc;
+        if (++s == S) s = 0;
+        if (s == 0) ph ^= 1u;   // stage c % S, phase (c / S) & 1, without the division
+        const int g = c / kGroup, a = (nAcc == 2) ? (g & 1) : 0;
         if (a != m) continue;
-        const uint32_t ph = (c / S) & 1;
+        const int gUse = (nAcc == 2) ? (g >> 1) : g;   // how often accumulator a was used before
         if (c % kGroup == 0 && g >= nAcc)
-          ok = mbar_wait(&barAccEmpty[a], ((g / nAcc) - 1) & 1, abortp, p.status,
+          ok = mbar_wait(&barAccEmpty[a], (gUse - 1) & 1, abortp, p.status,
                          kStatusTimeoutStageFree);
         // the transform warps arrive on barReady only after they saw barFull complete, so
         // the copies of this stage (the exp(P) tiles among them) have landed as well
@@ -447,9 +451,10 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     // chunk without any costs one comparison and no shared-memory access
     int nextCol = (gather && nLab > 0) ? (sKey[0] >> 8) : 0x7fffffff;
     float* elCol = gather ? p.EL + (i64)b * p.maxU * p.maxT + t0 + r : nullptr;  // my frame
+    int s = grp % S;
+    uint32_t ph = (grp / S) & 1;
     for (int c = grp; c < nChunks && ok; c += NTW) {
-      const int s = c % S;
-      ok = mbar_wait(&barFull[s], (c / S) & 1, abortp, p.status, kStatusTimeoutTma);
+      ok = mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
       if (!ok) break;
       const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
@@ -533,6 +538,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         mbar_arrive(&barReady[s]);
         if (c == 0) mbar_arrive(&barRef);
       }
+      s += NTW;   // (NTW <= 2 steps at a time; the ring holds at least one stage)
+      while (s >= S) { s -= S; ph ^= 1u; }
     }
   } else {
     // ---------------- accumulator drain + epilogue ----------------
@@ -546,8 +553,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     for (int j = 0; j < kDrainCols; ++j) sum[j] = 0.0f;
     bool ok = true;
     for (int g = 0; g < nGroups && ok; ++g) {
-      const int a = g % nAcc;
-      ok = mbar_wait(&barAccFull[a], (g / nAcc) & 1, abortp, p.status, kStatusTimeoutMma);
+      const int a = (nAcc == 2) ? (g & 1) : 0;
+      ok = mbar_wait(&barAccFull[a], ((nAcc == 2) ? (g >> 1) : g) & 1, abortp, p.status, kStatusTimeoutMma);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
