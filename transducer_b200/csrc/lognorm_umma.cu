@@ -774,10 +774,16 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
       auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
-    } else {
-      auto k = lognorm_umma_kernel<1, 2, 128>;  // 4 transform + 8 drain (128 columns each) warps
+    } else if (nPad <= 192) {
+      // wider label axes: one drain warpgroup per 64 accumulator columns (a thread that keeps 128
+      // running sums spills them), a single accumulator and a single MMA issuer
+      auto k = lognorm_umma_kernel<1, 3, 64>;   // 4 transform + 12 drain warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 15 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+    } else {
+      auto k = lognorm_umma_kernel<1, 4, 64>;   // 4 transform + 16 drain warps
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      k<<<grid, 23 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     }
   }
   TB200_CHECK_LAUNCH();
