@@ -638,13 +638,13 @@ def parity_block(w, r, device_case, state):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the named
 # kernel on this workload (1-pass captures at the bench size).  Keyed by (workload, kernel).
 NCU_TRAFFIC_BYTES = {
-    ("c3", "grads_umma"): 2466260480 + 2679300608,
-    ("c3", "lognorm_umma"): 2625806848 + 14500608,
-    ("c3", "alpha_warp"): 60119296 + 1955328,
-    ("c3", "gamma_warp"): 91227136 + 11807488,
-    ("c3", "lattice_prep"): 532158720 + 43793664,
-    ("c3", "expp_split"): 144711680 + 230021888,
-    ("c3", "lattice_unskew_round"): 65938432 + 18867200,
+    ("c3", "grads_umma"): 2460688896 + 2661452288,
+    ("c3", "lognorm_umma"): 2626279936 + 35040256,
+    ("c3", "alpha_warp"): 60133120 + 2445056,
+    ("c3", "gamma_warp"): 91231744 + 11596032,
+    ("c3", "lattice_prep"): 42460416 + 7390976,
+    ("c3", "expp_split"): 146920704 + 230604288,
+    ("c3", "lattice_unskew_round"): 65933568 + 19291904,
 }
 
 

@@ -500,16 +500,12 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       }
     } else {
       // ---- gradient group: egrads tile = expE * D1 - sparse (delta_b is inside W and the rows) ----
-      const float* embT = p.emT + (i64)b * p.maxU * p.ldT;
       // which of the block's label positions carry MY column (almost always none)
+      // (labels of this block beyond the kMaxStagedLabels staged ones are subtracted afterwards by
+      // label_overflow_kernel; that only happens for tiny vocabularies)
       unsigned stagedMine = 0;
-      bool extraMine = false;
-      for (int k = 0; k < nList; ++k) {
-        if (sListV[k] == vl) {
-          if (k < nStaged) stagedMine |= 1u << k;
-          else extraMine = true;
-        }
-      }
+      for (int k = 0; k < nStaged; ++k)
+        if (sListV[k] == vl) stagedMine |= 1u << k;
       int se = 0, eb = 0, db = 0;            // E stage, expE^T copy and D1 copy of tile i
       uint32_t sph = 0, eph = 0, dph = 0;    // and their phases
       for (int i = 0; i < nTiles && ok; ++i) {
@@ -555,14 +551,6 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
           const float* m = rows + (1 + (__ffs(m0) - 1)) * (kRowStride / 4);
 #pragma unroll
           for (int j = 0; j < TBH; ++j) d1[j] -= m[j];
-        }
-        for (int k = nStaged; extraMine && k < nList; ++k) {  // more labels than are staged
-          if (sListV[k] == vl) {
-            const float* m = embT + (i64)sListU[k] * p.ldT + t0 + h * TBH;
-#pragma unroll
-            for (int j = 0; j < TBH; ++j)
-              if (j < tValid) d1[j] -= m[j];
-          }
         }
 #pragma unroll
         for (int j = 0; j < TBH; ++j) {
@@ -740,6 +728,55 @@ __global__ void __launch_bounds__(1024, 2) unskew_round_kernel(
   }
 }
 
+// Label-arc terms that grads_umma_kernel does not stage: within one block of 128 vocabulary
+// columns it subtracts the occupancies of the first kMaxStagedLabels label positions (in
+// position order) whose label falls into the block; with a vocabulary of ten thousand entries a
+// block sees one or two labels, but a vocabulary of 100 puts all of an utterance's labels into
+// one block.  The remaining positions are applied here, one CTA per (block, utterance, 1024
+// frames), in position order (so that repeated labels are combined in a fixed order):
+//   egrads[b, t, label_u] -= emT[b, u, t]        (emT already carries delta_b)
+// The CTA rebuilds the block's list exactly as the gradient kernel does and returns at once if
+// it is short enough, which is the normal case.
+__global__ void __launch_bounds__(256) label_overflow_kernel(
+    const int* __restrict__ labels, const float* __restrict__ emT, float* __restrict__ egrads,
+    const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
+    int ldT) {
+  __shared__ short sU[128];
+  __shared__ short sV[128];
+  __shared__ int sCount;
+  const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
+  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  if (T <= 0 || U <= 1) return;
+  __shared__ int sLab[128];
+  int mine = -1;
+  if ((int)threadIdx.x < U - 1 && threadIdx.x < 128) mine = labels[(i64)b * (maxU - 1) + threadIdx.x];
+  if (threadIdx.x < 128) sLab[threadIdx.x] = mine;
+  // the normal case, decided by all threads at once: the block holds no more labels than are staged
+  if (__syncthreads_count(mine >= v0 && mine < v0 + kVBlock) <= kMaxStagedLabels) return;
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int u = 0; u < U - 1 && u < 128; ++u) {
+      const int lab = sLab[u];
+      if (lab >= v0 && lab < v0 + kVBlock) {
+        if (n >= kMaxStagedLabels) {
+          sU[n - kMaxStagedLabels] = (short)u;
+          sV[n - kMaxStagedLabels] = (short)(lab - v0);
+        }
+        ++n;
+      }
+    }
+    sCount = max(0, n - kMaxStagedLabels);
+  }
+  __syncthreads();
+  // a thread owns frames t = blockIdx.z * 1024 + thread + 256 j and applies the positions one
+  // after the other, so repeated labels are combined in position order
+  const int n = sCount;
+  for (int t = blockIdx.z * 1024 + threadIdx.x; t < min(T, (int)(blockIdx.z + 1) * 1024); t += 256) {
+    float* row = egrads + ((i64)b * maxT + t) * V + v0;
+    for (int k = 0; k < n; ++k) row[sV[k]] -= emT[((i64)b * maxU + sU[k]) * ldT + t];
+  }
+}
+
 struct TileCfg {
   int TB, SE, SW, EB, DB;
 };
@@ -872,6 +909,13 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
 #undef GO_TB
 #undef GO
   TB200_CHECK_LAUNCH();
+  // only a vocabulary block that can hold more labels than are staged needs the second kernel
+  if (d.maxU - 1 > kMaxStagedLabels) {
+    ScopedKernel sk("label_overflow", stream);
+    label_overflow_kernel<<<dim3(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024)), 256, 0, stream>>>(
+        labels, emT, egrads, inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
+    TB200_CHECK_LAUNCH();
+  }
 }
 
 }  // namespace tb200
