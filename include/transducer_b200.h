@@ -58,6 +58,8 @@ void* tb200_get_stream(void);
  *                   pgrads); 3: exp(P) split as well (smaller tiles, slower)
  *   "fused_gather"  1 (default): the tensor-core log-normaliser also hands out E[t,label_u] and
  *                   E[t,blank] from the rows it streams; 0: a separate gather pass fetches them
+ *   "maxplus_path"  label-arc scores of the Viterbi pass (tb200_label_arc_scores): 0 auto,
+ *                   1 the full loop over the alphabet, 2 candidate lists with an exact bound
  * Unknown keys return TB200_ERR_INVALID_ARGUMENT.  No counterpart in the reference. */
 int tb200_set_option(const char* key, int value);
 int tb200_get_option(const char* key, int* value);
@@ -194,6 +196,22 @@ int tb200_loss_backward(const float* emissions, const float* predictions,
                         int batchSize, int maxInputLength, int maxLabelLength,
                         int alphabetSize, int blank, void* workspace,
                         size_t workspaceBytes);
+
+/* transducer/transducer_cuda.cu:233-242, transducer_cpu.cpp:156-169 (the loop over the
+ * alphabet inside the Viterbi sweep), for every lattice node at once:
+ * best[b,t,u] = max over v != blank of emissions[b,t,v] + predictions[b,u,v], written for
+ * t < inputLengths[b], u < labelLengths[b] (row-major [batchSize, maxInputLength,
+ * maxLabelLength]; other entries untouched).  Alphabets of 1024 words and more are evaluated
+ * from per-frame and per-position candidate lists with an exact bound (bit-identical to the
+ * full loop; nodes the bound does not settle are evaluated in full);
+ * tb200_set_option("maxplus_path", 1) forces the full loop, 2 the lists. */
+size_t tb200_label_arc_scores_workspace_bytes(int batchSize, int maxInputLength,
+                                              int maxLabelLength, int alphabetSize);
+int tb200_label_arc_scores(const float* emissions, const float* predictions,
+                           const int* inputLengths, const int* labelLengths, float* best,
+                           int batchSize, int maxInputLength, int maxLabelLength,
+                           int alphabetSize, int blank, void* workspace,
+                           size_t workspaceBytes);
 
 /* transducer/torch_binding.py:130-177 (TransducerLoss.viterbi): log-normalisers +
  * best path, all temporaries in the caller's workspace. */

@@ -121,6 +121,17 @@ def viterbi_decode(E, P, il, ll, blank=0, fill=-1):
     return out
 
 
+def label_arc_scores(E, P, il, ll, blank=0, fill=float("nan")):
+    B, T, U, V = shapes(E, P)
+    out = torch.full((B, T, U), fill, dtype=torch.float32, device="cuda")
+    n = lib.tb200_label_arc_scores_workspace_bytes(B, T, U, V)
+    ws = workspace(max(n, 256))
+    use_torch_stream()
+    check(lib.tb200_label_arc_scores(ptr(E), ptr(P), ptr(il), ptr(ll), ptr(out), B, T, U, V,
+                                     blank, ptr(ws), n))
+    return out
+
+
 def case_to_device(c):
     """numpy case dict (E,P,labels,in_lens,lab_lens[,deltas]) -> device tensors."""
     d = dict(E=dev(c["E"]), P=dev(c["P"]), labels=dev(c["labels"], torch.int32),

@@ -48,6 +48,8 @@ SIGNATURES = {
     "tb200_loss_forward": (_i, [_p] * 8 + [_z] + [_i] * 5 + [_p, _z]),
     "tb200_loss_backward_workspace_bytes": (_z, [_i] * 4),
     "tb200_loss_backward": (_i, [_p] * 6 + [_z] + [_p] * 3 + [_i] * 5 + [_p, _z]),
+    "tb200_label_arc_scores_workspace_bytes": (_z, [_i] * 4),
+    "tb200_label_arc_scores": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
     "tb200_viterbi_decode_workspace_bytes": (_z, [_i] * 4),
     "tb200_viterbi_decode": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
 }

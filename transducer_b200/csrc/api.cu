@@ -25,6 +25,7 @@ struct Options {
   std::atomic<int> grads_path{0};
   std::atomic<int> grad_passes{2};
   std::atomic<int> fused_gather{1};
+  std::atomic<int> maxplus_path{0};   // 0 auto, 1 dense, 2 pruned (error if unsupported)
 };
 Options g_opt;
 
@@ -135,6 +136,7 @@ struct ViterbiWs {
   float *LN, *rowRef, *maxP, *best;
   uint32_t* decBits;
   float4* nodes;  // skewed per-node operands of the single-warp sweep (label axis <= 256)
+  char* prune;    // candidate lists of the pruned max-plus (null where it does not apply)
   ViterbiWs(Carver& c, const Dims& d) {
     const size_t B = d.B, T = d.maxT, U = d.maxU;
     LN = c.take<float>(B * T * U);
@@ -143,8 +145,22 @@ struct ViterbiWs {
     best = c.take<float>(B * T * U);
     decBits = c.take<uint32_t>(std::max(viterbi_decbits_words(d), viterbi_warp_decbits_words(d)));
     nodes = c.take<float4>(viterbi_warp_nodes(d));
+    prune = c.take<char>(maxplus_pruned_scratch_bytes(d));
   }
 };
+
+// Label-arc scores of every node, by the pruned evaluation where it applies.
+void best_label_scores(const float* E, const float* P, float* best, const int* inLens,
+                       const int* labLens, const Dims& d, void* pruneScratch) {
+  const bool can = maxplus_pruned_supported(d) && pruneScratch != nullptr;
+  if (g_opt.maxplus_path == 2 && !can)
+    throw std::invalid_argument("pruned max-plus does not apply to these sizes");
+  if (can && g_opt.maxplus_path != 1)
+    launch_maxplus_pruned(E, P, best, inLens, labLens, d, pruneScratch, device_status_word(),
+                          g_stream);
+  else
+    launch_maxplus(E, P, best, inLens, labLens, d, g_stream);
+}
 
 void need(size_t have, size_t want, const void* ws) {
   if (want > 0 && (ws == nullptr || have < want))
@@ -208,6 +224,7 @@ int tb200_set_option(const char* key, int value) {
   else if (!strcmp(key, "grads_path") && value >= 0 && value <= 2) g_opt.grads_path = value;
   else if (!strcmp(key, "grad_passes") && value >= 1 && value <= 3) g_opt.grad_passes = value;
   else if (!strcmp(key, "fused_gather") && value >= 0 && value <= 1) g_opt.fused_gather = value;
+  else if (!strcmp(key, "maxplus_path") && value >= 0 && value <= 2) g_opt.maxplus_path = value;
   else return fail(kErrInvalidArgument, std::string("unknown option or bad value: ") + key);
   return kOk;
 }
@@ -218,6 +235,7 @@ int tb200_get_option(const char* key, int* value) {
   else if (!strcmp(key, "grads_path")) *value = g_opt.grads_path;
   else if (!strcmp(key, "grad_passes")) *value = g_opt.grad_passes;
   else if (!strcmp(key, "fused_gather")) *value = g_opt.fused_gather;
+  else if (!strcmp(key, "maxplus_path")) *value = g_opt.maxplus_path;
   else return fail(kErrInvalidArgument, std::string("unknown option: ") + key);
   return kOk;
 }
@@ -284,11 +302,13 @@ int tb200_viterbi(const float* E, const float* P, const float* LN, int* labels,
       float* best = nullptr;
       uint32_t* dec = nullptr;
       float4* nodes = nullptr;
+      void* prune = nullptr;
       cudaStream_t stream;
       ~Temporaries() {
         if (best) cudaFreeAsync(best, stream);
         if (dec) cudaFreeAsync(dec, stream);
         if (nodes) cudaFreeAsync(nodes, stream);
+        if (prune) cudaFreeAsync(prune, stream);
       }
     } tmp;
     tmp.stream = g_stream;
@@ -297,7 +317,9 @@ int tb200_viterbi(const float* E, const float* P, const float* LN, int* labels,
     if (warp)
       TB200_CUDA_CHECK(cudaMallocAsync((void**)&tmp.nodes, sizeof(float4) * viterbi_warp_nodes(d),
                                        g_stream));
-    launch_maxplus(E, P, tmp.best, inLens, labLens, d, g_stream);
+    if (maxplus_pruned_supported(d) && g_opt.maxplus_path != 1)
+      TB200_CUDA_CHECK(cudaMallocAsync(&tmp.prune, maxplus_pruned_scratch_bytes(d), g_stream));
+    best_label_scores(E, P, tmp.best, inLens, labLens, d, tmp.prune);
     if (warp)
       launch_viterbi_warp(E, P, LN, tmp.best, tmp.nodes, tmp.dec, labels, inLens, labLens, d,
                           device_status_word(), g_stream);
@@ -436,6 +458,24 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
   });
 }
 
+size_t tb200_label_arc_scores_workspace_bytes(int B, int maxT, int maxU, int V) {
+  Dims d{B, maxT, maxU, V, 0};
+  return (maxplus_pruned_scratch_bytes(d) + 255) & ~size_t(255);
+}
+
+int tb200_label_arc_scores(const float* E, const float* P, const int* inLens, const int* labLens,
+                           float* best, int B, int maxT, int maxU, int V, int blank,
+                           void* workspace, size_t workspaceBytes) {
+  return guarded([&] {
+    Dims d{B, maxT, maxU, V, blank};
+    check_dims(d);
+    need(workspaceBytes, tb200_label_arc_scores_workspace_bytes(B, maxT, maxU, V), workspace);
+    if (B == 0 || maxT == 0 || maxU == 0) return;
+    best_label_scores(E, P, best, inLens, labLens, d,
+                      maxplus_pruned_supported(d) ? workspace : nullptr);
+  });
+}
+
 size_t tb200_viterbi_decode_workspace_bytes(int B, int maxT, int maxU, int V) {
   Dims d{B, maxT, maxU, V, 0};
   Carver c(nullptr);
@@ -456,7 +496,7 @@ int tb200_viterbi_decode(const float* E, const float* P, const int* inLens,
     ViterbiWs ws(c, d);
     LogNormWs lw(c, d);
     log_norms_impl(E, P, ws.LN, ws.rowRef, ws.maxP, inLens, labLens, d, lw);
-    launch_maxplus(E, P, ws.best, inLens, labLens, d, g_stream);
+    best_label_scores(E, P, ws.best, inLens, labLens, d, ws.prune);
     if (viterbi_warp_supported(d))
       launch_viterbi_warp(E, P, ws.LN, ws.best, ws.nodes, ws.decBits, labels, inLens, labLens, d,
                           device_status_word(), g_stream);

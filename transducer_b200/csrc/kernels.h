@@ -179,8 +179,20 @@ void launch_viterbi_warp(const float* E, const float* P, const float* LN, const 
                          const int* labLens, Dims d, int* status, cudaStream_t stream);
 
 // ---- maxplus.cu --------------------------------------------------------------
+// best[b,t,u] = max over v != blank of E[b,t,v] + P[b,u,v] for t < T_b, u < U_b - 1.  With
+// `guard`, the kernel does nothing unless *guard > guardCap (read on the device).
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,
-                    const int* labLens, Dims d, cudaStream_t stream);
+                    const int* labLens, Dims d, cudaStream_t stream, const int* guard = nullptr,
+                    int guardCap = 0);
+
+// ---- maxplus_pruned.cu -------------------------------------------------------
+// The same result, bit for bit, from candidate lists with an exact bound; nodes the bound does
+// not settle are evaluated densely.  `scratch` holds maxplus_pruned_scratch_bytes(d) bytes.
+bool maxplus_pruned_supported(Dims d);
+size_t maxplus_pruned_scratch_bytes(Dims d);
+void launch_maxplus_pruned(const float* E, const float* P, float* best, const int* inLens,
+                           const int* labLens, Dims d, void* scratch, int* status,
+                           cudaStream_t stream);
 
 // ---- grads_simt.cu -----------------------------------------------------------
 // egrads[b,t,v] = delta_b*(exp(E-rowRef)*sum_u W[t,u]*expP[u,v] - [v==blank]*eBlank[t]),

@@ -18,7 +18,8 @@ constexpr int TM = 64, TN = 64, TK = 16;
 __global__ void __launch_bounds__(256) maxplus_kernel(
     const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ best,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU,
-    int V, int blank) {
+    int V, int blank, const int* __restrict__ guard, int guardCap) {
+  if (guard != nullptr && *guard <= guardCap) return;
   __shared__ __align__(16) float Es[TK][TM + 4];
   __shared__ __align__(16) float Ps[TK][TN + 4];
   const int b = blockIdx.z, t0 = blockIdx.y * TM, u0 = blockIdx.x * TN;
@@ -88,7 +89,8 @@ template <int NT>
 __global__ void __launch_bounds__(256) maxplus_tiled_kernel(
     const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ best,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU,
-    int V, int blank) {
+    int V, int blank, const int* __restrict__ guard, int guardCap) {
+  if (guard != nullptr && *guard <= guardCap) return;
   constexpr int BN = 16 * NT;
   constexpr int kPLoads = (BN * 4 + 255) / 256;  // float4 loads of the P tile per thread
   __shared__ __align__(16) float Es[2][BK][BM + 4];
@@ -190,9 +192,10 @@ __global__ void __launch_bounds__(256) maxplus_tiled_kernel(
 }  // namespace
 
 void launch_maxplus(const float* E, const float* P, float* best, const int* inLens,
-                    const int* labLens, Dims d, cudaStream_t stream) {
+                    const int* labLens, Dims d, cudaStream_t stream, const int* guard,
+                    int guardCap) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 1) return;
-  ScopedKernel sk("maxplus", stream);
+  ScopedKernel sk(guard ? "maxplus_if_unsettled" : "maxplus", stream);
   const bool vec = d.V % 4 == 0 && (reinterpret_cast<uintptr_t>(E) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(P) & 15) == 0;
   if (vec) {
@@ -209,7 +212,8 @@ void launch_maxplus(const float* E, const float* P, float* best, const int* inLe
     }
 #define CALL(NT)                                                                         \
   maxplus_tiled_kernel<NT><<<dim3(div_up(n, 16 * NT), div_up(d.maxT, BM), d.B), 256, 0,  \
-                             stream>>>(E, P, best, inLens, labLens, d.maxT, d.maxU, d.V, d.blank)
+                             stream>>>(E, P, best, inLens, labLens, d.maxT, d.maxU, d.V, d.blank,   \
+                                       guard, guardCap)
     switch (bestNT) {
       case 4: CALL(4); break;
       case 5: CALL(5); break;
@@ -220,7 +224,7 @@ void launch_maxplus(const float* E, const float* P, float* best, const int* inLe
   } else {
     dim3 grid(div_up(d.maxU - 1, TN), div_up(d.maxT, TM), d.B);
     maxplus_kernel<<<grid, 256, 0, stream>>>(E, P, best, inLens, labLens, d.maxT, d.maxU, d.V,
-                                             d.blank);
+                                             d.blank, guard, guardCap);
   }
   TB200_CHECK_LAUNCH();
 }
