@@ -31,12 +31,12 @@ namespace {
 using namespace sm100;
 
 constexpr int kETop = 128;    // entries listed per frame
-constexpr int kPTop = 256;    // entries listed per label position
+constexpr int kPTop = 128;    // entries listed per label position
 constexpr int kBatchP = 8;    // list entries fetched at a time beyond the head
 constexpr int kPre = 32;      // entries of every position's list kept in shared memory
 constexpr int kPRows = kPTop + kBatchP;   // rows of a position list in memory
 // A frame's list in memory: offsets v*us (int) [kETop], values [kETop], bound, count, padding.
-// Entries from `count` up to the next multiple of 16 repeat entry 0.
+// Entries from `count` up to the next multiple of 32 repeat entry 0.
 constexpr int kEWords = 2 * kETop + 4;
 constexpr size_t kSelSmemBytes = 96 * 1024;   // rows staged per CTA of the selection kernels
 
@@ -106,7 +106,9 @@ __device__ float pick_threshold(float* row, int V, int vp, int blank, int K, int
   __syncwarp();
   if (lane == 0 && blank >= 0 && blank < V) row[blank] = neg_inf();
   __syncwarp();
+  bool plain = true;   // every entry finite: nothing is above the maximum, all but blank above -inf
   if (!(s2 < 3.0e38f) || !(mn > -3.0e38f)) {
+    plain = false;
     // ... and over the finite entries only if some are not
     mx = neg_inf(); mn = pos_inf(); s = 0.0f; s2 = 0.0f; n = 0;
     for (int v = lane; v < vp; v += 32) {
@@ -117,10 +119,10 @@ __device__ float pick_threshold(float* row, int V, int vp, int blank, int K, int
     }
     mx = warp_max(mx); mn = -warp_max(-mn); s = warp_sum(s); s2 = warp_sum(s2); n = warp_sum_int(n);
   }
-  if (count_above(row, vp, neg_inf(), lane) <= K) return neg_inf();
+  if (plain ? vp - 1 <= K : count_above(row, vp, neg_inf(), lane) <= K) return neg_inf();
   if (n == 0) return pos_inf();                       // only +inf entries, more than K of them
   float hi = mx;                                      // invariant: count(> hi) <= K
-  if (count_above(row, vp, hi, lane) > K) return pos_inf();
+  if (!plain && count_above(row, vp, hi, lane) > K) return pos_inf();
   float lo = mn;
   const float mean = s / n, sd = sqrtf(fmaxf(s2 / n - mean * mean, 0.0f));
   float probe = mean + sd * normal_quantile(fminf(0.5f, 0.75f * K / (float)n));
@@ -210,7 +212,7 @@ __global__ void select_e_kernel(const float* __restrict__ E, int* __restrict__ e
   }
   const float th = pick_threshold(row, V, vp, blank, kETop, lane);
   const float rest = collect_above(row, vp, th, lane, picked[w], &counts[w]);
-  const int n = counts[w], nPad = (n + 15) & ~15;
+  const int n = counts[w], nPad = (n + 31) & ~31;
   for (int k = lane; k < nPad; k += 32) {
     const int2 c = picked[w][k < n ? k : 0];
     out[k] = c.x * us;
@@ -256,24 +258,33 @@ __global__ void select_p_kernel(const float* __restrict__ P, int2* __restrict__ 
   const float th = pick_threshold(row, V, vp, blank, kPTop, lane);
   const float rest = collect_above(row, vp, th, lane, sel, &counts[w]);
   const int n = counts[w];
-  // rank sort (value descending, then index ascending), four entries per lane at a time
+  // rank sort (value descending, then index ascending) on one 64-bit key per entry, four
+  // entries per lane at a time
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(sel);
+  for (int i = lane; i < n; i += 32) {
+    const int2 c = sel[i];
+    const unsigned bits = (unsigned)c.y;   // order-preserving map of the value (no NaN here)
+    const unsigned ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    keys[i] = ((unsigned long long)ord << 32) | (unsigned)(0x7fffffff - c.x);
+  }
+  __syncwarp();
   for (int i0 = 0; i0 < n; i0 += 128) {
-    int2 me[4];
+    unsigned long long me[4];
     int rank[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int m = 0; m < 4; ++m) me[m] = sel[min(i0 + lane + 32 * m, n - 1)];
+    for (int m = 0; m < 4; ++m) me[m] = keys[min(i0 + lane + 32 * m, n - 1)];
     for (int k = 0; k < n; ++k) {
-      const int2 o = sel[k];
-      const float y = __int_as_float(o.y);
+      const unsigned long long o = keys[k];
 #pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        const float x = __int_as_float(me[m].y);
-        rank[m] += (y > x || (y == x && o.x < me[m].x)) ? 1 : 0;
-      }
+      for (int m = 0; m < 4; ++m) rank[m] += (o > me[m]) ? 1 : 0;
     }
 #pragma unroll
     for (int m = 0; m < 4; ++m)
-      if (i0 + lane + 32 * m < n) out[(i64)rank[m] * us] = me[m];
+      if (i0 + lane + 32 * m < n) {
+        const unsigned ord = (unsigned)(me[m] >> 32);
+        const unsigned bits = (ord & 0x80000000u) ? (ord & 0x7fffffffu) : ~ord;
+        out[(i64)rank[m] * us] = make_int2(0x7fffffff - (int)(unsigned)me[m], (int)bits);
+      }
   }
   if (lane == 0) {
     out[(i64)n * us] = make_int2(0, __float_as_int(neg_inf()));
