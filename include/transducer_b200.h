@@ -197,6 +197,29 @@ int tb200_loss_backward(const float* emissions, const float* predictions,
                         int alphabetSize, int blank, void* workspace,
                         size_t workspaceBytes);
 
+/* The same two calls for bf16 storage: emissions, predictions and both gradients are bfloat16
+ * in memory (2 bytes per element), which halves the bytes the path streams.  Every value is
+ * converted exactly to fp32 on the way in, all arithmetic and everything in `saved` is the
+ * fp32 path's, and the gradients are rounded to nearest on the way out: the results are those
+ * of tb200_loss_forward / tb200_loss_backward on the up-converted inputs, the gradients rounded
+ * once.  The reference takes fp32 only (transducer/torch_binding.py:195-197).  Needs
+ * alphabetSize % 8 == 0, maxLabelLength <= 128, 16-byte aligned buffers, and the default
+ * "grad_passes" = 2; otherwise TB200_ERR_INVALID_ARGUMENT.  Saved / workspace sizes are those
+ * of the fp32 calls. */
+int tb200_loss_forward_bf16(const void* emissions, const void* predictions,
+                            const int* labels, const int* inputLengths,
+                            const int* labelLengths, float* costs, float* lossSum,
+                            void* saved, size_t savedBytes, int batchSize,
+                            int maxInputLength, int maxLabelLength, int alphabetSize,
+                            int blank, void* workspace, size_t workspaceBytes);
+int tb200_loss_backward_bf16(const void* emissions, const void* predictions,
+                             const int* labels, const int* inputLengths,
+                             const int* labelLengths, const void* saved, size_t savedBytes,
+                             const float* deltas, void* egrads, void* pgrads,
+                             int batchSize, int maxInputLength, int maxLabelLength,
+                             int alphabetSize, int blank, void* workspace,
+                             size_t workspaceBytes);
+
 /* transducer/transducer_cuda.cu:233-242, transducer_cpu.cpp:156-169 (the loop over the
  * alphabet inside the Viterbi sweep), for every lattice node at once:
  * best[b,t,u] = max over v != blank of emissions[b,t,v] + predictions[b,u,v], written for

@@ -89,24 +89,24 @@ def loss_forward(E, P, labels, il, ll, blank=0):
     n = lib.tb200_loss_forward_workspace_bytes(B, T, U, V)
     ws = workspace(n)
     use_torch_stream()
-    check(lib.tb200_loss_forward(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(out["costs"]),
-                                 ptr(out["loss_sum"]), ptr(out["saved"]), ns, B, T, U, V, blank,
-                                 ptr(ws), n))
+    fn = lib.tb200_loss_forward_bf16 if E.dtype == torch.bfloat16 else lib.tb200_loss_forward
+    check(fn(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(out["costs"]),
+             ptr(out["loss_sum"]), ptr(out["saved"]), ns, B, T, U, V, blank, ptr(ws), n))
     return out
 
 
 def loss_backward(E, P, labels, il, ll, fwd, deltas=None, blank=0):
     B, T, U, V = shapes(E, P)
-    eg = torch.full((B, T, V), float("nan"), device="cuda")
-    pg = torch.full((B, U, V), float("nan"), device="cuda")
+    eg = torch.full((B, T, V), float("nan"), device="cuda", dtype=E.dtype)
+    pg = torch.full((B, U, V), float("nan"), device="cuda", dtype=E.dtype)
     if deltas is None:
         deltas = torch.ones((B,), device="cuda")
     n = lib.tb200_loss_backward_workspace_bytes(B, T, U, V)
     ws = workspace(n)
     use_torch_stream()
-    check(lib.tb200_loss_backward(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(fwd["saved"]),
-                                  fwd["saved"].numel(), ptr(deltas), ptr(eg), ptr(pg), B, T, U, V,
-                                  blank, ptr(ws), n))
+    fn = lib.tb200_loss_backward_bf16 if E.dtype == torch.bfloat16 else lib.tb200_loss_backward
+    check(fn(ptr(E), ptr(P), ptr(labels), ptr(il), ptr(ll), ptr(fwd["saved"]),
+             fwd["saved"].numel(), ptr(deltas), ptr(eg), ptr(pg), B, T, U, V, blank, ptr(ws), n))
     return eg, pg
 
 

@@ -46,6 +46,8 @@ SIGNATURES = {
     "tb200_loss_forward_workspace_bytes": (_z, [_i] * 4),
     "tb200_loss_saved_bytes": (_z, [_i] * 4),
     "tb200_loss_forward": (_i, [_p] * 8 + [_z] + [_i] * 5 + [_p, _z]),
+    "tb200_loss_forward_bf16": (_i, [_p] * 8 + [_z] + [_i] * 5 + [_p, _z]),
+    "tb200_loss_backward_bf16": (_i, [_p] * 6 + [_z] + [_p] * 3 + [_i] * 5 + [_p, _z]),
     "tb200_loss_backward_workspace_bytes": (_z, [_i] * 4),
     "tb200_loss_backward": (_i, [_p] * 6 + [_z] + [_p] * 3 + [_i] * 5 + [_p, _z]),
     "tb200_label_arc_scores_workspace_bytes": (_z, [_i] * 4),

@@ -110,6 +110,36 @@ PYBIND11_MODULE(_transducer, m) {
         "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a, "blank"_a, "workspace"_a,
         "workspace_bytes"_a);
 
+  m.def("loss_forward_bf16",
+        [](addr e, addr p, addr labels, addr ilen, addr llen, addr costs, addr loss_sum,
+           addr saved, size_t savedBytes, int B, int T, int U, int V, int blank, addr ws,
+           size_t wsBytes) {
+          check(tb200_loss_forward_bf16(at<const void>(e), at<const void>(p),
+                                        at<const int>(labels), at<const int>(ilen),
+                                        at<const int>(llen), at<float>(costs), at<float>(loss_sum),
+                                        at<void>(saved), savedBytes, B, T, U, V, blank,
+                                        at<void>(ws), wsBytes));
+        },
+        "emissions"_a, "predictions"_a, "labels"_a, "input_lengths"_a, "label_lengths"_a,
+        "costs"_a, "loss_sum"_a, "saved"_a, "saved_bytes"_a, "batch_size"_a,
+        "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a, "blank"_a, "workspace"_a,
+        "workspace_bytes"_a);
+
+  m.def("loss_backward_bf16",
+        [](addr e, addr p, addr labels, addr ilen, addr llen, addr saved, size_t savedBytes,
+           addr deltas, addr eg, addr pg, int B, int T, int U, int V, int blank, addr ws,
+           size_t wsBytes) {
+          check(tb200_loss_backward_bf16(at<const void>(e), at<const void>(p),
+                                         at<const int>(labels), at<const int>(ilen),
+                                         at<const int>(llen), at<const void>(saved), savedBytes,
+                                         at<const float>(deltas), at<void>(eg), at<void>(pg), B,
+                                         T, U, V, blank, at<void>(ws), wsBytes));
+        },
+        "emissions"_a, "predictions"_a, "labels"_a, "input_lengths"_a, "label_lengths"_a,
+        "saved"_a, "saved_bytes"_a, "deltas"_a, "egrads"_a, "pgrads"_a, "batch_size"_a,
+        "max_input_length"_a, "max_label_length"_a, "alphabet_size"_a, "blank"_a, "workspace"_a,
+        "workspace_bytes"_a);
+
   m.def("loss_backward",
         [](addr e, addr p, addr labels, addr ilen, addr llen, addr saved, size_t savedBytes,
            addr deltas, addr eg, addr pg, int B, int T, int U, int V, int blank, addr ws,

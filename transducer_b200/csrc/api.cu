@@ -171,7 +171,7 @@ void need(size_t have, size_t want, const void* ws) {
 // Log-normalisers plus the row shifts.  With the exact path rowRef is the true row
 // maximum of E.
 // Returns true if the pass also produced the label / blank emissions (EL, ebl) it was offered.
-bool log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+bool log_norms_impl(const void* E, const void* P, float* LN, float* rowRef, float* maxP,
                     const int* inLens, const int* labLens, const Dims& d, LogNormWs& ws,
                     bool fixup = true, const int* labels = nullptr, float* EL = nullptr,
                     float* ebl = nullptr) {
@@ -181,6 +181,10 @@ bool log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
     throw std::invalid_argument(
         "tensor-core log-normaliser needs alphabetSize % 4 == 0, alphabetSize >= 32, "
         "maxLabelLength <= 256 and 16-byte aligned emissions");
+  if (d.dtype != kDtypeF32 && !(can && g_opt.lognorm_path != 1))
+    throw std::invalid_argument(
+        "bf16 emissions need the tensor-core log-normaliser: alphabetSize % 8 == 0, "
+        "alphabetSize >= 32, 16-byte aligned emissions and predictions");
   if (can && g_opt.lognorm_path != 1) {
     // the kernel needs somewhere to put the row shifts even if the caller does not want them
     float* mp = maxP ? maxP : ws.maxPScratch;
@@ -191,9 +195,11 @@ bool log_norms_impl(const float* E, const float* P, float* LN, float* rowRef, fl
                         gathers ? EL : nullptr, gathers ? ebl : nullptr);
     return gathers;
   }
-  launch_lognorm_exact(E, P, LN, inLens, labLens, d, g_stream);
-  if (rowRef) launch_row_max(E, rowRef, inLens, 0, d.B, d.maxT, d.V, g_stream);
-  if (maxP) launch_row_max(P, maxP, labLens, 1, d.B, d.maxU, d.V, g_stream);
+  const float* Ef = static_cast<const float*>(E);
+  const float* Pf = static_cast<const float*>(P);
+  launch_lognorm_exact(Ef, Pf, LN, inLens, labLens, d, g_stream);
+  if (rowRef) launch_row_max(Ef, rowRef, inLens, 0, d.B, d.maxT, d.V, g_stream);
+  if (maxP) launch_row_max(Pf, maxP, labLens, 1, d.B, d.maxU, d.V, g_stream);
   return false;
 }
 
@@ -363,13 +369,17 @@ size_t tb200_loss_forward_workspace_bytes(int B, int maxT, int maxU, int V) {
   return c.total();
 }
 
-int tb200_loss_forward(const float* E, const float* P, const int* labels, const int* inLens,
-                       const int* labLens, float* costs, float* lossSum, void* saved,
-                       size_t savedBytes, int B, int maxT, int maxU, int V, int blank,
-                       void* workspace, size_t workspaceBytes) {
+namespace {
+
+int loss_forward_any(const void* E, const void* P, const int* labels, const int* inLens,
+                     const int* labLens, float* costs, float* lossSum, void* saved,
+                     size_t savedBytes, int B, int maxT, int maxU, int V, int blank,
+                     void* workspace, size_t workspaceBytes, int dtype) {
   return guarded([&] {
-    Dims d{B, maxT, maxU, V, blank};
+    Dims d{B, maxT, maxU, V, blank, dtype};
     check_dims(d);
+    if (dtype != kDtypeF32 && !lattice_warp_supported(d))
+      throw std::invalid_argument("bf16 emissions: the label axis must not exceed 128 positions");
     need(workspaceBytes, tb200_loss_forward_workspace_bytes(B, maxT, maxU, V), workspace);
     need(savedBytes, tb200_loss_saved_bytes(B, maxT, maxU, V), saved);
     Carver cs(saved);
@@ -393,9 +403,27 @@ int tb200_loss_forward(const float* E, const float* P, const int* labels, const 
       launch_alpha_warp(st.arcs, costs, st.alphasS, st.deltas, g, inLens, labLens, d, lossSum,
                         lossSum ? ws.ticket : nullptr, device_status_word(), g_stream);
     else
-      launch_alpha_skew(P, costs, st.alphasS, st.LNs, st.ELs, st.ebl, g, labels, inLens, labLens,
-                        d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
+      launch_alpha_skew(static_cast<const float*>(P), costs, st.alphasS, st.LNs, st.ELs, st.ebl, g,
+                        labels, inLens, labLens, d, lossSum, lossSum ? ws.ticket : nullptr, g_stream);
   });
+}
+
+}  // namespace
+
+int tb200_loss_forward(const float* E, const float* P, const int* labels, const int* inLens,
+                       const int* labLens, float* costs, float* lossSum, void* saved,
+                       size_t savedBytes, int B, int maxT, int maxU, int V, int blank,
+                       void* workspace, size_t workspaceBytes) {
+  return loss_forward_any(E, P, labels, inLens, labLens, costs, lossSum, saved, savedBytes, B, maxT,
+                          maxU, V, blank, workspace, workspaceBytes, kDtypeF32);
+}
+
+int tb200_loss_forward_bf16(const void* E, const void* P, const int* labels, const int* inLens,
+                            const int* labLens, float* costs, float* lossSum, void* saved,
+                            size_t savedBytes, int B, int maxT, int maxU, int V, int blank,
+                            void* workspace, size_t workspaceBytes) {
+  return loss_forward_any(E, P, labels, inLens, labLens, costs, lossSum, saved, savedBytes, B, maxT,
+                          maxU, V, blank, workspace, workspaceBytes, kDtypeBf16);
 }
 
 size_t tb200_loss_backward_workspace_bytes(int B, int maxT, int maxU, int V) {
@@ -405,12 +433,15 @@ size_t tb200_loss_backward_workspace_bytes(int B, int maxT, int maxU, int V) {
   return c.total();
 }
 
-int tb200_loss_backward(const float* E, const float* P, const int* labels, const int* inLens,
-                        const int* labLens, const void* saved, size_t savedBytes,
-                        const float* deltas, float* egrads, float* pgrads, int B, int maxT,
-                        int maxU, int V, int blank, void* workspace, size_t workspaceBytes) {
+namespace {
+
+int loss_backward_any(const void* E, const void* P, const int* labels, const int* inLens,
+                      const int* labLens, const void* saved, size_t savedBytes,
+                      const float* deltas, void* egrads, void* pgrads, int B, int maxT,
+                      int maxU, int V, int blank, void* workspace, size_t workspaceBytes,
+                      int dtype) {
   return guarded([&] {
-    Dims d{B, maxT, maxU, V, blank};
+    Dims d{B, maxT, maxU, V, blank, dtype};
     check_dims(d);
     need(workspaceBytes, tb200_loss_backward_workspace_bytes(B, maxT, maxU, V), workspace);
     need(savedBytes, tb200_loss_saved_bytes(B, maxT, maxU, V), saved);
@@ -428,6 +459,14 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
           "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
           "maxLabelLength <= 128 and 16-byte aligned emissions and egrads");
     const bool tensorCore = can && g_opt.grads_path != 1;
+    if (dtype != kDtypeF32 && !(tensorCore && lattice_warp_supported(d)))
+      throw std::invalid_argument(
+          "bf16 gradients need the tensor-core gradient kernel: alphabetSize % 8 == 0, "
+          "maxLabelLength <= 128, grad_passes = 2, 16-byte aligned buffers");
+    const float* Ef = static_cast<const float*>(E);   // (fp32 from here on where used as such)
+    const float* Pf = static_cast<const float*>(P);
+    float* egf = static_cast<float*>(egrads);
+    float* pgf = static_cast<float*>(pgrads);
     if (lattice_warp_supported(d)) {
       // single-warp reverse sweep: blank/label arc occupancies to the skewed lattices
       // ws.Ws / ws.EMs, then re-laid out for whichever gradient kernels follow
@@ -445,17 +484,35 @@ int tb200_loss_backward(const float* E, const float* P, const int* labels, const
       launch_unskew_round(ws.Ws, ws.EMs, st.LNs, st.rowRef, st.maxP, nullptr, ws.W, ws.em,
                           nullptr, ws.eBlank, inLens, labLens, g, d, false, g_stream);
     } else {
-      launch_gamma_skew(P, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
+      launch_gamma_skew(Pf, st.alphasS, st.LNs, st.ELs, st.ebl, g, st.rowRef, st.maxP, labels,
                         inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
                         g_stream);
       launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
     }
-    launch_exp_rows(P, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
-    launch_egrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
-                      egrads, inLens, labLens, d, g_stream);
-    launch_pgrad_simt(E, st.rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,
-                      pgrads, inLens, labLens, d, g_stream);
+    launch_exp_rows(Pf, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
+    launch_egrad_simt(Ef, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,
+                      egf, inLens, labLens, d, g_stream);
+    launch_pgrad_simt(Ef, st.rowRef, ws.W, ldW, ws.expP, ws.pBlank, ws.pLabel, labels, deltas,
+                      pgf, inLens, labLens, d, g_stream);
   });
+}
+
+}  // namespace
+
+int tb200_loss_backward(const float* E, const float* P, const int* labels, const int* inLens,
+                        const int* labLens, const void* saved, size_t savedBytes,
+                        const float* deltas, float* egrads, float* pgrads, int B, int maxT,
+                        int maxU, int V, int blank, void* workspace, size_t workspaceBytes) {
+  return loss_backward_any(E, P, labels, inLens, labLens, saved, savedBytes, deltas, egrads, pgrads,
+                           B, maxT, maxU, V, blank, workspace, workspaceBytes, kDtypeF32);
+}
+
+int tb200_loss_backward_bf16(const void* E, const void* P, const int* labels, const int* inLens,
+                             const int* labLens, const void* saved, size_t savedBytes,
+                             const float* deltas, void* egrads, void* pgrads, int B, int maxT,
+                             int maxU, int V, int blank, void* workspace, size_t workspaceBytes) {
+  return loss_backward_any(E, P, labels, inLens, labLens, saved, savedBytes, deltas, egrads, pgrads,
+                           B, maxT, maxU, V, blank, workspace, workspaceBytes, kDtypeBf16);
 }
 
 size_t tb200_label_arc_scores_workspace_bytes(int B, int maxT, int maxU, int V) {

@@ -34,6 +34,11 @@ inline void cuda_check(cudaError_t err, const char* file, int line) {
 #define TB200_CUDA_CHECK(expr) ::tb200::cuda_check((expr), __FILE__, __LINE__)
 #define TB200_CHECK_LAUNCH() ::tb200::cuda_check(cudaGetLastError(), __FILE__, __LINE__)
 
+struct bf16 {
+  unsigned short bits;
+};
+constexpr int kDtypeF32 = 0, kDtypeBf16 = 1;
+
 __host__ __device__ inline int div_up(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ inline i64 div_up64(i64 a, i64 b) { return (a + b - 1) / b; }
 __host__ __device__ inline i64 round_up64(i64 a, i64 b) { return div_up64(a, b) * b; }
@@ -48,6 +53,22 @@ __device__ __forceinline__ float lse2(float a, float b) {
   if (a == neg_inf()) return b;
   if (b == neg_inf()) return a;
   return fmaxf(a, b) + log1pf(expf(-fabsf(a - b)));
+}
+
+// Storage types of emissions / predictions / gradients: fp32, or bf16 held as raw bits.  All
+// arithmetic is fp32 on the exactly converted values.
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __uint_as_float((unsigned)x.bits << 16); }
+__device__ __forceinline__ void from_f32(float& d, float x) { d = x; }
+__device__ __forceinline__ void from_f32(bf16& d, float x) {   // round to nearest even
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(d.bits) : "f"(x));
+}
+// four consecutive elements (16-byte resp. 8-byte aligned)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                     __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
 }
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -49,6 +49,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "kernels.h"
 #include "profile.h"
@@ -69,7 +70,7 @@ constexpr int kStageRows = 2 + kMaxStagedLabels;  // row shifts, blank-arc sums,
 constexpr int kMaxRing = 4;
 
 struct GradParams {
-  const float* P;
+  const void* P;         // [B,maxU,V] fp32 or bf16, as are egrads and pgrads
   const float* maxP;     // [B,maxU]
   const float* pBlank;   // [B,maxU]
   const float* pLabel;   // [B,maxU]
@@ -78,8 +79,8 @@ struct GradParams {
   const int* inLens;
   const int* labLens;
   const float* deltas;
-  float* egrads;
-  float* pgrads;
+  void* egrads;
+  void* pgrads;
   int* status;
   int maxT, maxU, V, blank;
   int ldT;      // maxT rounded up to 4: row length of nref / eBlank / emT
@@ -97,8 +98,11 @@ struct GradMaps {
 };
 
 __host__ __device__ constexpr int row_stride_bytes(int tb) { return (tb * 4 + 127) & ~127; }
-__host__ __device__ constexpr int e_stage_bytes(int tb) {
-  return (4 * tb * 128 + kStageRows * row_stride_bytes(tb) + 1023) & ~1023;
+// an E tile is 128 columns x tb frames in boxes of 128-byte rows: 4 boxes of 32 fp32 columns or
+// 2 boxes of 64 bf16 columns
+__host__ __device__ constexpr int e_boxes(bool bf) { return bf ? 2 : 4; }
+__host__ __device__ constexpr int e_stage_bytes(int tb, bool bf = false) {
+  return (e_boxes(bf) * tb * 128 + kStageRows * row_stride_bytes(tb) + 1023) & ~1023;
 }
 
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
@@ -107,24 +111,26 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
 }
 
 // ESPLIT / PSPLIT: split exp(E) / exp(P) into TF32 hi + lo (two MMAs per k-step) instead
-// of rounding once.
-template <int TB, bool ESPLIT, bool PSPLIT>
+// of rounding once.  BF: E, P and both gradients are bf16 in memory (converted exactly to fp32
+// on the way in, rounded to nearest on the way out; everything in between is the fp32 path).
+template <int TB, bool ESPLIT, bool PSPLIT, bool BF = false>
 __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     const __grid_constant__ GradMaps tm, const GradParams p) {
+  using TIO = typename std::conditional<BF, bf16, float>::type;
   constexpr int TBH = TB / 2;  // frames per owner half
   static_assert(TBH % 8 == 0, "tile halves move through TMEM in 8-column pieces");
   const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float delta = p.deltas ? p.deltas[b] : 1.0f;
-  float* eg = p.egrads + (i64)b * p.maxT * p.V;
-  float* pg = p.pgrads + (i64)b * p.maxU * p.V;
+  TIO* eg = static_cast<TIO*>(p.egrads) + (i64)b * p.maxT * p.V;
+  TIO* pg = static_cast<TIO*>(p.pgrads) + (i64)b * p.maxU * p.V;
 
   if (T <= 0 || U <= 0) {  // nothing flows through this utterance: gradients are zero
     const int v = v0 + threadIdx.x;
     if (threadIdx.x < kVBlock && v < p.V) {
-      for (int t = 0; t < p.maxT; ++t) eg[(i64)t * p.V + v] = 0.0f;
-      for (int u = 0; u < p.maxU; ++u) pg[(i64)u * p.V + v] = 0.0f;
+      for (int t = 0; t < p.maxT; ++t) from_f32(eg[(i64)t * p.V + v], 0.0f);
+      for (int u = 0; u < p.maxU; ++u) from_f32(pg[(i64)u * p.V + v], 0.0f);
     }
     return;
   }
@@ -134,11 +140,13 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
                                              ~uintptr_t(1023));
   const int SE = p.stagesE, SW = p.stagesW;
   const int nUB = p.ldW / 32;
-  constexpr int kBoxBytes = TB * 128;          // one 32-column box of a tile
-  constexpr int kEBytes = 4 * kBoxBytes;       // E tile
+  constexpr int kBoxBytes = TB * 128;          // one box of a tile: TB rows of 128 bytes
+  constexpr int kBoxes = e_boxes(BF);          // boxes of an E / gradient tile
+  constexpr int kBoxCols = 128 / kBoxes;       // vocabulary columns per box
+  constexpr int kEBytes = kBoxes * kBoxBytes;  // E tile
   constexpr int kRowBytes = TB * 4;            // one row of per-frame scalars
   constexpr int kRowStride = row_stride_bytes(TB);  // TMA destinations are 128-byte aligned
-  constexpr int kEStage = e_stage_bytes(TB);   // E tile + kStageRows rows of scalars
+  constexpr int kEStage = e_stage_bytes(TB, BF);   // E tile + kStageRows rows of scalars
   const int wBytes = nUB * kBoxBytes;
   const int wStage = 2 * wBytes;               // K-major copy, MN-major copy
   uint8_t* smemW = smem + (size_t)SE * kEStage;
@@ -243,13 +251,13 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     const CUtensorMap* myMap = nullptr;
     int myDst = 0, myX = 0, myZ = 0;
     bool yIsT0 = true;   // E: (x = column, y = t0, z = b); scalar rows: (x = t0, y, z)
-    if (lane < 4) {  // (a box beyond the vocabulary reads as zeros and still counts its bytes)
-      myMap = &tm.E; myDst = lane * kBoxBytes; myX = v0 + 32 * lane; myZ = b;
+    if (lane < kBoxes) {  // (a box beyond the vocabulary reads as zeros and still counts its bytes)
+      myMap = &tm.E; myDst = lane * kBoxBytes; myX = v0 + kBoxCols * lane; myZ = b;
     } else if (lane == 4) {
       myMap = &tm.nref; myDst = kEBytes; myX = b; myZ = 0; yIsT0 = false;
     } else if (lane == 5) {
       if (blankHere) { myMap = &tm.ebl; myDst = kEBytes + kRowStride; myX = b; myZ = 0; yIsT0 = false; }
-    } else if (lane - 6 < nStaged) {
+    } else if (lane >= 6 && lane - 6 < nStaged) {
       myMap = &tm.emT; myDst = kEBytes + (lane - 4) * kRowStride; myX = sListU[lane - 6]; myZ = b; yIsT0 = false;
     }
     int fs = 0;  // stage of the next fill
@@ -271,8 +279,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       if (!__all_sync(0xffffffffu, ok)) break;
       // lanes 0..3 store one 32-column box each (every lane has a bulk group of its own), and
       // wait until the store engine has read their box before the stage is refilled
-      if (lane < 4 && v0 + 32 * lane < p.V) {
-        tma_store_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + 32 * lane, i * TB, b);
+      if (lane < kBoxes && v0 + kBoxCols * lane < p.V) {
+        tma_store_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + kBoxCols * lane, i * TB, b);
         tma_store_commit();
         if (issued < nTiles) tma_store_wait_read();
       }
@@ -280,7 +288,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       if (issued < nTiles) fill(issued++);
       if (++ss == SE) { ss = 0; sph ^= 1u; }
     }
-    if (lane < 4) {
+    if (lane < kBoxes) {
       // all stores complete (not only read) before the CTA ends
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -409,7 +417,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
     // expP^T[v, u] = exp(P[u,v] - maxP[u]) for u < U, zero beyond: resident A operand of GEMM1
     {
-      const float* pp = p.P + (i64)b * p.maxU * p.V;
+      const TIO* pp = static_cast<const TIO*>(p.P) + (i64)b * p.maxU * p.V;
       const float* mp = p.maxP + (i64)b * p.maxU;
       const int vc = min(v, p.V - 1);
       for (int u0 = 8 * part; u0 < p.Ku; u0 += 32) {
@@ -418,7 +426,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int uc = min(u0 + j, U - 1);
-          raw[j] = pp[(i64)uc * p.V + vc];
+          raw[j] = to_f32(pp[(i64)uc * p.V + vc]);
           sh[j] = mp[uc];
         }
         uint32_t hi[8], lo[8];
@@ -438,9 +446,13 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       if (lane == 0) mbar_arrive(&barPReady);
     }
 
-    // my column inside an E stage: box q, 4-byte element `lane` of each (swizzled) 128-byte row
-    const int colOff = q * kBoxBytes + (lane & 3) * 4;
-    const int chunk = lane >> 2;
+    // my column inside an E stage: fp32: box q, 4-byte element `lane` of each (swizzled) 128-byte
+    // row; bf16: box q/2, 2-byte element (q&1)*32 + lane
+    const int colOff = BF ? (q >> 1) * kBoxBytes + (lane & 7) * 2 : q * kBoxBytes + (lane & 3) * 4;
+    const int chunk = BF ? (q & 1) * 4 + (lane >> 3) : lane >> 2;
+    auto elemAt = [&](uint8_t* col, int t) {
+      return reinterpret_cast<TIO*>(col + t * 128 + ((chunk ^ (t & 7)) << 4));
+    };
 
     if (grp == 0) {
       // ---- exp group: raw E -> exp(E - ref), in place, and into TMEM as GEMM2's A operand ----
@@ -468,9 +480,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int t = h * TBH + j + k;
-            xs[j + k] = fmaf(
-                *reinterpret_cast<const float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)), kLog2e,
-                shj[k]);
+            xs[j + k] = fmaf(to_f32(*elemAt(col, t)), kLog2e, shj[k]);
           }
         }
         if (tValid < TBH) {  // last tile of the utterance (or a column beyond the vocabulary):
@@ -556,7 +566,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         for (int j = 0; j < TBH; ++j) {
           const int t = h * TBH + j;
           // (frames at or beyond T_b: expE and the rows of W are zero there, so is d1)
-          *reinterpret_cast<float*>(col + t * 128 + ((chunk ^ (t & 7)) << 4)) = d1[j];
+          from_f32(*elemAt(col, t), d1[j]);
         }
         fence_proxy_async_smem();  // the tile is read next by TMA stores
         __syncwarp();
@@ -569,7 +579,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
     // padded frames beyond the last tile: exact zeros
     if (vOk)
-      for (int t = nTiles * TB + part; t < p.maxT; t += 4) eg[(i64)t * p.V + v] = 0.0f;
+      for (int t = nTiles * TB + part; t < p.maxT; t += 4) from_f32(eg[(i64)t * p.V + v], 0.0f);
 
     // pgrads[u, v] = delta * (expP[u,v] * D2[v,u] - sparse)
     if (ok) ok = mbar_wait(&barD2Done, 0, abortp, p.status, kStatusTimeoutMma);
@@ -594,7 +604,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
               if (v == p.blank) val -= delta * sPb[u];
               if (sLab[u] == v) val -= delta * sPl[u];
             }
-            pg[(i64)u * p.V + v] = val;
+            from_f32(pg[(i64)u * p.V + v], val);
           }
         }
       }
@@ -611,8 +621,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     // its whole slice of both gradients becomes NaN rather than a plausible-looking number
     const float bad = __int_as_float(0x7fc00000);
     const int v = v0 + threadIdx.x;
-    for (int t = 0; t < p.maxT; ++t) eg[(i64)t * p.V + v] = bad;
-    for (int u = 0; u < p.maxU; ++u) pg[(i64)u * p.V + v] = bad;
+    for (int t = 0; t < p.maxT; ++t) from_f32(eg[(i64)t * p.V + v], bad);
+    for (int u = 0; u < p.maxU; ++u) from_f32(pg[(i64)u * p.V + v], bad);
   }
 }
 
@@ -737,8 +747,9 @@ __global__ void __launch_bounds__(1024, 2) unskew_round_kernel(
 //   egrads[b, t, label_u] -= emT[b, u, t]        (emT already carries delta_b)
 // The CTA rebuilds the block's list exactly as the gradient kernel does and returns at once if
 // it is short enough, which is the normal case.
+template <typename TIO>
 __global__ void __launch_bounds__(256) label_overflow_kernel(
-    const int* __restrict__ labels, const float* __restrict__ emT, float* __restrict__ egrads,
+    const int* __restrict__ labels, const float* __restrict__ emT, TIO* __restrict__ egrads,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
     int ldT) {
   __shared__ short sU[128];
@@ -772,8 +783,9 @@ __global__ void __launch_bounds__(256) label_overflow_kernel(
   // after the other, so repeated labels are combined in position order
   const int n = sCount;
   for (int t = blockIdx.z * 1024 + threadIdx.x; t < min(T, (int)(blockIdx.z + 1) * 1024); t += 256) {
-    float* row = egrads + ((i64)b * maxT + t) * V + v0;
-    for (int k = 0; k < n; ++k) row[sV[k]] -= emT[((i64)b * maxU + sU[k]) * ldT + t];
+    TIO* row = egrads + ((i64)b * maxT + t) * V + v0;
+    for (int k = 0; k < n; ++k)
+      from_f32(row[sV[k]], to_f32(row[sV[k]]) - emT[((i64)b * maxU + sU[k]) * ldT + t]);
   }
 }
 
@@ -785,7 +797,7 @@ struct TileCfg {
 // DB*TB (D1) + N2 (D2) <= 512 columns.  Shared memory: SE E stages + SW W stages within the
 // 227 KB of a CTA.  Preference: at least three E stages (copies issued two tiles ahead), then
 // the double-buffered TMEM operands, then the taller tile.
-TileCfg pick_tile(int Ku, int ldW, int N2, int passes, int staticSmem) {
+TileCfg pick_tile(int Ku, int ldW, int N2, int passes, int staticSmem, bool bf = false) {
   const int fp = passes == 3 ? 2 : 1, fe = passes >= 2 ? 2 : 1;
   const int room = 227 * 1024 - staticSmem - 2048;
   TileCfg best{0, 0, 0, 0, 0};
@@ -793,7 +805,7 @@ TileCfg pick_tile(int Ku, int ldW, int N2, int passes, int staticSmem) {
   for (int TB : {64, 48, 32}) {
     const int wStage = 2 * (ldW / 32) * TB * 128;
     const int SW = 2;
-    const int SE = std::min(kMaxRing, (room - SW * wStage) / e_stage_bytes(TB));
+    const int SE = std::min(kMaxRing, (room - SW * wStage) / e_stage_bytes(TB, bf));
     if (SE < 2) continue;
     for (int bufs = 3; bufs >= 0; --bufs) {  // (EB,DB) = (2,2), (2,1), (1,2), (1,1)
       const int EB = 1 + (bufs >> 1), DB = 1 + (bufs & 1);
@@ -809,9 +821,9 @@ TileCfg pick_tile(int Ku, int ldW, int N2, int passes, int staticSmem) {
   return best;
 }
 
-template <int TB, bool ESPLIT, bool PSPLIT>
+template <int TB, bool ESPLIT, bool PSPLIT, bool BF = false>
 void launch_variant(const GradMaps& tm, GradParams p, TileCfg cfg, Dims d, cudaStream_t stream) {
-  const int eStage = e_stage_bytes(TB);
+  const int eStage = e_stage_bytes(TB, BF);
   const int wStage = 2 * (p.ldW / 32) * TB * 128;
   p.stagesE = cfg.SE;
   p.stagesW = cfg.SW;
@@ -821,11 +833,11 @@ void launch_variant(const GradMaps& tm, GradParams p, TileCfg cfg, Dims d, cudaS
   p.tmemCols = pow2_cols(cols);
   size_t smem = (size_t)cfg.SE * eStage + (size_t)cfg.SW * wStage + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it may hold all 512 TMEM columns
-  TB200_CUDA_CHECK(cudaFuncSetAttribute(grads_umma_kernel<TB, ESPLIT, PSPLIT>,
+  TB200_CUDA_CHECK(cudaFuncSetAttribute(grads_umma_kernel<TB, ESPLIT, PSPLIT, BF>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(div_up(d.V, kVBlock), d.B);
   ScopedKernel sk("grads_umma", stream);
-  grads_umma_kernel<TB, ESPLIT, PSPLIT><<<grid, kGradThreads, smem, stream>>>(tm, p);
+  grads_umma_kernel<TB, ESPLIT, PSPLIT, BF><<<grid, kGradThreads, smem, stream>>>(tm, p);
 }
 
 constexpr int kStaticSmemBound = 3 * 1024;  // barriers + per-position tables of the kernel
@@ -835,16 +847,18 @@ constexpr int kStaticSmemBound = 3 * 1024;  // barriers + per-position tables of
 int grads_umma_ld_w(Dims d) { return (int)round_up64(d.maxU > 0 ? d.maxU : 1, 32); }
 int grads_umma_ld_t(Dims d) { return (int)round_up64(d.maxT > 0 ? d.maxT : 1, 4); }
 
-bool grads_umma_supported(const float* E, const float* P, const float* egrads,
-                          const float* pgrads, Dims d, int passes) {
-  if (d.V % 4 != 0 || d.V < 32 || d.maxU < 1 || d.maxU > 128 || d.B > 65535) return false;
+bool grads_umma_supported(const void* E, const void* P, const void* egrads,
+                          const void* pgrads, Dims d, int passes) {
+  const bool bf = d.dtype == kDtypeBf16;
+  if (d.V % (bf ? 8 : 4) != 0 || d.V < 32 || d.maxU < 1 || d.maxU > 128 || d.B > 65535) return false;
+  if (bf && passes != 2) return false;   // one operand precision is built for bf16 storage
   // E and egrads are TMA operands (16-byte base); the column owners read P and write pgrads
   // with plain 4-byte accesses, but a caller whose P / pgrads are offset by a few bytes gets
   // the same routing as for E: the SIMT kernels
-  for (const float* ptr : {E, P, egrads, pgrads})
+  for (const void* ptr : {E, P, egrads, pgrads})
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return false;
   const int Ku = (int)round_up64(d.maxU, 8);
-  return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound).TB > 0;
+  return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound, bf).TB > 0;
 }
 
 void launch_unskew_round(const float* stayS, const float* stepS, const float* LNs,
@@ -872,10 +886,10 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
   TB200_CHECK_LAUNCH();
 }
 
-void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
+void launch_grads_umma(const void* E, const void* P, const float* maxP, const float* W,
                        const float* emT, const float* nref, const float* ebl, const float* pBlank,
-                       const float* pLabel, const int* labels, const float* deltas, float* egrads,
-                       float* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
+                       const float* pLabel, const int* labels, const float* deltas, void* egrads,
+                       void* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
                        int* status, cudaStream_t stream) {
   if (d.B <= 0 || d.V <= 0) return;
   GradParams p;
@@ -888,13 +902,19 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
   p.Ku = (int)round_up64(d.maxU, 8);
   p.N2 = (int)round_up64(d.maxU, 16);
   p.stagesE = p.stagesW = p.eBufs = p.dBufs = p.tmemCols = 0;
-  const TileCfg cfg = pick_tile(p.Ku, p.ldW, p.N2, passes, kStaticSmemBound);
+  const bool bf = d.dtype == kDtypeBf16;
+  const TileCfg cfg = pick_tile(p.Ku, p.ldW, p.N2, passes, kStaticSmemBound, bf);
   if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
   const int TB = cfg.TB;
   const uint64_t V = d.V, T = d.maxT, B = d.B, ldW = p.ldW, ldT = p.ldT, U = d.maxU;
   GradMaps tm;
-  tm.E = make_tmap_f32_3d(E, V, T, B, V * 4, T * V * 4, TB);
-  tm.G = make_tmap_f32_3d(egrads, V, T, B, V * 4, T * V * 4, TB);
+  if (bf) {
+    tm.E = make_tmap_bf16_3d(E, V, T, B, V * 2, T * V * 2, 64, TB);
+    tm.G = make_tmap_bf16_3d(egrads, V, T, B, V * 2, T * V * 2, 64, TB);
+  } else {
+    tm.E = make_tmap_f32_3d(E, V, T, B, V * 4, T * V * 4, TB);
+    tm.G = make_tmap_f32_3d(egrads, V, T, B, V * 4, T * V * 4, TB);
+  }
   tm.Wk = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB);
   tm.Wmn = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB, /*atom32=*/true);
   tm.nref = make_tmap_f32_rows(nref, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
@@ -903,7 +923,12 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
 #define GO(TBV, EV, PV) launch_variant<TBV, EV, PV>(tm, p, cfg, d, stream)
 #define GO_TB(EV, PV) \
   do { if (TB == 64) GO(64, EV, PV); else if (TB == 48) GO(48, EV, PV); else GO(32, EV, PV); } while (0)
-  if (passes == 3) GO_TB(true, true);
+  if (bf) {
+    if (passes != 2) throw std::invalid_argument("bf16 gradients are built for grad_passes = 2 only");
+    if (TB == 64) launch_variant<64, true, false, true>(tm, p, cfg, d, stream);
+    else if (TB == 48) launch_variant<48, true, false, true>(tm, p, cfg, d, stream);
+    else launch_variant<32, true, false, true>(tm, p, cfg, d, stream);
+  } else if (passes == 3) GO_TB(true, true);
   else if (passes == 2) GO_TB(true, false);
   else GO_TB(false, false);
 #undef GO_TB
@@ -912,8 +937,13 @@ void launch_grads_umma(const float* E, const float* P, const float* maxP, const 
   // only a vocabulary block that can hold more labels than are staged needs the second kernel
   if (d.maxU - 1 > kMaxStagedLabels) {
     ScopedKernel sk("label_overflow", stream);
-    label_overflow_kernel<<<dim3(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024)), 256, 0, stream>>>(
-        labels, emT, egrads, inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
+    const dim3 grid(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024));
+    if (bf)
+      label_overflow_kernel<bf16><<<grid, 256, 0, stream>>>(
+          labels, emT, static_cast<bf16*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
+    else
+      label_overflow_kernel<float><<<grid, 256, 0, stream>>>(
+          labels, emT, static_cast<float*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
     TB200_CHECK_LAUNCH();
   }
 }

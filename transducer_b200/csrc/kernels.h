@@ -13,8 +13,11 @@ namespace tb200 {
 // Problem geometry shared by all launchers (names follow transducer/transducer.h):
 // emissions [B,maxT,V], predictions [B,maxU,V] (maxU = longest label + 1),
 // lattices [B,maxT,maxU], labels [B,maxU-1].
+// dtype: storage type of emissions, predictions and their gradients (kDtypeF32 / kDtypeBf16);
+// launchers that take them as `const void*` read it, all others are fp32 only.
 struct Dims {
   int B, maxT, maxU, V, blank;
+  int dtype = kDtypeF32;
 };
 
 constexpr int kMaxLatticeU = 8192;  // widest label axis the wavefront kernels take
@@ -55,7 +58,8 @@ constexpr int kNoArcByte = 0xF0;
 // the blank arc and the label arc leaving node (t,u), kNoArcBits where there is none.
 // If ELrow is not null it holds E[t,label_u] as [B,maxU,maxT] (frames contiguous) and ebl is an
 // INPUT (both written by launch_lognorm_umma): nothing is gathered from E here.
-void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
+// E and P are of d.dtype.
+void launch_lattice_prep(const void* E, const void* P, const float* LN, float* LNs,
                          float* ELs, float* ebl, float2* arcs, const int* labels,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream, const float* ELrow = nullptr);
@@ -106,10 +110,11 @@ void launch_exp_rows(const float* P, float* expP, float* maxP, const int* labLen
                      int B, int maxU, int V, cudaStream_t stream);
 
 // ---- lognorm_umma.cu ----------------------------------------------------------
-// Tensor-core log-normalisers (one pass over E).  Usable when lognorm_umma_supported();
+// Tensor-core log-normalisers (one pass over E; E and P of d.dtype, bf16 only for label axes of
+// at most 128 positions).  Usable when lognorm_umma_supported();
 // splitWs holds lognorm_umma_workspace_floats(d) floats; status is the device status word
 // (api_internal.h): [0] first device-side error code (0 = none), [1] nodes recomputed exactly.
-bool lognorm_umma_supported(const float* E, const float* P, Dims d);
+bool lognorm_umma_supported(const void* E, const void* P, Dims d);
 size_t lognorm_umma_workspace_floats(Dims d);
 // Nodes whose factored sum left the fp32 range come out of the kernel as NaN; with `fixup` a
 // second kernel recomputes them exactly, without it the caller must (lattice_prep does).
@@ -117,7 +122,7 @@ size_t lognorm_umma_workspace_floats(Dims d);
 // lognorm_umma_gathers(d), the kernel also writes EL[b,u,t] = E[b,t,labels[b,u]] (u < U_b - 1)
 // and ebl[b,t] = E[b,t,blank] for the valid frames, from the chunks it streams anyway.
 bool lognorm_umma_gathers(Dims d);
-void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+void launch_lognorm_umma(const void* E, const void* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
                          int* status, bool fixup, cudaStream_t stream,
                          const int* labels = nullptr, float* EL = nullptr, float* ebl = nullptr);
@@ -127,8 +132,8 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
 // grads_umma_supported(); passes = 1..3 selects the operand precision (see grads_umma.cu).
 int grads_umma_ld_w(Dims d);  // row length of W: maxU rounded up to 32
 int grads_umma_ld_t(Dims d);  // row length of nref / ebl / emT: maxT rounded up to 4
-bool grads_umma_supported(const float* E, const float* P, const float* egrads,
-                          const float* pgrads, Dims d, int passes);
+bool grads_umma_supported(const void* E, const void* P, const void* egrads,
+                          const void* pgrads, Dims d, int passes);
 // After the reverse sweep of lattice_warp.cu: stayS/stepS/LNs (skewed) ->
 //   tensorCore: W [B,maxT,ldW] rounded to TF32, emT [B,maxU,ldT], ebl [B,ldT] (row sums of
 //               stay); rowRef -> nref = -rowRef*log2(e) [B,ldT].  W, emT and ebl are scaled by
@@ -141,10 +146,11 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
                          float* emT, float* nref, float* ebl, const int* inLens,
                          const int* labLens, SkewGeom g, Dims d, bool tensorCore,
                          cudaStream_t stream);
-void launch_grads_umma(const float* E, const float* P, const float* maxP, const float* W,
+// E, P, egrads and pgrads are of d.dtype (bf16: passes = 2 only).
+void launch_grads_umma(const void* E, const void* P, const float* maxP, const float* W,
                        const float* emT, const float* nref, const float* ebl, const float* pBlank,
-                       const float* pLabel, const int* labels, const float* deltas, float* egrads,
-                       float* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
+                       const float* pLabel, const int* labels, const float* deltas, void* egrads,
+                       void* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
                        int* status, cudaStream_t stream);
 
 // ---- lattice_warp.cu -------------------------------------------------------------

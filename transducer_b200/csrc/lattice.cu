@@ -608,8 +608,9 @@ namespace {
 // With ELrow ([B,maxU,maxT], frames contiguous, written by the tensor-core log-normaliser
 // together with ebl) the label and blank emissions are read from there, coalesced, instead of
 // being gathered from E one DRAM sector per node.
+template <typename TIn>
 __global__ void __launch_bounds__(256) lattice_prep_kernel(
-    const float* __restrict__ E, const float* __restrict__ P, const float* __restrict__ LN,
+    const TIn* __restrict__ E, const TIn* __restrict__ P, const float* __restrict__ LN,
     float* __restrict__ LNs, float* __restrict__ ELs, float* __restrict__ ebl,
     float2* __restrict__ arcs, const float* __restrict__ ELrow, const int* __restrict__ labels,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
@@ -619,7 +620,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
   if (t0 >= T || u0 >= U) return;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const float* e = E + (i64)b * maxT * V;
+  const TIn* e = E + (i64)b * maxT * V;
   const float* ln = LN + (i64)b * maxT * maxU;
   const float* elr = ELrow ? ELrow + (i64)b * maxU * maxT : nullptr;
   const int* lab = labels + (i64)b * (maxU - 1);
@@ -627,9 +628,9 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   const int myLab = (u < U - 1) ? lab[u] : blank;
   float pbl = 0.0f, plab = 0.0f;
   if (arcs != nullptr && u < U) {
-    const float* p = P + (i64)b * maxU * V;
-    pbl = p[(i64)u * V + blank];
-    plab = p[(i64)u * V + myLab];
+    const TIn* p = P + (i64)b * maxU * V;
+    pbl = to_f32(p[(i64)u * V + blank]);
+    plab = to_f32(p[(i64)u * V + myLab]);
   }
   // all loads first (unconditional, clamped into the lattice): the gathers of the four rows
   // are in flight together
@@ -641,7 +642,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     for (int k = 0; k < 4; ++k) {
       const int tc = min(t0 + w * 4 + k, T - 1);
       va[k] = ln[(i64)tc * maxU + uc];
-      vc[k] = elr ? 0.0f : e[(i64)tc * V + labc];
+      vc[k] = elr ? 0.0f : to_f32(e[(i64)tc * V + labc]);
     }
   }
 #pragma unroll
@@ -658,14 +659,14 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
     while (todo) {
       const int src = __ffs(todo) - 1;
       todo &= todo - 1;
-      const float* er = e + (i64)t * V;
-      const float* pr = P + ((i64)b * maxU + u0 + src) * V;
+      const TIn* er = e + (i64)t * V;
+      const TIn* pr = P + ((i64)b * maxU + u0 + src) * V;
       float m = neg_inf();
-      for (int v = lane; v < V; v += 32) m = fmaxf(m, er[v] + pr[v]);
+      for (int v = lane; v < V; v += 32) m = fmaxf(m, to_f32(er[v]) + to_f32(pr[v]));
       m = warp_max(m);
       float s = 0.0f;
       if (m != neg_inf() && m != pos_inf())
-        for (int v = lane; v < V; v += 32) s += expf((er[v] + pr[v]) - m);
+        for (int v = lane; v < V; v += 32) s += expf((to_f32(er[v]) + to_f32(pr[v])) - m);
       s = warp_sum(s);
       if (lane == src) a = logf(s) + m;
     }
@@ -682,7 +683,7 @@ __global__ void __launch_bounds__(256) lattice_prep_kernel(
   }
   if (threadIdx.x < 32) {
     float v = 0.0f;
-    if (t0 + lane < T) v = elr ? ebl[(i64)b * maxT + t0 + lane] : e[(i64)(t0 + lane) * V + blank];
+    if (t0 + lane < T) v = elr ? ebl[(i64)b * maxT + t0 + lane] : to_f32(e[(i64)(t0 + lane) * V + blank]);
     tEb[lane] = v;
     if (!elr && u0 == 0 && t0 + lane < T) ebl[(i64)b * maxT + t0 + lane] = v;
   }
@@ -745,7 +746,7 @@ __global__ void __launch_bounds__(256) lattice_unskew_kernel(
 
 }  // namespace
 
-void launch_lattice_prep(const float* E, const float* P, const float* LN, float* LNs,
+void launch_lattice_prep(const void* E, const void* P, const float* LN, float* LNs,
                          float* ELs, float* ebl, float2* arcs, const int* labels,
                          const int* inLens, const int* labLens, SkewGeom g, Dims d,
                          cudaStream_t stream, const float* ELrow) {
@@ -754,9 +755,14 @@ void launch_lattice_prep(const float* E, const float* P, const float* LN, float*
     TB200_CUDA_CHECK(cudaMemsetAsync(arcs, kNoArcByte, sizeof(float2) * (size_t)d.B * g.stride, stream));
   dim3 grid(div_up(d.maxU, 32), div_up(d.maxT, 32), d.B);
   ScopedKernel sk("lattice_prep", stream);
-  lattice_prep_kernel<<<grid, 256, 0, stream>>>(E, P, LN, LNs, ELs, ebl, arcs, ELrow, labels,
-                                                inLens, labLens, d.maxT, d.maxU, d.V, d.blank,
-                                                g.ld, g.stride);
+  if (d.dtype == kDtypeBf16)
+    lattice_prep_kernel<bf16><<<grid, 256, 0, stream>>>(
+        static_cast<const bf16*>(E), static_cast<const bf16*>(P), LN, LNs, ELs, ebl, arcs, ELrow,
+        labels, inLens, labLens, d.maxT, d.maxU, d.V, d.blank, g.ld, g.stride);
+  else
+    lattice_prep_kernel<float><<<grid, 256, 0, stream>>>(
+        static_cast<const float*>(E), static_cast<const float*>(P), LN, LNs, ELs, ebl, arcs, ELrow,
+        labels, inLens, labLens, d.maxT, d.maxU, d.V, d.blank, g.ld, g.stride);
   TB200_CHECK_LAUNCH();
 }
 

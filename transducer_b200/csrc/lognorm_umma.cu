@@ -83,6 +83,26 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
   return m;
 }
 
+CUtensorMap make_tmap_bf16_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0,
+                              uint32_t box1) {
+  const EncodeFn encode = tensor_map_encoder();
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1Bytes, stride2Bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  // rows of the box are 64 or 128 bytes: the swizzle of that width
+  const CUresult rc = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             box0 * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    throw CudaError("cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string((int)rc));
+  return m;
+}
+
 CUtensorMap make_tmap_f32_rows(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0) {
   const EncodeFn encode = tensor_map_encoder();
@@ -109,15 +129,17 @@ using namespace sm100;
 constexpr int kTileM = 128;
 constexpr int kMaxSMs = 256;                      // slots for the partial sums of split tiles
 constexpr int kChunkK = 32;                       // floats per K-chunk = one 128-byte swizzle row
-constexpr int kRawBytes = kTileM * kChunkK * 4;   // 16 KB
+// raw E chunk of a stage: 128 frames x 32 words, rows of 128 bytes (fp32) or 64 bytes (bf16)
+__host__ __device__ constexpr int raw_bytes(bool bf) { return kTileM * kChunkK * (bf ? 2 : 4); }
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kSumLo = 1e-30f, kSumHi = 1e30f;
 
 // ---------------------------------------------------------------------------------
 // exp(P - maxP) split into TF32 hi/lo, zero-padded to [B][nPad][kPad]
 // ---------------------------------------------------------------------------------
+template <typename TIn>
 __global__ void __launch_bounds__(256) expp_split_kernel(
-    const float* __restrict__ P, float* __restrict__ bHi, float* __restrict__ bLo,
+    const TIn* __restrict__ P, float* __restrict__ bHi, float* __restrict__ bLo,
     float* __restrict__ maxP, const int* __restrict__ labLens, int maxU, int V, int nPad,
     int kPad) {
   __shared__ float red[8];
@@ -135,11 +157,10 @@ __global__ void __launch_bounds__(256) expp_split_kernel(
     if (u < maxU && threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = 0.0f;
     return;
   }
-  const float* p = P + ((i64)b * maxU + u) * V;
-  const float4* p4 = reinterpret_cast<const float4*>(p);
+  const TIn* p = P + ((i64)b * maxU + u) * V;
   float m = neg_inf();
   for (int v = threadIdx.x; v < V / 4; v += blockDim.x) {
-    const float4 x = p4[v];
+    const float4 x = ld4(p + 4 * v);
     m = fmaxf(fmaxf(m, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
   }
   m = warp_max(m);
@@ -151,7 +172,7 @@ __global__ void __launch_bounds__(256) expp_split_kernel(
   for (int v = threadIdx.x; v < kPad / 4; v += blockDim.x) {
     float xs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, h[4], l[4];
     if (4 * v < V) {
-      const float4 x = p4[v];
+      const float4 x = ld4(p + 4 * v);
       xs[0] = expf(x.x - m); xs[1] = expf(x.y - m); xs[2] = expf(x.z - m); xs[3] = expf(x.w - m);
     }
 #pragma unroll
@@ -210,7 +231,8 @@ constexpr int kGroup = 2;
 // schedule from them itself (B <= 1024; larger batches are not split).
 constexpr int kMaxParts = 8;
 constexpr int kMaxLabels = 256;
-template <int NTW, int NDRAIN, int DCOLS>
+// BF: the emissions are bf16 (the raw chunk of a stage then has 64-byte rows, 64-byte swizzle).
+template <int NTW, int NDRAIN, int DCOLS, bool BF = false>
 __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_umma_kernel(
     const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmHi,
     const __grid_constant__ CUtensorMap tmLo, const LnParams p) {
@@ -218,6 +240,41 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   constexpr int kProducerWarp = kDrainWarp0 + 4 * NDRAIN, kMmaWarp = kProducerWarp + 1;
   constexpr int kThreads = (kMmaWarp + 2) * 32;  // two MMA-issuing warps
   constexpr int kDrainCols = DCOLS;
+  constexpr int kRawBytes = raw_bytes(BF);
+  constexpr int kRowBytes = BF ? 64 : 128;
+  // 16 consecutive words of frame r's row of the raw chunk, starting at word 16 * half, as fp32
+  auto load16 = [](const uint8_t* row, int r, int half, float (&x)[16]) {
+    if constexpr (BF) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int jj = half * 2 + j;  // 16-byte piece (8 words) of the 64-byte row
+        const uint4 q = *reinterpret_cast<const uint4*>(row + ((jj ^ ((r >> 1) & 3)) << 4));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          x[8 * j + 2 * k] = __uint_as_float(w[k] << 16);
+          x[8 * j + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int jj = half * 4 + j;  // 16-byte piece of the 128-byte row
+        const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
+        x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
+      }
+    }
+  };
+  // word `off` (0..31) of frame r's row
+  auto load1 = [](const uint8_t* row, int r, int off) {
+    if constexpr (BF) {
+      const unsigned short h = *reinterpret_cast<const unsigned short*>(
+          row + (((off >> 3) ^ ((r >> 1) & 3)) << 4) + (off & 7) * 2);
+      return __uint_as_float((uint32_t)h << 16);
+    } else {
+      return *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
+    }
+  };
   // ---- which work item is this CTA? (warp 0 scans the lengths; before any allocation) ----
   __shared__ int sItem[6];  // b, tile, part, parts, split-tile index, valid
   if (threadIdx.x < 32) {
@@ -457,19 +514,19 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
       ok = mbar_wait(&barFull[s], ph, abortp, p.status, kStatusTimeoutTma);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the aligned TMEM ops
       if (!ok) break;
-      const uint8_t* row = smem + (size_t)s * stageBytes + r * 128;
+      const uint8_t* row = smem + (size_t)s * stageBytes + r * kRowBytes;
       const int kLeft = p.V - chunkOf(c) * kChunkK;  // valid columns in this chunk
       const bool refOnly = refFirst && c == 0;           // its terms belong to part 0
       if (c == 0) {
         // the frame's shift: maximum of the first 32 entries of the row
         float m = neg_inf();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 v4 = *reinterpret_cast<const float4*>(row + ((j ^ (r & 7)) << 4));
-          if (4 * j < kLeft) m = fmaxf(m, v4.x);
-          if (4 * j + 1 < kLeft) m = fmaxf(m, v4.y);
-          if (4 * j + 2 < kLeft) m = fmaxf(m, v4.z);
-          if (4 * j + 3 < kLeft) m = fmaxf(m, v4.w);
+        for (int half = 0; half < 2; ++half) {
+          float x[16];
+          load16(row, r, half, x);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (half * 16 + j < kLeft) m = fmaxf(m, x[j]);
         }
         // a -inf/NaN prefix would poison every term; fall back to 0 and let the
         // range check route the row to the exact path if needed
@@ -484,7 +541,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         while ((key >> 8) < col0 && ++cur < nLab) key = sKey[cur];   // the other group's chunks
         while (cur < nLab && (key >> 8) < col0 + kChunkK) {
           const int off = (key >> 8) - col0;
-          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
+          const float v = load1(row, r, off);
           // (the 128 threads of the group write 128 consecutive floats of row u)
           if (t0 + r < T) elCol[(i64)(key & 0xff) * p.maxT] = v;
           if (++cur < nLab) key = sKey[cur];
@@ -494,7 +551,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
       if (gather && !refOnly) {
         if (p.blank >= col0 && p.blank < col0 + kChunkK) {
           const int off = p.blank - col0;
-          const float v = *reinterpret_cast<const float*>(row + (((off >> 2) ^ (r & 7)) << 4) + (off & 3) * 4);
+          const float v = load1(row, r, off);
           if (t0 + r < T) p.ebl[(i64)b * p.maxT + t0 + r] = v;
         }
       }
@@ -503,12 +560,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
 #pragma unroll
       for (int half = 0; half < 2; ++half) {  // 16 columns at a time (registers)
         float x[16];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int jj = half * 4 + j;  // 16-byte piece of the 128-byte row
-          const float4 v4 = *reinterpret_cast<const float4*>(row + ((jj ^ (r & 7)) << 4));
-          x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
-        }
+        load16(row, r, half, x);
         const int kLeftMine = refOnly ? 0 : kLeft - half * 16;
         uint32_t hi[16], lo[16];
         if (kLeftMine >= 16) {
@@ -649,8 +701,9 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
 
 // Recomputes marked nodes (NaN in LN) with the exact fp32 logsumexp.  One warp per frame
 // (b, t): it scans the frame's nodes 32 at a time; marked ones are evaluated by the whole warp.
+template <typename TIn>
 __global__ void __launch_bounds__(256) lognorm_fixup_kernel(
-    const float* __restrict__ E, const float* __restrict__ P, float* __restrict__ LN,
+    const TIn* __restrict__ E, const TIn* __restrict__ P, float* __restrict__ LN,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int B, int maxT, int maxU,
     int V) {
   const int lane = threadIdx.x & 31;
@@ -659,7 +712,7 @@ __global__ void __launch_bounds__(256) lognorm_fixup_kernel(
   const int b = (int)(row / maxT), t = (int)(row % maxT);
   if (t >= min(inLens[b], maxT)) return;
   const int U = min(labLens[b] + 1, maxU);
-  const float* er = E + row * V;
+  const TIn* er = E + row * V;
   float* ln = LN + row * maxU;
   for (int u0 = 0; u0 < U; u0 += 32) {
     const int u = u0 + lane;
@@ -668,13 +721,13 @@ __global__ void __launch_bounds__(256) lognorm_fixup_kernel(
     while (todo) {
       const int src = __ffs(todo) - 1;
       todo &= todo - 1;
-      const float* pr = P + ((i64)b * maxU + u0 + src) * V;
+      const TIn* pr = P + ((i64)b * maxU + u0 + src) * V;
       float m = neg_inf();
-      for (int v = lane; v < V; v += 32) m = fmaxf(m, er[v] + pr[v]);
+      for (int v = lane; v < V; v += 32) m = fmaxf(m, to_f32(er[v]) + to_f32(pr[v]));
       m = warp_max(m);
       float s = 0.0f;
       if (m != neg_inf() && m != pos_inf())
-        for (int v = lane; v < V; v += 32) s += expf((er[v] + pr[v]) - m);
+        for (int v = lane; v < V; v += 32) s += expf((to_f32(er[v]) + to_f32(pr[v])) - m);
       s = warp_sum(s);
       if (lane == 0) ln[u0 + src] = logf(s) + m;
     }
@@ -689,8 +742,8 @@ int pow2_at_least(int x) {
 
 }  // namespace
 
-bool lognorm_umma_supported(const float* E, const float* P, Dims d) {
-  return d.V % 4 == 0 && d.V >= 32 && d.maxU >= 1 && d.maxU <= 256 &&
+bool lognorm_umma_supported(const void* E, const void* P, Dims d) {
+  return d.V % (d.dtype == kDtypeBf16 ? 8 : 4) == 0 && d.V >= 32 && d.maxU >= 1 && d.maxU <= 256 &&
          (reinterpret_cast<uintptr_t>(E) & 15) == 0 && (reinterpret_cast<uintptr_t>(P) & 15) == 0 &&
          d.B <= 65535;
 }
@@ -704,24 +757,34 @@ size_t lognorm_umma_workspace_floats(Dims d) {
 
 bool lognorm_umma_gathers(Dims d) { return d.maxU >= 1 && round_up64(d.maxU, 16) <= 128; }
 
-void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRef, float* maxP,
+void launch_lognorm_umma(const void* E, const void* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
                          int* status, bool fixup, cudaStream_t stream, const int* labels,
                          float* EL, float* ebl) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
   const int nPad = (int)round_up64(d.maxU, 16);
   const int kPad = (int)round_up64(d.V, kChunkK);
+  const bool bf = d.dtype == kDtypeBf16;
+  if (bf && nPad > 128)
+    throw std::invalid_argument("bf16 emissions: the label axis must not exceed 128 positions");
   float* bHi = splitWs;
   float* bLo = splitWs + (size_t)d.B * nPad * kPad;
   {
     ScopedKernel sk("expp_split", stream);
-    expp_split_kernel<<<dim3(nPad, d.B), 256, 0, stream>>>(P, bHi, bLo, maxP, labLens, d.maxU,
-                                                           d.V, nPad, kPad);
+    if (bf)
+      expp_split_kernel<bf16><<<dim3(nPad, d.B), 256, 0, stream>>>(
+          static_cast<const bf16*>(P), bHi, bLo, maxP, labLens, d.maxU, d.V, nPad, kPad);
+    else
+      expp_split_kernel<float><<<dim3(nPad, d.B), 256, 0, stream>>>(
+          static_cast<const float*>(P), bHi, bLo, maxP, labLens, d.maxU, d.V, nPad, kPad);
   }
   TB200_CHECK_LAUNCH();
 
-  const CUtensorMap tmE = make_tmap_f32_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B,
-                                           (uint64_t)d.V * 4, (uint64_t)d.maxT * d.V * 4, kTileM);
+  const CUtensorMap tmE =
+      bf ? make_tmap_bf16_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)d.V * 2,
+                             (uint64_t)d.maxT * d.V * 2, kChunkK, kTileM)
+         : make_tmap_f32_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)d.V * 4,
+                            (uint64_t)d.maxT * d.V * 4, kTileM);
   const CUtensorMap tmHi = make_tmap_f32_3d(bHi, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
                                             (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPad);
   const CUtensorMap tmLo = make_tmap_f32_3d(bLo, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
@@ -741,7 +804,7 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   p.partial = bLo + (size_t)d.B * nPad * kPad;
   p.tickets = reinterpret_cast<unsigned*>(p.partial + (size_t)kMaxSMs * kTileM * nPad);
   TB200_CUDA_CHECK(cudaMemsetAsync(p.tickets, 0, sizeof(unsigned) * kMaxSMs, stream));
-  const int stageBytes = kRawBytes + 2 * nPad * kChunkK * 4;
+  const int stageBytes = raw_bytes(bf) + 2 * nPad * kChunkK * 4;
   // Tensor memory (512 columns): accumulators first, then the operand stages (64 columns
   // each).  Two accumulators let the MMA run while the previous group is drained; a wide
   // label axis leaves room for only one.  One CTA per SM (the kernel asks for > 114 KB).
@@ -770,7 +833,12 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
     if (labels != nullptr && EL != nullptr && ebl != nullptr && lognorm_umma_gathers(d)) {
       p.labels = labels; p.EL = EL; p.ebl = ebl;
     }
-    if (nPad <= 128 && stages == 4 && nAcc == 2) {
+    if (bf) {
+      if (!(stages == 4 && nAcc == 2)) throw std::invalid_argument("bf16 emissions: unsupported shape");
+      auto k = lognorm_umma_kernel<2, 2, 64, true>;
+      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+    } else if (nPad <= 128 && stages == 4 && nAcc == 2) {
       auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
@@ -790,8 +858,14 @@ void launch_lognorm_umma(const float* E, const float* P, float* LN, float* rowRe
   if (fixup) {
     ScopedKernel sk("lognorm_fixup", stream);
     const unsigned rows = (unsigned)d.B * (unsigned)d.maxT;
-    lognorm_fixup_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(E, P, LN, inLens, labLens, d.B,
-                                                             d.maxT, d.maxU, d.V);
+    if (bf)
+      lognorm_fixup_kernel<bf16><<<(rows + 7) / 8, 256, 0, stream>>>(
+          static_cast<const bf16*>(E), static_cast<const bf16*>(P), LN, inLens, labLens, d.B,
+          d.maxT, d.maxU, d.V);
+    else
+      lognorm_fixup_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(
+          static_cast<const float*>(E), static_cast<const float*>(P), LN, inLens, labLens, d.B,
+          d.maxT, d.maxU, d.V);
   }
   TB200_CHECK_LAUNCH();
 }

@@ -299,6 +299,12 @@ CUtensorMap make_tmap_f32_3d(const void* base, uint64_t d0, uint64_t d1, uint64_
                              uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box1,
                              bool atom32 = false);
 
+// bf16 tensor [d2][d1][d0], box [1][box1][box0] with box0 = 32 or 64 elements (rows of 64 or
+// 128 bytes) and the swizzle of that width.
+CUtensorMap make_tmap_bf16_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0,
+                              uint32_t box1);
+
 // fp32 tensor [d2][d1][d0], box [1][1][box0] without swizzle (rows of scalars).
 CUtensorMap make_tmap_f32_rows(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1Bytes, uint64_t stride2Bytes, uint32_t box0);

@@ -51,7 +51,7 @@ class Transducer(torch.autograd.Function):
     def forward(ctx, emissions, predictions, labels, input_lengths, label_lengths, blank=0,
                 validate_lengths=True, check_status=False):
         certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
-                       validate_lengths)
+                       validate_lengths, allow_bf16=True)
         device = emissions.device
         emissions = emissions.contiguous()
         predictions = predictions.contiguous()
@@ -65,7 +65,9 @@ class Transducer(torch.autograd.Function):
             saved = _workspace(saved_bytes, device)
             nbytes = _transducer.loss_forward_workspace_bytes(B, T, U, V)
             ws = _workspace(nbytes, device)
-            _transducer.loss_forward(
+            fwd = _transducer.loss_forward_bf16 if emissions.dtype is torch.bfloat16 \
+                else _transducer.loss_forward
+            fwd(
                 emissions.data_ptr(), predictions.data_ptr(), labels.data_ptr(),
                 input_lengths.data_ptr(), label_lengths.data_ptr(), costs.data_ptr(),
                 loss_sum.data_ptr(), saved.data_ptr(), saved_bytes, B, T, U, V, blank,
@@ -89,12 +91,14 @@ class Transducer(torch.autograd.Function):
         B, T, V = emissions.shape
         U = predictions.shape[1]
         deltas = deltas.to(torch.float32).contiguous()
-        egrads = torch.empty((B, T, V), device=device, dtype=torch.float32)
-        pgrads = torch.empty((B, U, V), device=device, dtype=torch.float32)
+        egrads = torch.empty((B, T, V), device=device, dtype=emissions.dtype)
+        pgrads = torch.empty((B, U, V), device=device, dtype=emissions.dtype)
         with DeviceManager(device):
             nbytes = _transducer.loss_backward_workspace_bytes(B, T, U, V)
             ws = _workspace(nbytes, device)
-            _transducer.loss_backward(
+            bwd = _transducer.loss_backward_bf16 if emissions.dtype is torch.bfloat16 \
+                else _transducer.loss_backward
+            bwd(
                 emissions.data_ptr(), predictions.data_ptr(), labels.data_ptr(),
                 input_lengths.data_ptr(), label_lengths.data_ptr(), saved.data_ptr(),
                 saved.numel(), deltas.data_ptr(), egrads.data_ptr(), pgrads.data_ptr(),
@@ -146,6 +150,9 @@ class TransducerLoss(torch.nn.Module):
         """
         emissions    float32 [B, T, V]    unnormalised scores per frame
         predictions  float32 [B, U+1, V]  unnormalised scores per label position
+                     (both may be bfloat16 instead: the loss is then computed in fp32 on the
+                     exactly up-converted values and the gradients come back in bfloat16;
+                     needs V % 8 == 0 and U + 1 <= 128)
         labels       int32   [B, U]       padded to the longest label sequence
         input_lengths, label_lengths  int32 [B]
         Returns costs float32 [B] (no reduction), differentiable w.r.t. emissions and
@@ -203,17 +210,21 @@ def check_dim(var, dim, name):
 
 
 def certify_inputs(emissions, predictions, labels, input_lengths, label_lengths,
-                   validate_lengths=True):
+                   validate_lengths=True, allow_bf16=False):
     """Argument checks with the reference's exception types and messages
     (transducer/torch_binding.py:195-229).  Dimensionality is checked first here so a
-    wrong rank reports itself rather than an index error."""
+    wrong rank reports itself rather than an index error.  allow_bf16: emissions and
+    predictions may both be bfloat16 instead of float32 (the loss; not in the reference)."""
     check_dim(emissions, 3, "emissions")
     check_dim(predictions, 3, "predictions")
     check_dim(labels, 2, "labels")
     check_dim(input_lengths, 1, "input_lengths")
     check_dim(label_lengths, 1, "label_lengths")
-    check_type(emissions, torch.float32, "emissions")
-    check_type(predictions, torch.float32, "predictions")
+    if allow_bf16 and emissions.dtype is torch.bfloat16:
+        check_type(predictions, torch.bfloat16, "predictions")
+    else:
+        check_type(emissions, torch.float32, "emissions")
+        check_type(predictions, torch.float32, "predictions")
     check_type(labels, torch.int32, "labels")
     check_type(input_lengths, torch.int32, "input_lengths")
     check_type(label_lengths, torch.int32, "label_lengths")
