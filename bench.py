@@ -161,7 +161,8 @@ def time_cpu_path(w, budget_s, steps, warmup, keep_outputs=False, source=None):
         pass
     def take(count):
         if source is not None:
-            return [t[:count].detach().cpu().numpy() for t in source]
+            return [(t[:count].detach().float() if t.is_floating_point() else t[:count].detach())
+                    .cpu().numpy() for t in source]
         return [t.numpy() for t in workloads.generate(w, "cpu", first=0, count=count)]
 
     probe = take(1)
@@ -313,6 +314,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-cuda"])
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"],
+                    help="storage type of emissions, predictions and gradients (loss tasks; "
+                         "the arithmetic is fp32 either way)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true",
@@ -356,6 +360,12 @@ def main():
         first = rank * B
     global_B = w.B if (scaling_of(w) == "strong" and args.batch <= 0) else world * B
     E, P, labels, il, ll = workloads.generate(w, dev, first=first, count=B)
+    bf16 = args.dtype == "bf16"
+    if bf16:
+        if w.task == "viterbi":
+            raise SystemExit("bench.py: --dtype bf16 applies to the loss tasks")
+        E, P = E.to(torch.bfloat16), P.to(torch.bfloat16)
+    elem_bytes = 2 if bf16 else 4
     deltas = torch.ones(B, device=dev)
     # lengths come from the workload generator and fit the padded shapes: skip the wrapper's
     # per-call read-back of their maxima (a host synchronisation; it also forbids graph capture)
@@ -509,14 +519,14 @@ def main():
     # ---- roofline of the dominant kernel -------------------------------------------
     peaks = load_peaks()
     il_c, ll_c = il.cpu(), ll.cpu()
-    alg = workloads.algorithmic_bytes(w, il_c, ll_c)
+    alg = workloads.algorithmic_bytes(w, il_c, ll_c, elem_bytes)
     alg_step = {"loss": alg["total"], "loss_fwd": alg["fwd"],
                 "viterbi": viterbi_algorithmic_bytes(w, il_c, ll_c)}[w.task]
     per_kernel = {k: {"launches": n, "ms_per_launch": ms / n} for k, (n, ms) in kernels.items() if n}
     total_kernel_ms = sum(v["ms_per_launch"] * v["launches"] for v in per_kernel.values()) / args.steps
     top = max(per_kernel, key=lambda k: per_kernel[k]["ms_per_launch"] * per_kernel[k]["launches"]) \
         if per_kernel else None
-    kernel_bytes = kernel_algorithmic_bytes(w, il_c, ll_c)
+    kernel_bytes = kernel_algorithmic_bytes(w, il_c, ll_c, elem_bytes)
     roofline = None
     clk = clocks.summary()
     if top is not None:
@@ -525,7 +535,7 @@ def main():
         achieved = (ab / (ms * 1e-3) / 1e9) if ab else None
         roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
-                    "traffic": NCU_TRAFFIC_BYTES.get((w.name, top)) if B == w.B else None,
+                    "traffic": NCU_TRAFFIC_BYTES.get((w.name, top)) if B == w.B and not bf16 else None,
                     "peak_source": peaks["source"], "ms_per_launch": ms,
                     "algorithmic_bytes_per_launch": ab}
         if top.startswith("maxplus"):
@@ -590,8 +600,9 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": scaling_of(w),
             "vs_baseline": (B / (ms_step * 1e-3)) / (32 / (A100_README_MS * 1e-3))
-            if w.name == "c3" and B == w.B else None,
-            "dtype": "f32", "data": "synthetic", "config": workload_config(w, world, B),
+            if w.name == "c3" and B == w.B and not bf16 else None,
+            "dtype": "f32 arithmetic on bf16 storage (emissions, predictions, gradients)" if bf16 else "f32",
+            "data": "synthetic", "config": workload_config(w, world, B),
             "clocks": clk, "e2e": e2e, "gpu_launches": int(launches),
             "cuda_graph": graphed, "eager_ms_per_step": eager_ms, "roofline": roofline,
             "whole_step": whole, "cpu_baseline": cpu, "parity": parity, "incumbent": incumbent,
@@ -634,6 +645,11 @@ def parity_block(w, r, device_case, state):
         out["egrad_rel_to_max"] = rel(E.grad, want["egrads"])
         out["pgrad_rel_to_max"] = rel(P.grad, want["pgrads"])
         out["bar"] = 1e-3
+        if E.dtype is torch.bfloat16:
+            out["bar"] = 2.0 ** -8 + 1e-3
+            out["note"] = ("reference run on the up-converted inputs; a bf16 gradient carries 8 "
+                           "significant bits: the bar is the fp32 bar plus one rounding (2^-8) of "
+                           "the maximum")
         # the oracle's own distance to a float64 evaluation, one utterance: its fp32 noise floor
         c = [a[:1] for a in r["case"]]
         truth = O.truth64(c[0], c[1], c[2], c[3], c[4], blank=w.blank)
@@ -666,9 +682,10 @@ def viterbi_algorithmic_bytes(w, il, ll):
     return 4.0 * w.V * (sum_t + sum_u) + 6 * 4.0 * sum_tu
 
 
-def kernel_algorithmic_bytes(w, il, ll):
-    """Bytes each kernel of the path must move per launch (fp32): E/P rows it reads,
-    gradient rows it writes, lattice cells it touches."""
+def kernel_algorithmic_bytes(w, il, ll, elem_bytes=4):
+    """Bytes each kernel of the path must move per launch: E/P rows it reads and gradient rows
+    it writes (elem_bytes per element), lattice cells it touches (fp32)."""
+    eb = float(elem_bytes)
     sum_t = float(il.sum())
     sum_u = float((ll + 1).sum())
     sum_tu = float((il.double() * (ll.double() + 1)).sum())
@@ -676,7 +693,7 @@ def kernel_algorithmic_bytes(w, il, ll):
     V = w.V
     return {
         "lognorm_exact": 4.0 * V * (sum_t + sum_u) + 4.0 * sum_tu,
-        "lognorm_umma": 4.0 * V * (sum_t + sum_u) + 4.0 * sum_tu,
+        "lognorm_umma": eb * V * (sum_t + sum_u) + 4.0 * sum_tu,
         "maxplus": 4.0 * V * (sum_t + sum_u) + 4.0 * sum_tu,
         "maxplus_pruned": 4.0 * V * sum_t + 4.0 * sum_tu,    # E rows in, scores out
         "maxplus_select_e": 4.0 * V * sum_t,
@@ -687,7 +704,7 @@ def kernel_algorithmic_bytes(w, il, ll):
         "viterbi_warp": 4 * 4.0 * sum_tu,  # one float4 record per node in
         "egrad_simt": 4.0 * V * sum_t + 4.0 * V * n * w.T + 4.0 * V * sum_u,
         "pgrad_simt": 4.0 * V * sum_t + 4.0 * V * n * (w.U + 1) + 4.0 * V * sum_u,
-        "grads_umma": 4.0 * V * (sum_t + sum_u) + 4.0 * V * n * (w.T + w.U + 1) + 4.0 * sum_tu,
+        "grads_umma": eb * V * (sum_t + sum_u) + eb * V * n * (w.T + w.U + 1) + 4.0 * sum_tu,
         "row_max": 4.0 * V * sum_t,
         "exp_rows": 2 * 4.0 * V * sum_u,
     }
@@ -704,14 +721,14 @@ def run_e2e(w, crit, device_case, dev, distributed, world, global_B, steps):
     from transducer_b200 import HostLossPipeline
     E, P, labels, il, ll = device_case
     B = E.shape[0]
-    per_utt = 4.0 * (E[0].numel() + P[0].numel()) * (2 if w.task == "loss" else 1)
+    per_utt = float(E.element_size()) * (E[0].numel() + P[0].numel()) * (2 if w.task == "loss" else 1)
     n = int(max(1, min(B, 8e9 // per_utt)))
     host = [t[:n].detach().cpu().pin_memory() for t in (E, P, labels, il, ll)]
     out_costs = torch.empty(n, dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host)
     if w.task == "loss":
-        out_eg = torch.empty(host[0].shape, dtype=torch.float32).pin_memory()
-        out_pg = torch.empty(host[1].shape, dtype=torch.float32).pin_memory()
+        out_eg = torch.empty(host[0].shape, dtype=E.dtype).pin_memory()
+        out_pg = torch.empty(host[1].shape, dtype=E.dtype).pin_memory()
         d2h = sum(t.numel() * t.element_size() for t in (out_costs, out_eg, out_pg))
         pipe = HostLossPipeline(blank=crit.blank, chunk=2, slots=4, device=dev)
         api = "transducer_b200.HostLossPipeline(chunk=2, slots=4)"

@@ -7,9 +7,8 @@ fp32 path's, so
   * the costs are those of the fp32 entry points on the up-converted inputs (compared bit for
     bit, and with the CPU oracle run on the up-converted inputs at the usual 1e-4),
   * the gradients are those of the fp32 entry points rounded once to bf16: within one bf16
-    unit in the last place of them, and within 2^-8 of the gradient's maximum of the oracle's
-    (a bf16 value carries 8 significant bits; the fp32 bar of 1e-3 is finer than the storage
-    type)."""
+    unit in the last place of them, and within 1e-3 + 2^-8 of the gradient's maximum of the
+    oracle's (the fp32 bar plus one rounding: a bf16 value carries 8 significant bits)."""
 import numpy as np
 import pytest
 import torch
@@ -19,7 +18,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-BF16_GRAD_TOL = 2.0 ** -8
+BF16_GRAD_TOL = 1e-3 + 2.0 ** -8
 
 
 def make_case(B, T, U, V, blank, seed, scale=1.0):
@@ -115,6 +114,7 @@ def test_python_surface_takes_bf16_and_returns_bf16_gradients():
     assert torch.equal(costs, costs32)
     assert abi.rel_to_max(E.grad.float().cpu().numpy(), E32.grad.cpu().numpy()) <= 2.0 ** -8
     assert abi.rel_to_max(P.grad.float().cpu().numpy(), P32.grad.cpu().numpy()) <= 2.0 ** -8
+    # (against the fp32 path of this library the distance is one rounding, no more)
     # mixed storage types are refused with the reference's exception type
     with pytest.raises(TypeError):
         crit(E, P32, labels, il, ll)

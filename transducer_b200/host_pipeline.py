@@ -24,27 +24,28 @@ class _Slot(object):
         self.stream = torch.cuda.Stream(device=device)
         self.shape = None
 
-    def fit(self, n, T, U, V, device, forward_only=False):
-        if self.shape == (n, T, U, V, forward_only):
+    def fit(self, n, T, U, V, device, forward_only=False, dtype=torch.float32):
+        if self.shape == (n, T, U, V, forward_only, dtype):
             return
         f32 = dict(device=device, dtype=torch.float32)
+        io = dict(device=device, dtype=dtype)   # emissions, predictions and their gradients
         i32 = dict(device=device, dtype=torch.int32)
         u8 = dict(device=device, dtype=torch.uint8)
-        self.E = torch.empty((n, T, V), **f32)
-        self.P = torch.empty((n, U, V), **f32)
+        self.E = torch.empty((n, T, V), **io)
+        self.P = torch.empty((n, U, V), **io)
         self.labels = torch.empty((n, max(U - 1, 0)), **i32)
         self.il = torch.empty((n,), **i32)
         self.ll = torch.empty((n,), **i32)
         self.deltas = torch.empty((n,), **f32)
         self.costs = torch.empty((n,), **f32)
-        self.eg = None if forward_only else torch.empty((n, T, V), **f32)
-        self.pg = None if forward_only else torch.empty((n, U, V), **f32)
+        self.eg = None if forward_only else torch.empty((n, T, V), **io)
+        self.pg = None if forward_only else torch.empty((n, U, V), **io)
         self.saved_bytes = _transducer.loss_saved_bytes(n, T, U, V)
         self.saved = torch.empty(max(self.saved_bytes, 1), **u8)
         self.fwd_bytes = _transducer.loss_forward_workspace_bytes(n, T, U, V)
         self.bwd_bytes = 0 if forward_only else _transducer.loss_backward_workspace_bytes(n, T, U, V)
         self.ws = torch.empty(max(self.fwd_bytes, self.bwd_bytes, 1), **u8)
-        self.shape = (n, T, U, V, forward_only)
+        self.shape = (n, T, U, V, forward_only, dtype)
 
 
 class HostLossPipeline(object):
@@ -61,8 +62,10 @@ class HostLossPipeline(object):
 
     Call with host tensors (pinned memory, or the copies will not overlap):
         emissions float32 [B,T,V], predictions float32 [B,U+1,V], labels int32 [B,U],
-        input_lengths, label_lengths int32 [B]; outputs costs [B], egrads [B,T,V],
+        input_lengths, label_lengths int32 [B]; outputs costs float32 [B], egrads [B,T,V],
         pgrads [B,U+1,V]; optional deltas float32 [B] (upstream gradient, default ones).
+        emissions, predictions and both gradient buffers may all be bfloat16 instead (half the
+        bytes over the link; see TransducerLoss for the shapes that takes).
     The call is asynchronous like any CUDA work: it returns a 1-element device tensor with
     the sum of the costs; the outputs are complete once the current stream (which is made
     to wait for the pipeline) has been synchronised.
@@ -95,6 +98,16 @@ class HostLossPipeline(object):
         if not self.forward_only and (egrads.shape != emissions.shape or
                                       pgrads.shape != predictions.shape):
             raise ValueError("gradient buffers must have the shapes of their inputs")
+        dtype = emissions.dtype
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("emissions must be torch.float32 or torch.bfloat16")
+        for name, t in (("predictions", predictions),) + (() if self.forward_only else
+                                                           (("egrads", egrads), ("pgrads", pgrads))):
+            if t.dtype is not dtype:
+                raise TypeError("%s must be %s like emissions" % (name, dtype))
+        bf = dtype is torch.bfloat16
+        loss_forward = _transducer.loss_forward_bf16 if bf else _transducer.loss_forward
+        loss_backward = _transducer.loss_backward_bf16 if bf else _transducer.loss_backward
         dev = self.device
         n_chunks = (B + self.chunk - 1) // self.chunk
         if self.loss_parts is None or self.loss_parts.numel() != max(n_chunks, 1):
@@ -109,7 +122,7 @@ class HostLossPipeline(object):
                 slot = self.slots[i % len(self.slots)]
                 slot.stream.wait_event(start)
                 with torch.cuda.stream(slot.stream):
-                    slot.fit(self.chunk, T, U, V, dev, self.forward_only)  # views of n <= chunk rows below
+                    slot.fit(self.chunk, T, U, V, dev, self.forward_only, dtype)  # views of n <= chunk rows below
                     slot.E[:n].copy_(emissions[lo:hi], non_blocking=True)
                     slot.P[:n].copy_(predictions[lo:hi], non_blocking=True)
                     slot.labels[:n].copy_(labels[lo:hi], non_blocking=True)
@@ -120,14 +133,14 @@ class HostLossPipeline(object):
                     else:
                         slot.deltas[:n].copy_(deltas[lo:hi], non_blocking=True)
                     _transducer.set_stream(slot.stream.cuda_stream)
-                    _transducer.loss_forward(
+                    loss_forward(
                         slot.E.data_ptr(), slot.P.data_ptr(), slot.labels.data_ptr(),
                         slot.il.data_ptr(), slot.ll.data_ptr(), slot.costs.data_ptr(),
                         self.loss_parts[i:].data_ptr(), slot.saved.data_ptr(), slot.saved_bytes,
                         n, T, U, V, self.blank, slot.ws.data_ptr(), slot.fwd_bytes)
                     costs[lo:hi].copy_(slot.costs[:n], non_blocking=True)
                     if not self.forward_only:
-                        _transducer.loss_backward(
+                        loss_backward(
                             slot.E.data_ptr(), slot.P.data_ptr(), slot.labels.data_ptr(),
                             slot.il.data_ptr(), slot.ll.data_ptr(), slot.saved.data_ptr(),
                             slot.saved_bytes, slot.deltas.data_ptr(), slot.eg.data_ptr(),

@@ -96,16 +96,18 @@ def generate(w, device="cpu", first=0, count=None, force_full_first=True):
     return E, P, labels.to(dev), in_lens.to(dev), lab_lens.to(dev)
 
 
-def algorithmic_bytes(w, in_lens, lab_lens):
-    """HBM bytes the loss must move at minimum (4-byte floats): forward reads E and
-    P once over the valid rows and writes/reads the lattices; backward re-reads E
-    and P, writes the full padded gradients and touches four lattices."""
+def algorithmic_bytes(w, in_lens, lab_lens, elem_bytes=4):
+    """HBM bytes the loss must move at minimum (emissions, predictions and gradients of
+    elem_bytes each, fp32 lattices): forward reads E and P once over the valid rows and
+    writes/reads the lattices; backward re-reads E and P, writes the full padded gradients and
+    touches four lattices."""
+    eb = float(elem_bytes)
     sum_t = float(in_lens.sum())
     sum_u = float((lab_lens + 1).sum())
     sum_tu = float((in_lens.double() * (lab_lens.double() + 1)).sum())
     n = len(in_lens)
-    fwd = 4.0 * w.V * (sum_t + sum_u) + 3 * 4.0 * sum_tu
-    bwd = 4.0 * w.V * (sum_t + sum_u) + 4.0 * w.V * n * (w.T + w.U + 1) + 4 * 4.0 * sum_tu
+    fwd = eb * w.V * (sum_t + sum_u) + 3 * 4.0 * sum_tu
+    bwd = eb * w.V * (sum_t + sum_u) + eb * w.V * n * (w.T + w.U + 1) + 4 * 4.0 * sum_tu
     return {"fwd": fwd, "bwd": bwd, "total": fwd + bwd}
 
 
