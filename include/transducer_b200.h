@@ -186,7 +186,11 @@ int tb200_loss_forward(const float* emissions, const float* predictions,
 /* transducer/torch_binding.py:60-90 (Transducer.backward): reverse sweep + dense
  * gradient contractions + deltas scaling, from the same inputs and the `saved`
  * buffer of the forward call.  Every element of egrads [B,maxT,V] and pgrads
- * [B,maxU,V] is written (zeros in the padding). */
+ * [B,maxU,V] is written (zeros in the padding).  egrads may be the emissions buffer itself
+ * and pgrads the predictions buffer (gradients in place: every tile is read before it is
+ * written and nothing else in the call reads them) whenever the tensor-core gradient kernel
+ * runs (alphabetSize % 4 == 0, maxLabelLength <= 128, 16-byte aligned buffers); otherwise
+ * aliasing is refused with TB200_ERR_INVALID_ARGUMENT. */
 size_t tb200_loss_backward_workspace_bytes(int batchSize, int maxInputLength,
                                            int maxLabelLength, int alphabetSize);
 int tb200_loss_backward(const float* emissions, const float* predictions,

@@ -463,6 +463,10 @@ int loss_backward_any(const void* E, const void* P, const int* labels, const int
       throw std::invalid_argument(
           "bf16 gradients need the tensor-core gradient kernel: alphabetSize % 8 == 0, "
           "maxLabelLength <= 128, grad_passes = 2, 16-byte aligned buffers");
+    if ((egrads == E || pgrads == P) && !(tensorCore && lattice_warp_supported(d)))
+      throw std::invalid_argument(
+          "gradients in place (egrads == emissions / pgrads == predictions) need the "
+          "tensor-core gradient kernel: alphabetSize % 4 == 0, maxLabelLength <= 128");
     const float* Ef = static_cast<const float*>(E);   // (fp32 from here on where used as such)
     const float* Pf = static_cast<const float*>(P);
     float* egf = static_cast<float*>(egrads);
