@@ -196,7 +196,10 @@ struct LnParams {
   const int* inLens;
   const int* labLens;
   int* status;       // [0] first error code, [1] number of nodes handed to the fix-up
-  int maxT, maxU, V, nPad, stages, nAcc, tmemCols;
+  int maxT, maxU, V, stages, nAcc, tmemCols;
+  // A label axis of more than 128 positions is cut into `halves` = 2 column ranges of nPad
+  // positions; a work item is then (tile, range) and reads the tile's chunks of E again.
+  int nPad, halves;
   // last-wave splitting (see lognorm_umma_kernel)
   int B, tilesX, nSM;
   float* partial;    // [nSM][kTileM][nPad] partial sums of split tiles
@@ -279,13 +282,21 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   __shared__ int sItem[6];  // b, tile, part, parts, split-tile index, valid
   if (threadIdx.x < 32) {
     const int lane0 = threadIdx.x;
-    const int nNatural = p.tilesX * p.B;
+    const int perUtt = p.tilesX * p.halves;   // grid slots per utterance
+    const int nNatural = perUtt * p.B;
     const bool worker = (int)blockIdx.x >= nNatural;
-    const int myB = worker ? -1 : (int)blockIdx.x / p.tilesX, myX = worker ? 0 : (int)blockIdx.x % p.tilesX;
+    const int myB = worker ? -1 : (int)blockIdx.x / perUtt, myX = worker ? 0 : (int)blockIdx.x % perUtt;
+    // live work items of an utterance: tiles x column ranges that hold positions (item ix is
+    // range ix % ranges of tile ix / ranges, so the ranges of a tile run side by side and
+    // share its chunks of E in L2)
+    auto ranges = [&](int bb) {
+      const int Ub = min(p.labLens[bb] + 1, p.maxU);
+      return min(p.halves, (Ub + p.nPad - 1) / p.nPad);
+    };
     auto liveTiles = [&](int bb) {
       if (bb >= p.B) return 0;
       const int Tb = min(p.inLens[bb], p.maxT), Ub = min(p.labLens[bb] + 1, p.maxU);
-      return (Tb > 0 && Ub > 0) ? (Tb + kTileM - 1) / kTileM : 0;
+      return (Tb > 0 && Ub > 0) ? ((Tb + kTileM - 1) / kTileM) * ranges(bb) : 0;
     };
     int n = 0, before = 0;  // live tiles in all, and in the utterances before mine
     for (int b0 = 0; b0 < p.B; b0 += 32) {
@@ -341,9 +352,12 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
   }
   __syncthreads();
   if (!sItem[5]) return;
-  const int b = sItem[0], t0 = sItem[1] * kTileM;
+  const int b = sItem[0];
   const int part = sItem[2], parts = sItem[3], splitIdx = sItem[4];
   const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
+  const int nRanges = min(p.halves, (U + p.nPad - 1) / p.nPad);
+  const int t0 = (sItem[1] / nRanges) * kTileM;
+  const int uOff = (sItem[1] % nRanges) * p.nPad;   // first label position of my column range
 
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) &
@@ -388,8 +402,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     fence_mbar_init();
   }
   for (int u = threadIdx.x; u < p.nPad; u += kThreads)
-    sMaxP[u] = (u < U) ? p.maxP[(i64)b * p.maxU + u] : 0.0f;
-  const bool gather = p.EL != nullptr;
+    sMaxP[u] = (uOff + u < U) ? p.maxP[(i64)b * p.maxU + uOff + u] : 0.0f;
+  const bool gather = p.EL != nullptr && uOff == 0;   // (one range hands out the emissions)
   const int nLab = gather ? min(U - 1, kMaxLabels) : 0;
   if (gather) {  // rank sort by column (from a shared-memory copy); ties keep position order
     __shared__ int sLab[kMaxLabels];
@@ -432,8 +446,8 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         mbar_arrive_expect_tx(&barFull[s], (uint32_t)stageBytes);
         const int col = chunkOf(c) * kChunkK;
         tma_load_3d(st, &tmE, &barFull[s], col, t0, b);
-        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], col, 0, b);
-        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], col, 0, b);
+        tma_load_3d(st + kRawBytes, &tmHi, &barFull[s], col, uOff, b);
+        tma_load_3d(st + kRawBytes + bBytes, &tmLo, &barFull[s], col, uOff, b);
         issued = c + 1;
         if (++s == S) { s = 0; ph ^= 1u; }
       }
@@ -532,7 +546,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         // range check route the row to the exact path if needed
         ref = (m > -3.0e38f && m < 3.0e38f) ? m : 0.0f;
         sRef[r] = ref;
-        if (t0 + r < T && part == 0) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
+        if (t0 + r < T && part == 0 && uOff == 0) p.rowRef[(i64)b * p.maxT + t0 + r] = ref;
       }
       const int col0 = chunkOf(c) * kChunkK;
       if (gather && !refOnly && nextCol < col0 + kChunkK) {
@@ -676,10 +690,10 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
         float* out = p.LN + ((i64)b * p.maxT + t) * p.maxU;
 #pragma unroll
         for (int j = 0; j < kDrainCols; ++j) {
-          const int u = c0 + j;
-          if (u < U) {
+          const int u = uOff + c0 + j;
+          if (c0 + j < c1 && u < U) {
             const float acc = sum[j];
-            float ln = (logf(acc) + ref) + sMaxP[u];
+            float ln = (logf(acc) + ref) + sMaxP[c0 + j];
             if (!(acc >= kSumLo && acc <= kSumHi)) {
               ln = bad;  // marker: recompute exactly
               ++flagged;
@@ -748,25 +762,37 @@ bool lognorm_umma_supported(const void* E, const void* P, Dims d) {
          d.B <= 65535;
 }
 
+// Label axis as the kernel sees it: up to 128 positions in one column range, more in two equal
+// ranges (each a multiple of 16); the operand arrays hold ranges * part rows.
+struct LabelAxis {
+  int ranges, part;
+  int rows() const { return ranges * part; }
+};
+LabelAxis label_axis(int maxU) {
+  const int n = (int)round_up64(maxU > 0 ? maxU : 1, 16);
+  if (n <= 128) return LabelAxis{1, n};
+  return LabelAxis{2, (int)round_up64((n + 1) / 2, 16)};
+}
+
 size_t lognorm_umma_workspace_floats(Dims d) {
-  const size_t nPad = (size_t)round_up64(d.maxU > 0 ? d.maxU : 1, 16);
+  const size_t nPad = (size_t)label_axis(d.maxU).rows();
   const size_t kPad = (size_t)round_up64(d.V, kChunkK);
   // exp(P) hi and lo; partial sums of split tiles (one slot per SM at most); their tickets
   return 2 * (size_t)d.B * nPad * kPad + (size_t)kMaxSMs * kTileM * nPad + kMaxSMs;
 }
 
-bool lognorm_umma_gathers(Dims d) { return d.maxU >= 1 && round_up64(d.maxU, 16) <= 128; }
+bool lognorm_umma_gathers(Dims d) { return d.maxU >= 1 && d.maxU <= kMaxLabels; }
 
 void launch_lognorm_umma(const void* E, const void* P, float* LN, float* rowRef, float* maxP,
                          const int* inLens, const int* labLens, Dims d, float* splitWs,
                          int* status, bool fixup, cudaStream_t stream, const int* labels,
                          float* EL, float* ebl) {
   if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
-  const int nPad = (int)round_up64(d.maxU, 16);
+  const LabelAxis axis = label_axis(d.maxU);
+  const int nPad = axis.rows();          // rows of the exp(P) operand arrays
+  const int nPart = axis.part;           // label positions per work item
   const int kPad = (int)round_up64(d.V, kChunkK);
   const bool bf = d.dtype == kDtypeBf16;
-  if (bf && nPad > 128)
-    throw std::invalid_argument("bf16 emissions: the label axis must not exceed 128 positions");
   float* bHi = splitWs;
   float* bLo = splitWs + (size_t)d.B * nPad * kPad;
   {
@@ -786,14 +812,14 @@ void launch_lognorm_umma(const void* E, const void* P, float* LN, float* rowRef,
          : make_tmap_f32_3d(E, (uint64_t)d.V, (uint64_t)d.maxT, (uint64_t)d.B, (uint64_t)d.V * 4,
                             (uint64_t)d.maxT * d.V * 4, kTileM);
   const CUtensorMap tmHi = make_tmap_f32_3d(bHi, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
-                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPad);
+                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPart);
   const CUtensorMap tmLo = make_tmap_f32_3d(bLo, (uint64_t)kPad, (uint64_t)nPad, (uint64_t)d.B,
-                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPad);
+                                            (uint64_t)kPad * 4, (uint64_t)nPad * kPad * 4, nPart);
 
   LnParams p;
   p.LN = LN; p.rowRef = rowRef; p.maxP = maxP; p.inLens = inLens; p.labLens = labLens;
   p.status = status;
-  p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.nPad = nPad;
+  p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.nPad = nPart; p.halves = axis.ranges;
   p.labels = nullptr; p.EL = nullptr; p.ebl = nullptr; p.blank = d.blank;
   int dev = 0, nSM = 0;
   TB200_CUDA_CHECK(cudaGetDevice(&dev));
@@ -804,54 +830,36 @@ void launch_lognorm_umma(const void* E, const void* P, float* LN, float* rowRef,
   p.partial = bLo + (size_t)d.B * nPad * kPad;
   p.tickets = reinterpret_cast<unsigned*>(p.partial + (size_t)kMaxSMs * kTileM * nPad);
   TB200_CUDA_CHECK(cudaMemsetAsync(p.tickets, 0, sizeof(unsigned) * kMaxSMs, stream));
-  const int stageBytes = raw_bytes(bf) + 2 * nPad * kChunkK * 4;
-  // Tensor memory (512 columns): accumulators first, then the operand stages (64 columns
-  // each).  Two accumulators let the MMA run while the previous group is drained; a wide
-  // label axis leaves room for only one.  One CTA per SM (the kernel asks for > 114 KB).
-  const int maxStagesSmem = (int)((220 * 1024 - 2048) / stageBytes);
-  // (With two accumulators the two MMA-issuing threads take the chunks in groups of two, so a
-  // stage has a single consumer, in program order, only when there are exactly four stages;
-  // with fewer, a fast issuer could mistake an older phase of a stage's barrier for its own.)
-  int nAcc = 2;
-  int stages = std::min(4, std::min(maxStagesSmem, (512 - 2 * nPad) / 64));
-  if (stages < 4) stages = 0;  // fall through to the single-accumulator, single-issuer form
-  if (stages < 2) {
-    nAcc = 1;
-    stages = std::min(4, std::min(maxStagesSmem, (512 - nPad) / 64));
-  }
-  if (stages < 1) throw std::invalid_argument("label axis too long for the tensor-core log-normaliser");
+  const int stageBytes = raw_bytes(bf) + 2 * nPart * kChunkK * 4;
+  // Tensor memory (512 columns): two accumulators of nPart <= 128 columns (the MMA of one group
+  // of chunks runs while the previous group is drained), then four operand stages of 64 columns.
+  // Four stages exactly: the two MMA-issuing threads take the chunks in groups of two, and only
+  // then does every stage have a single consumer of each kind, in program order (with fewer, a
+  // fast issuer could mistake an older phase of a stage's barrier for its own).  One CTA per SM.
+  const int stages = 4, nAcc = 2;
+  if (stages * stageBytes + 2048 > 220 * 1024 || nAcc * nPart + stages * 64 > 512)
+    throw std::invalid_argument("label axis too long for the tensor-core log-normaliser");
   p.stages = stages;
   p.nAcc = nAcc;
-  p.tmemCols = pow2_at_least(nAcc * nPad + stages * 64);
+  p.tmemCols = pow2_at_least(nAcc * nPart + stages * 64);
   size_t smem = (size_t)stages * stageBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  dim3 grid((unsigned)(p.tilesX * d.B + p.nSM));  // one CTA per tile + workers for split tiles
+  // one CTA per (tile, column range) + workers for the split items of the last round
+  dim3 grid((unsigned)(p.tilesX * p.halves * d.B + p.nSM));
   {
     ScopedKernel sk("lognorm_umma", stream);
-    // the two-group transform and the two MMA issuers rely on exactly four stages (each stage
-    // then has one consumer of each kind, in program order)
     if (labels != nullptr && EL != nullptr && ebl != nullptr && lognorm_umma_gathers(d)) {
       p.labels = labels; p.EL = EL; p.ebl = ebl;
     }
+    // 8 transform + 8 drain (64 columns each) warps, producer, two MMA issuers
     if (bf) {
-      if (!(stages == 4 && nAcc == 2)) throw std::invalid_argument("bf16 emissions: unsupported shape");
       auto k = lognorm_umma_kernel<2, 2, 64, true>;
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
-    } else if (nPad <= 128 && stages == 4 && nAcc == 2) {
-      auto k = lognorm_umma_kernel<2, 2, 64>;   // 8 transform + 8 drain (64 columns each) warps
-      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
-    } else if (nPad <= 192) {
-      // wider label axes: one drain warpgroup per 64 accumulator columns (a thread that keeps 128
-      // running sums spills them), a single accumulator and a single MMA issuer
-      auto k = lognorm_umma_kernel<1, 3, 64>;   // 4 transform + 12 drain warps
-      TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     } else {
-      auto k = lognorm_umma_kernel<1, 4, 64>;   // 4 transform + 16 drain warps
+      auto k = lognorm_umma_kernel<2, 2, 64>;
       TB200_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      k<<<grid, 23 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
+      k<<<grid, 19 * 32, smem, stream>>>(tmE, tmHi, tmLo, p);
     }
   }
   TB200_CHECK_LAUNCH();
