@@ -287,7 +287,7 @@ def per_rank_batch(w, world, rank, override=0):
     return w.B
 
 
-def workload_config(w, n_gpus, per_rank):
+def workload_config(w, n_gpus, per_rank, reduce="nccl"):
     strong = scaling_of(w) == "strong"
     return {"workload": "%s: %s, B=%d %s, T=%d, U=%d, V=%d, N(0,%g) fp32, lengths %s/%s%s%s"
                         % (w.name, TASK_TEXT[w.task], w.B if strong else per_rank,
@@ -297,7 +297,9 @@ def workload_config(w, n_gpus, per_rank):
                            ", blank column +%g" % w.blank_bias if w.blank_bias else ""),
             "per_gpu_batch": per_rank, "global_batch": w.B if strong else per_rank * n_gpus,
             "T": w.T, "U": w.U, "V": w.V, "task": TASK_TEXT[w.task],
-            "parallelism": "batch-sharded x%d, NCCL all-reduce of the loss sum" % n_gpus
+            "parallelism": ("batch-sharded x%d, " % n_gpus +
+                            ("NCCL all-reduce of the loss sum" if reduce == "nccl" else
+                             "loss sums exchanged by peer stores (tb200_loss_sum_exchange)"))
                            if w.task != "viterbi" else "batch-sharded x%d, no exchange" % n_gpus,
             "l2_policy": "inputs (%.2f GB per rank) larger than the 126 MB L2" %
                          (4.0 * per_rank * w.T * w.V / 1e9)}
@@ -317,6 +319,9 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"],
                     help="storage type of emissions, predictions and gradients (loss tasks; "
                          "the arithmetic is fp32 either way)")
+    ap.add_argument("--reduce", default="nccl", choices=["nccl", "peer"],
+                    help="how the ranks' loss sums are added: an NCCL all-reduce, or the library's "
+                         "own exchange by peer stores (transducer_b200.distributed.PeerLossSum)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true",
@@ -397,6 +402,7 @@ def main():
     # sum into a slot of its own and goes on with the next step, the side stream reduces the slot.
     side = torch.cuda.Stream(device=dev) if distributed and has_loss else None
     reduced = torch.zeros(1, device=dev)
+    peer_sum = D.PeerLossSum(device=dev) if side is not None and args.reduce == "peer" else None
 
     def reduce_async(loss_sum):
         if side is None:
@@ -406,6 +412,8 @@ def main():
         reduced.copy_(loss_sum)
         side.wait_stream(main)
         with torch.cuda.stream(side):
+            if peer_sum is not None:
+                return peer_sum(reduced)
             dist.all_reduce(reduced)
         return reduced
 
@@ -602,7 +610,7 @@ def main():
             "vs_baseline": (B / (ms_step * 1e-3)) / (32 / (A100_README_MS * 1e-3))
             if w.name == "c3" and B == w.B and not bf16 else None,
             "dtype": "f32 arithmetic on bf16 storage (emissions, predictions, gradients)" if bf16 else "f32",
-            "data": "synthetic", "config": workload_config(w, world, B),
+            "data": "synthetic", "config": workload_config(w, world, B, args.reduce),
             "clocks": clk, "e2e": e2e, "gpu_launches": int(launches),
             "cuda_graph": graphed, "eager_ms_per_step": eager_ms, "roofline": roofline,
             "whole_step": whole, "cpu_baseline": cpu, "parity": parity, "incumbent": incumbent,
@@ -612,6 +620,8 @@ def main():
             line["fwd_bwd_ms"] = ms_step
         print(json.dumps(line), flush=True)
     if distributed:
+        if peer_sum is not None:
+            peer_sum.close()
         dist.destroy_process_group()
 
 

@@ -250,6 +250,31 @@ int tb200_viterbi_decode(const float* emissions, const float* predictions,
                          int alphabetSize, int blank, void* workspace,
                          size_t workspaceBytes);
 
+/* The path's one collective without a collective library: the per-rank loss sums (4 bytes
+ * each) exchanged by plain peer stores over NVLink, one launch of one warp per rank and step.
+ * The reference is single-GPU (nothing to cite); the usual route is an all-reduce of the
+ * lossSum that tb200_loss_forward wrote (NCCL), which this replaces.
+ *
+ * Every rank (one process per GPU) owns a slot buffer: tb200_peer_alloc (cudaMalloc'ed, zeroed,
+ * tb200_peer_slots_bytes() bytes); tb200_peer_export writes its 64-byte CUDA IPC handle, which
+ * the caller sends to the other ranks by any means; tb200_peer_import opens a peer's handle
+ * (peer access is enabled on demand) and tb200_peer_close / tb200_peer_free undo the two.
+ * tb200_loss_sum_exchange, called by every rank with the same seq = 1, 2, 3, ... (one per
+ * step) and peerSlots[r] = rank r's buffer as seen from this process (its own for r == rank):
+ * stores (seq, *lossSum) into every rank's buffer, waits until its own buffer holds all ranks'
+ * values of this seq, and writes their sum, added in rank order (identical bits on every
+ * rank), to *total.  Asynchronous on the current stream like every other call.  A peer whose
+ * value does not arrive within timeoutUs microseconds (0: the library's 2 s limit) makes
+ * *total NaN and is reported by tb200_check_status; the context stays usable.  world <= 32. */
+size_t tb200_peer_slots_bytes(void);
+int tb200_peer_alloc(void** slots);
+int tb200_peer_free(void* slots);
+int tb200_peer_export(const void* slots, void* handle64);
+int tb200_peer_import(const void* handle64, void** slots);
+int tb200_peer_close(void* slots);
+int tb200_loss_sum_exchange(const float* lossSum, void* const* peerSlots, int rank, int world,
+                            unsigned seq, float* total, unsigned timeoutUs);
+
 #ifdef __cplusplus
 }
 #endif

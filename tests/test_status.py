@@ -27,9 +27,10 @@ def test_return_codes_map_to_exceptions():
 
 def test_status_names_without_a_gpu():
     from transducer_b200 import _lib
-    names = [_lib.lib.tb200_status_name(c).decode() for c in range(0, 7)]
-    assert names[0] == "ok" and "copy never landed" in names[1] and "unknown" in names[6]
-    assert len(set(names[:6])) == 6
+    names = [_lib.lib.tb200_status_name(c).decode() for c in range(0, 8)]
+    assert names[0] == "ok" and "copy never landed" in names[1] and "peer" in names[6]
+    assert "unknown" in names[7]
+    assert len(set(names[:7])) == 7
 
 
 @pytest.mark.gpu

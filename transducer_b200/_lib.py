@@ -54,6 +54,13 @@ SIGNATURES = {
     "tb200_label_arc_scores": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
     "tb200_viterbi_decode_workspace_bytes": (_z, [_i] * 4),
     "tb200_viterbi_decode": (_i, [_p] * 5 + [_i] * 5 + [_p, _z]),
+    "tb200_peer_slots_bytes": (_z, []),
+    "tb200_peer_alloc": (_i, [ctypes.POINTER(_p)]),
+    "tb200_peer_free": (_i, [_p]),
+    "tb200_peer_export": (_i, [_p, _p]),
+    "tb200_peer_import": (_i, [_p, ctypes.POINTER(_p)]),
+    "tb200_peer_close": (_i, [_p]),
+    "tb200_loss_sum_exchange": (_i, [_p, _p, _i, _i, ctypes.c_uint, _p, ctypes.c_uint]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -23,7 +23,8 @@ enum : int {
   kStatusTimeoutOperand = 2,   // operand stage never produced
   kStatusTimeoutMma = 3,       // MMA completion never signalled
   kStatusTimeoutStageFree = 4, // stage never released
-  kStatusTimeoutSelfTest = 5   // the wait of tb200_selftest_wait_timeout (never satisfied)
+  kStatusTimeoutSelfTest = 5,  // the wait of tb200_selftest_wait_timeout (never satisfied)
+  kStatusTimeoutPeer = 6       // a peer's loss sum never arrived (tb200_loss_sum_exchange)
 };
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s

@@ -58,6 +58,7 @@ const char* status_name(int code) {
     case sm100::kStatusTimeoutOperand: return "an operand stage was never produced";
     case sm100::kStatusTimeoutMma: return "an MMA completion was never signalled";
     case sm100::kStatusTimeoutStageFree: return "a pipeline stage was never released";
+    case sm100::kStatusTimeoutPeer: return "a peer's loss sum never arrived";
     case sm100::kStatusTimeoutSelfTest: return "self-test wait (nothing arrives on its barrier)";
     default: return "unknown device status code";
   }
