@@ -485,27 +485,35 @@ __global__ void __launch_bounds__(256) viterbi_prep_kernel(
 // from (t,u-1).  All positions then flush their words at the same steps.
 __host__ __device__ inline int viterbi_words_d(int maxT, int maxU) { return (maxT + maxU + 31) / 32; }
 
-// NPL label positions per lane: u = NPL*lane + r.  256 threads: warp 0 sweeps, then thread 0
-// backtracks and all warps resolve the labels on the path.
+// NPL label positions per lane: u = NPL*lane + r.  One warp per utterance sweeps, then its
+// first thread backtracks and writes, for every label position, the frame at which the label was
+// emitted (frames [B,maxU], -1 where there is none); viterbi_labels_kernel resolves the labels.
+// The decision bits live in shared memory behind the ring where they fit (decInSmem), in the
+// decBits scratch otherwise: the backtrack is a chain of dependent reads of them.
 template <int NPL>
-__global__ void __launch_bounds__(256) viterbi_warp_kernel(
-    const float* __restrict__ E, const float* __restrict__ P, const float4* __restrict__ nodes,
-    int ld, i64 latStride, int nDiag, int ringDepth, uint32_t* __restrict__ decBits,
-    int* __restrict__ labelsOut, const int* __restrict__ inLens, const int* __restrict__ labLens,
-    int maxT, int maxU, int V, int blank, int* status) {
+__global__ void __launch_bounds__(32) viterbi_warp_kernel(
+    const float* __restrict__ P, const float4* __restrict__ nodes,
+    int ld, i64 latStride, int nDiag, int ringDepth, uint32_t* __restrict__ decBits, int decInSmem,
+    int* __restrict__ frames, int* __restrict__ labelsOut, const int* __restrict__ inLens,
+    const int* __restrict__ labLens, int maxT, int maxU, int V, int blank, int* status) {
   extern __shared__ __align__(128) uint8_t smemV[];
   __shared__ uint64_t bar[kRing];
   __shared__ int abortFlag;
   __shared__ int sFrame[256];  // frame at which label u-1 was emitted (U <= 256 here)
   const int b = blockIdx.x, i = threadIdx.x, lane = i & 31, warp = i >> 5;
   const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
-  if (T <= 0 || U <= 0) return;
-  const float* e = E + (i64)b * maxT * V;
+  int* fr = frames + (i64)b * maxU;
+  if (T <= 0 || U <= 0) {
+    for (int u = i; u < maxU; u += 32) fr[u] = -1;
+    return;
+  }
   const float* p = P + (i64)b * maxU * V;
   const float4* nd = nodes + (i64)b * latStride;
   const int wordsD = viterbi_words_d(maxT, maxU);
-  uint32_t* dec = decBits + (i64)b * maxU * wordsD;
-  for (int u = i; u < U; u += 256) sFrame[u] = -1;
+  uint32_t* dec = decInSmem
+                      ? reinterpret_cast<uint32_t*>(smemV + (size_t)ringDepth * kDiag * ld * 16)
+                      : decBits + (i64)b * maxU * wordsD;
+  for (int u = i; u < 256; u += 32) sFrame[u] = -1;
   if (i == 0) {
     for (int s = 0; s < kRing; ++s) mbar_init(&bar[s], 1);
     abortFlag = 0;
@@ -599,7 +607,8 @@ __global__ void __launch_bounds__(256) viterbi_warp_kernel(
   }
   __syncthreads();
   if (abortFlag) {  // a copy never landed (recorded in the status word): no path, labels = -1
-    for (int u = i; u < U - 1; u += 256) labelsOut[(i64)b * (maxU - 1) + u] = -1;
+    for (int u = i; u < U - 1; u += 32) labelsOut[(i64)b * (maxU - 1) + u] = -1;
+    for (int u = i; u < maxU; u += 32) fr[u] = -1;
     return;
   }
 
@@ -622,58 +631,65 @@ __global__ void __launch_bounds__(256) viterbi_warp_kernel(
     }
   }
   __syncthreads();
+  for (int u = i; u < maxU; u += 32) fr[u] = (u < U) ? sFrame[u] : -1;
+}
 
-  // Label on each emitting arc of the path: lowest-index argmax over v != blank
-  // of E[t,v] + P[u-1,v] (strict '>' in index order, as the reference's getMax).
-  int* out = labelsOut + (i64)b * (maxU - 1);
-  const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(e) | reinterpret_cast<uintptr_t>(p)) & 15) == 0;
-  for (int u = 1 + warp; u < U; u += 8) {
-    const int t = sFrame[u];
-    if (t < 0) continue;
-    const float* er = e + (i64)t * V;
-    const float* pr = p + (i64)(u - 1) * V;
-    float m = neg_inf();
-    int arg = 0x7fffffff;
-    if (vec4) {  // 16 loads in flight per lane; each lane still visits its entries in index order
-      const float4* e4 = reinterpret_cast<const float4*>(er);
-      const float4* p4 = reinterpret_cast<const float4*>(pr);
-      const int n4 = V >> 2;
-      for (int q0 = lane; q0 < n4; q0 += 128) {
-        float4 a[4], c[4];
+// Label on each emitting arc of the path: lowest-index argmax over v != blank of
+// E[t,v] + P[u-1,v] (strict '>' in index order, as the reference's getMax,
+// transducer_cpu.cpp:156-169), one warp per label position, t = frames[b,u].
+__global__ void __launch_bounds__(256) viterbi_labels_kernel(
+    const float* __restrict__ E, const float* __restrict__ P, const int* __restrict__ frames,
+    int* __restrict__ labelsOut, const int* __restrict__ labLens, int maxT, int maxU, int V,
+    int blank) {
+  const int b = blockIdx.y, lane = threadIdx.x & 31;
+  const int u = 1 + blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (u >= min(labLens[b] + 1, maxU)) return;
+  const int t = frames[(i64)b * maxU + u];
+  if (t < 0) return;
+  const float* er = E + ((i64)b * maxT + t) * V;
+  const float* pr = P + ((i64)b * maxU + u - 1) * V;
+  const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(er) | reinterpret_cast<uintptr_t>(pr)) & 15) == 0;
+  float m = neg_inf();
+  int arg = 0x7fffffff;
+  if (vec4) {  // 16 loads in flight per lane; each lane still visits its entries in index order
+    const float4* e4 = reinterpret_cast<const float4*>(er);
+    const float4* p4 = reinterpret_cast<const float4*>(pr);
+    const int n4 = V >> 2;
+    for (int q0 = lane; q0 < n4; q0 += 128) {
+      float4 a[4], c[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int q = min(q0 + 32 * j, n4 - 1);
-          a[j] = e4[q];
-          c[j] = p4[q];
-        }
+      for (int j = 0; j < 4; ++j) {
+        const int q = min(q0 + 32 * j, n4 - 1);
+        a[j] = e4[q];
+        c[j] = p4[q];
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int q = q0 + 32 * j;
-          if (q < n4) {
-            const float x[4] = {a[j].x + c[j].x, a[j].y + c[j].y, a[j].z + c[j].z, a[j].w + c[j].w};
+      for (int j = 0; j < 4; ++j) {
+        const int q = q0 + 32 * j;
+        if (q < n4) {
+          const float x[4] = {a[j].x + c[j].x, a[j].y + c[j].y, a[j].z + c[j].z, a[j].w + c[j].w};
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const int v = 4 * q + h;
-              if (v != blank && x[h] > m) { m = x[h]; arg = v; }
-            }
+          for (int h = 0; h < 4; ++h) {
+            const int v = 4 * q + h;
+            if (v != blank && x[h] > m) { m = x[h]; arg = v; }
           }
         }
       }
-    } else {
-      for (int v = lane; v < V; v += 32) {
-        if (v == blank) continue;
-        const float x = er[v] + pr[v];
-        if (x > m) { m = x; arg = v; }
-      }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
-      const int a2 = __shfl_xor_sync(0xffffffffu, arg, o);
-      if (m2 > m || (m2 == m && a2 < arg)) { m = m2; arg = a2; }
+  } else {
+    for (int v = lane; v < V; v += 32) {
+      if (v == blank) continue;
+      const float x = er[v] + pr[v];
+      if (x > m) { m = x; arg = v; }
     }
-    if (lane == 0) out[u - 1] = (arg == 0x7fffffff) ? 0 : arg;
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const int a2 = __shfl_xor_sync(0xffffffffu, arg, o);
+    if (m2 > m || (m2 == m && a2 < arg)) { m = m2; arg = a2; }
+  }
+  if (lane == 0) labelsOut[(i64)b * (maxU - 1) + u - 1] = (arg == 0x7fffffff) ? 0 : arg;
 }
 
 template <typename K>
@@ -722,8 +738,9 @@ void launch_gamma_warp(const float2* arcs, const float* alphasS, const float* de
 bool viterbi_warp_supported(Dims d) { return d.maxU >= 1 && d.maxU <= 256; }
 
 size_t viterbi_warp_decbits_words(Dims d) {
+  // decision bits, then the frames at which the labels are emitted [B,maxU]
   return viterbi_warp_supported(d)
-             ? (size_t)d.B * (size_t)d.maxU * (size_t)viterbi_words_d(d.maxT, d.maxU)
+             ? (size_t)d.B * (size_t)d.maxU * (size_t)(viterbi_words_d(d.maxT, d.maxU) + 1)
              : 0;
 }
 
@@ -745,16 +762,24 @@ void launch_viterbi_warp(const float* E, const float* P, const float* LN, const 
                                                   d.maxU, d.V, d.blank, g.ld, g.stride);
     TB200_CHECK_LAUNCH();
   }
+  // shared memory: the decision bits (if they leave room for a ring of at least three blocks
+  // of node records), then the ring
   const int slotBytes = kDiag * g.ld * 16;
-  const int ringDepth = std::max(2, std::min(kRing, (200 * 1024) / slotBytes));
-  const int smem = ringDepth * slotBytes;
+  const int decBytes = d.maxU * viterbi_words_d(d.maxT, d.maxU) * 4;
+  const int room = 216 * 1024;
+  const int decInSmem = decBytes + 3 * slotBytes <= room ? 1 : 0;
+  const int ringDepth = std::max(2, std::min(kRing, (room - (decInSmem ? decBytes : 0)) / slotBytes));
+  const int smem = ringDepth * slotBytes + (decInSmem ? decBytes : 0);
+  int* frames = reinterpret_cast<int*>(decBits) +
+                (size_t)d.B * d.maxU * viterbi_words_d(d.maxT, d.maxU);
+  {
   ScopedKernel sk("viterbi_warp", stream);
 #define CALL(NPL)                                                                              \
   do {                                                                                         \
     allow_dyn_smem(viterbi_warp_kernel<NPL>, smem);                                            \
-    viterbi_warp_kernel<NPL><<<d.B, 256, smem, stream>>>(                                      \
-        E, P, nodes, g.ld, g.stride, g.nDiag, ringDepth, decBits, labels, inLens, labLens,     \
-        d.maxT, d.maxU, d.V, d.blank, status);                                                 \
+    viterbi_warp_kernel<NPL><<<d.B, 32, smem, stream>>>(                                       \
+        P, nodes, g.ld, g.stride, g.nDiag, ringDepth, decBits, decInSmem, frames, labels,      \
+        inLens, labLens, d.maxT, d.maxU, d.V, d.blank, status);                                \
   } while (0)
   switch (g.ld / 32) {
     case 1: CALL(1); break;
@@ -767,7 +792,14 @@ void launch_viterbi_warp(const float* E, const float* P, const float* LN, const 
     default: CALL(8); break;
   }
 #undef CALL
+  }
   TB200_CHECK_LAUNCH();
+  if (d.maxU > 1) {
+    ScopedKernel sk("viterbi_labels", stream);
+    viterbi_labels_kernel<<<dim3(div_up(d.maxU - 1, 8), d.B), 256, 0, stream>>>(
+        E, P, frames, labels, labLens, d.maxT, d.maxU, d.V, d.blank);
+    TB200_CHECK_LAUNCH();
+  }
 }
 
 }  // namespace tb200
