@@ -639,13 +639,14 @@ __global__ void __launch_bounds__(32) viterbi_warp_kernel(
 // transducer_cpu.cpp:156-169), one warp per label position, t = frames[b,u].
 __global__ void __launch_bounds__(256) viterbi_labels_kernel(
     const float* __restrict__ E, const float* __restrict__ P, const int* __restrict__ frames,
-    int* __restrict__ labelsOut, const int* __restrict__ labLens, int maxT, int maxU, int V,
-    int blank) {
-  const int b = blockIdx.y, lane = threadIdx.x & 31;
+    int* __restrict__ labelsOut, const int* __restrict__ labLens, int B, int maxT, int maxU,
+    int V, int blank) {
+  const int lane = threadIdx.x & 31;
   const int u = 1 + blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (u >= min(labLens[b] + 1, maxU)) return;
+  for (int b = blockIdx.y; b < B; b += gridDim.y) {
+  if (u >= min(labLens[b] + 1, maxU)) continue;
   const int t = frames[(i64)b * maxU + u];
-  if (t < 0) return;
+  if (t < 0) continue;
   const float* er = E + ((i64)b * maxT + t) * V;
   const float* pr = P + ((i64)b * maxU + u - 1) * V;
   const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(er) | reinterpret_cast<uintptr_t>(pr)) & 15) == 0;
@@ -690,6 +691,7 @@ __global__ void __launch_bounds__(256) viterbi_labels_kernel(
     if (m2 > m || (m2 == m && a2 < arg)) { m = m2; arg = a2; }
   }
   if (lane == 0) labelsOut[(i64)b * (maxU - 1) + u - 1] = (arg == 0x7fffffff) ? 0 : arg;
+  }
 }
 
 template <typename K>
@@ -796,8 +798,8 @@ void launch_viterbi_warp(const float* E, const float* P, const float* LN, const 
   TB200_CHECK_LAUNCH();
   if (d.maxU > 1) {
     ScopedKernel sk("viterbi_labels", stream);
-    viterbi_labels_kernel<<<dim3(div_up(d.maxU - 1, 8), d.B), 256, 0, stream>>>(
-        E, P, frames, labels, labLens, d.maxT, d.maxU, d.V, d.blank);
+    viterbi_labels_kernel<<<dim3(div_up(d.maxU - 1, 8), std::min(d.B, 65535)), 256, 0, stream>>>(
+        E, P, frames, labels, labLens, d.B, d.maxT, d.maxU, d.V, d.blank);
     TB200_CHECK_LAUNCH();
   }
 }

@@ -135,7 +135,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kSumLo = 1e-30f, kSumHi = 1e30f;
 
 // ---------------------------------------------------------------------------------
-// exp(P - maxP) split into TF32 hi/lo, zero-padded to [B][nPad][kPad]
+// exp(P - maxP) split into TF32 hi/lo as [B][nPad][kPad]: rows u < U_b, columns zero-padded to kPad
 // ---------------------------------------------------------------------------------
 template <typename TIn>
 __global__ void __launch_bounds__(256) expp_split_kernel(
@@ -152,8 +152,9 @@ __global__ void __launch_bounds__(256) expp_split_kernel(
   float4* hi4 = reinterpret_cast<float4*>(hi);
   float4* lo4 = reinterpret_cast<float4*>(lo);
   if (u >= U) {
-    const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int v = threadIdx.x; v < kPad / 4; v += blockDim.x) { hi4[v] = z; lo4[v] = z; }
+    // Rows beyond the utterance's label axis are left as they are: row u of the operand only
+    // feeds column u of the accumulator, which nobody reads for u >= U_b -- whatever the row
+    // holds (stale numbers, NaN patterns) stays in that column.
     if (u < maxU && threadIdx.x == 0 && maxP) maxP[(i64)b * maxU + u] = 0.0f;
     return;
   }

@@ -532,7 +532,7 @@ struct Scratch {
 
 bool maxplus_pruned_supported(Dims d) {
   // below ~1000 words the lists are most of the row
-  return d.B > 0 && d.maxT > 0 && d.maxU > 1 && d.V >= 1024 && d.V <= kMaxWords &&
+  return d.B > 0 && d.B <= 65535 && d.maxT > 0 && d.maxU > 1 && d.V >= 1024 && d.V <= kMaxWords &&
          (i64)d.V * label_stride(d) < (i64(1) << 31);
 }
 
