@@ -667,6 +667,11 @@ def parity_block(w, r, device_case, state):
         out["oracle_vs_fp64_floor"] = {
             "egrad": float(np.abs(want["egrads"][:1] - truth["egrads"]).max() / den_e),
             "pgrad": float(np.abs(want["pgrads"][:1] - truth["pgrads"]).max() / den_p)}
+        # ... and this run's distance to the same float64 evaluation (same utterance)
+        ge = E.grad[:1].detach().float().cpu().numpy().astype(np.float64)
+        gp = P.grad[:1].detach().float().cpu().numpy().astype(np.float64)
+        out["ours_vs_fp64"] = {"egrad": float(np.abs(ge - truth["egrads"]).max() / den_e),
+                               "pgrad": float(np.abs(gp - truth["pgrads"]).max() / den_p)}
     return out
 
 
