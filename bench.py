@@ -745,15 +745,27 @@ def run_e2e(w, crit, device_case, dev, distributed, world, global_B, steps):
         out_eg = torch.empty(host[0].shape, dtype=E.dtype).pin_memory()
         out_pg = torch.empty(host[1].shape, dtype=E.dtype).pin_memory()
         d2h = sum(t.numel() * t.element_size() for t in (out_costs, out_eg, out_pg))
-        pipe = HostLossPipeline(blank=crit.blank, chunk=2, slots=4, device=dev)
-        api = "transducer_b200.HostLossPipeline(chunk=2, slots=4)"
+        pipe = HostLossPipeline(blank=crit.blank, chunk=2, slots=4, device=dev, valid_rows_only=True)
+        api = "transducer_b200.HostLossPipeline(chunk=2, slots=4, valid_rows_only=True)"
+        valid = host[3].clamp(max=w.T).double()
+        valid_u = (host[4] + 1).clamp(max=w.U + 1).double()
+        moved = float(valid.sum()) * w.V * host[0].element_size() + \
+            float(valid_u.sum()) * w.V * host[1].element_size()
+        h2d = moved + sum(t.numel() * t.element_size() for t in host[2:])
+        d2h = moved + out_costs.numel() * 4
 
         def local():
             return pipe(*host, out_costs, out_eg, out_pg)
     elif w.task == "loss_fwd":
         d2h = out_costs.numel() * 4
-        pipe = HostLossPipeline(blank=crit.blank, chunk=4, slots=3, device=dev, forward_only=True)
-        api = "transducer_b200.HostLossPipeline(chunk=4, slots=3, forward_only=True)"
+        pipe = HostLossPipeline(blank=crit.blank, chunk=4, slots=3, device=dev, forward_only=True,
+                                valid_rows_only=True)
+        api = "transducer_b200.HostLossPipeline(chunk=4, slots=3, forward_only=True, valid_rows_only=True)"
+        valid = host[3].clamp(max=w.T).double()
+        valid_u = (host[4] + 1).clamp(max=w.U + 1).double()
+        h2d = float(valid.sum()) * w.V * host[0].element_size() + \
+            float(valid_u.sum()) * w.V * host[1].element_size() + \
+            sum(t.numel() * t.element_size() for t in host[2:])
 
         def local():
             return pipe(*host, out_costs, None, None)
@@ -761,9 +773,13 @@ def run_e2e(w, crit, device_case, dev, distributed, world, global_B, steps):
         out_labels = torch.empty((n, w.U), dtype=torch.int32).pin_memory()
         d2h = out_labels.numel() * 4
         h2d -= host[2].numel() * 4   # labels are an output here
-        api = "TransducerLoss.viterbi on chunks of 8 utterances, 3 streams"
+        api = "TransducerLoss.viterbi on chunks of 8 utterances, 3 streams, valid frames / positions only over the link"
         slots = [(torch.cuda.Stream(device=dev), {}) for _ in range(3)]
         chunk = 8
+        t_len = [min(int(x), w.T) for x in host[3].tolist()]
+        u_len = [min(int(x) + 1, w.U + 1) for x in host[4].tolist()]
+        h2d = (sum(t_len) * host[0].element_size() + sum(u_len) * host[1].element_size()) * w.V + \
+            host[3].numel() * 4 + host[4].numel() * 4 + host[2].numel() * 4
 
         def local():
             main = torch.cuda.current_stream()
@@ -778,8 +794,9 @@ def run_e2e(w, crit, device_case, dev, distributed, world, global_B, steps):
                         buf["il"] = torch.empty((hi - lo,), dtype=torch.int32, device=dev)
                         buf["ll"] = torch.empty((hi - lo,), dtype=torch.int32, device=dev)
                         buf["n"] = hi - lo
-                    buf["E"].copy_(host[0][lo:hi], non_blocking=True)
-                    buf["P"].copy_(host[1][lo:hi], non_blocking=True)
+                    for k in range(hi - lo):   # (the kernels never read the padding)
+                        buf["E"][k, :t_len[lo + k]].copy_(host[0][lo + k, :t_len[lo + k]], non_blocking=True)
+                        buf["P"][k, :u_len[lo + k]].copy_(host[1][lo + k, :u_len[lo + k]], non_blocking=True)
                     buf["il"].copy_(host[3][lo:hi], non_blocking=True)
                     buf["ll"].copy_(host[4][lo:hi], non_blocking=True)
                     lab = crit.viterbi(buf["E"], buf["P"], buf["il"], buf["ll"])

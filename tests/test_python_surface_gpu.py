@@ -147,6 +147,33 @@ def test_host_pipeline_matches_whole_batch_call():
         pipe(E.cuda(), P, labels, il, ll, costs, eg, pg)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_host_pipeline_moving_valid_rows_only_gives_the_same_outputs(dtype):
+    """valid_rows_only: the padding never crosses the link; the outputs are complete all the same
+    (the padding of the gradients is zero-filled on the host)."""
+    from transducer_b200 import HostLossPipeline
+    g = torch.Generator().manual_seed(23)
+    B, T, U, V = 5, 140, 20, 512
+    E = torch.randn((B, T, V), generator=g).to(dtype).pin_memory()
+    P = torch.randn((B, U, V), generator=g).to(dtype).pin_memory()
+    labels = torch.randint(1, V, (B, U - 1), generator=g, dtype=torch.int32).pin_memory()
+    il = torch.randint(T // 3, T + 1, (B,), generator=g, dtype=torch.int32).pin_memory()
+    ll = torch.randint(0, U, (B,), generator=g, dtype=torch.int32).pin_memory()
+    il[1], ll[1] = T, U - 1
+    outs = {}
+    for sparse in (False, True):
+        costs = torch.full((B,), float("nan")).pin_memory()
+        eg = torch.full(E.shape, float("nan"), dtype=dtype).pin_memory()
+        pg = torch.full(P.shape, float("nan"), dtype=dtype).pin_memory()
+        pipe = HostLossPipeline(chunk=2, slots=2, valid_rows_only=sparse)
+        for _ in range(2):   # (the second call finds other utterances' rows in the slots)
+            pipe(E, P, labels, il, ll, costs, eg, pg)
+            torch.cuda.synchronize()
+        outs[sparse] = (costs, eg, pg)
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+
+
 def test_forward_backward_can_be_captured_in_a_cuda_graph():
     """The fused calls only enqueue work (kernels, memsets) on the chosen stream, so a training
     step can be captured once and replayed."""

@@ -59,6 +59,12 @@ class HostLossPipeline(object):
         device: CUDA device (default: the current one).
         forward_only (bool): compute the costs only (no gradients; pass None for egrads and
             pgrads).
+        valid_rows_only (bool): move only the frames t < input_lengths[b] of the emissions and
+            of their gradient, and only the positions u <= label_lengths[b] of the predictions
+            and of theirs, over the link (the kernels never read the padding, and its gradient
+            is zero by definition); the padding of egrads / pgrads is zero-filled on the host
+            while the device works, so the outputs are complete either way.  Saves the padded
+            share of the traffic: 12 % at lengths of 1500..2000 in 2000 frames.
 
     Call with host tensors (pinned memory, or the copies will not overlap):
         emissions float32 [B,T,V], predictions float32 [B,U+1,V], labels int32 [B,U],
@@ -71,7 +77,8 @@ class HostLossPipeline(object):
     to wait for the pipeline) has been synchronised.
     """
 
-    def __init__(self, blank=0, chunk=8, slots=3, device=None, forward_only=False):
+    def __init__(self, blank=0, chunk=8, slots=3, device=None, forward_only=False,
+                 valid_rows_only=False):
         if not torch.cuda.is_available():
             raise RuntimeError("transducer_b200 runs on CUDA devices only")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
@@ -81,6 +88,7 @@ class HostLossPipeline(object):
         self.slots = [_Slot(self.device) for _ in range(int(slots))]
         self.loss_parts = None
         self.forward_only = bool(forward_only)
+        self.valid_rows_only = bool(valid_rows_only)
 
     def __call__(self, emissions, predictions, labels, input_lengths, label_lengths,
                  costs, egrads, pgrads, deltas=None):
@@ -112,6 +120,10 @@ class HostLossPipeline(object):
         n_chunks = (B + self.chunk - 1) // self.chunk
         if self.loss_parts is None or self.loss_parts.numel() != max(n_chunks, 1):
             self.loss_parts = torch.zeros((max(n_chunks, 1),), device=dev, dtype=torch.float32)
+        sparse = self.valid_rows_only
+        if sparse:
+            t_len = [min(int(x), T) for x in input_lengths.tolist()]
+            u_len = [min(int(x) + 1, U) for x in label_lengths.tolist()]
         caller = torch.cuda.current_stream(dev)
         start = torch.cuda.Event()
         start.record(caller)
@@ -123,8 +135,15 @@ class HostLossPipeline(object):
                 slot.stream.wait_event(start)
                 with torch.cuda.stream(slot.stream):
                     slot.fit(self.chunk, T, U, V, dev, self.forward_only, dtype)  # views of n <= chunk rows below
-                    slot.E[:n].copy_(emissions[lo:hi], non_blocking=True)
-                    slot.P[:n].copy_(predictions[lo:hi], non_blocking=True)
+                    if sparse:
+                        for k in range(n):
+                            slot.E[k, :t_len[lo + k]].copy_(emissions[lo + k, :t_len[lo + k]],
+                                                            non_blocking=True)
+                            slot.P[k, :u_len[lo + k]].copy_(predictions[lo + k, :u_len[lo + k]],
+                                                            non_blocking=True)
+                    else:
+                        slot.E[:n].copy_(emissions[lo:hi], non_blocking=True)
+                        slot.P[:n].copy_(predictions[lo:hi], non_blocking=True)
                     slot.labels[:n].copy_(labels[lo:hi], non_blocking=True)
                     slot.il[:n].copy_(input_lengths[lo:hi], non_blocking=True)
                     slot.ll[:n].copy_(label_lengths[lo:hi], non_blocking=True)
@@ -146,11 +165,26 @@ class HostLossPipeline(object):
                             slot.saved_bytes, slot.deltas.data_ptr(), slot.eg.data_ptr(),
                             slot.pg.data_ptr(), n, T, U, V, self.blank, slot.ws.data_ptr(),
                             slot.bwd_bytes)
-                        egrads[lo:hi].copy_(slot.eg[:n], non_blocking=True)
-                        pgrads[lo:hi].copy_(slot.pg[:n], non_blocking=True)
+                        if sparse:
+                            for k in range(n):
+                                egrads[lo + k, :t_len[lo + k]].copy_(slot.eg[k, :t_len[lo + k]],
+                                                                     non_blocking=True)
+                                pgrads[lo + k, :u_len[lo + k]].copy_(slot.pg[k, :u_len[lo + k]],
+                                                                     non_blocking=True)
+                        else:
+                            egrads[lo:hi].copy_(slot.eg[:n], non_blocking=True)
+                            pgrads[lo:hi].copy_(slot.pg[:n], non_blocking=True)
             for slot in self.slots:
                 done = torch.cuda.Event()
                 done.record(slot.stream)
                 caller.wait_event(done)
             _transducer.set_stream(caller.cuda_stream)
+        if sparse and not self.forward_only:
+            # the padding of the gradients, on the host, while the device works (the copies
+            # above touch other rows of the same buffers)
+            for bb in range(B):
+                if t_len[bb] < T:
+                    egrads[bb, t_len[bb]:].zero_()
+                if u_len[bb] < U:
+                    pgrads[bb, u_len[bb]:].zero_()
         return self.loss_parts.sum().reshape(1)
