@@ -43,7 +43,10 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-A100_README_MS = 223.33  # B=32,T=2000,U=100,V=10000 on A100 (reference README.md:80)
+# fwd+bwd milliseconds the reference publishes for these shapes (A100, its README.md:68-71,80):
+# workload -> (batch, ms)
+PUBLISHED_MS = {"c3": (32, 223.33), "c2_v100": (8, 8.18), "c2_v1000": (8, 13.64),
+                "c2_v2000": (8, 18.83), "c2_v10000": (8, 59.18)}
 
 METRICS = {"loss": "rnnt_loss_fwd_bwd_utterances_per_s",
            "loss_fwd": "rnnt_loss_fwd_utterances_per_s",
@@ -607,8 +610,8 @@ def main():
             "metric": METRICS[w.task], "value": value, "unit": "utterances/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": scaling_of(w),
-            "vs_baseline": (B / (ms_step * 1e-3)) / (32 / (A100_README_MS * 1e-3))
-            if w.name == "c3" and B == w.B and not bf16 else None,
+            "vs_baseline": value / (PUBLISHED_MS[w.name][0] / (PUBLISHED_MS[w.name][1] * 1e-3))
+            if w.name in PUBLISHED_MS and B == w.B and not bf16 else None,
             "dtype": "f32 arithmetic on bf16 storage (emissions, predictions, gradients)" if bf16 else "f32",
             "data": "synthetic", "config": workload_config(w, world, B, args.reduce),
             "clocks": clk, "e2e": e2e, "gpu_launches": int(launches),
