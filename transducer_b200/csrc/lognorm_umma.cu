@@ -5,22 +5,25 @@
 // which is what the reference computes with torch ops (transducer/torch_binding.py:35-40:
 // row maxima, exp, bmm, log) -- here in ONE pass over E and without storing exp(E).
 //
-// Tile: 128 frames of one utterance (UMMA M=128) x all label positions (N = maxU rounded
-// up to 16, <= 256) x the whole vocabulary in K-chunks of 32 floats.
+// Work item: 128 frames of one utterance (UMMA M=128) x up to 128 label positions (N = the
+// positions rounded up to 16; a label axis of 129..256 positions is cut into two column ranges,
+// each a work item of its own that reads the tile's chunks of E again) x the whole vocabulary
+// in K-chunks of 32 words.  Emissions fp32 or bf16 (converted in the transform).
 //
-// Roles inside a CTA (one CTA per SM, 10 or 14 warps):
-//   warps 0-3   operand transform.  Thread r owns frame r of the tile (= TMEM lane r):
-//               reads its 128-byte row of the raw E chunk from shared memory, computes
-//               x = exp(E - ref), splits x = hi + lo with hi exactly representable in
-//               TF32, and stores hi/lo straight into TENSOR MEMORY (the A operand of the
-//               MMA is read from TMEM, so the transformed tile never goes back through
-//               shared memory).
-//   warps 4-7   (and 8-11 when the label axis exceeds 128) accumulator drain + epilogue:
-//               after every kGroup chunks they add the TMEM accumulator into fp32
-//               registers (round-to-nearest) and hand the accumulator back, so the tensor
-//               core's truncating accumulation never runs over more than 24 steps.
-//   next warp   TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage.
-//   last 2 warps MMA issuers (one accumulator each): per 8-wide k-step three kind::tf32 MMAs
+// Roles inside a CTA (one CTA per SM, 19 warps):
+//   warps 0-7   operand transform, two groups of four that take alternate chunks.  Thread r of
+//               a group owns frame r of the tile (= TMEM lane r): reads its row of the raw E
+//               chunk from shared memory, computes x = exp(E - ref), splits x = hi + lo with hi
+//               exactly representable in TF32, and stores hi/lo straight into TENSOR MEMORY
+//               (the A operand of the MMA is read from TMEM, so the transformed tile never goes
+//               back through shared memory).  On the way it hands out E[t,label_u] and
+//               E[t,blank] for the lattice sweeps.
+//   warps 8-15  accumulator drain + epilogue, one warpgroup per 64 accumulator columns: after
+//               every kGroup chunks they add the TMEM accumulator into fp32 registers
+//               (round-to-nearest) and hand the accumulator back, so the tensor core's
+//               truncating accumulation never runs over more than 24 steps.
+//   warp 16     TMA producer: raw E chunk + pre-split exp(P) hi/lo chunks per stage (4 stages).
+//   warps 17-18 MMA issuers (one accumulator each): per 8-wide k-step three kind::tf32 MMAs
 //               hi*Bhi + lo*Bhi + hi*Blo into the current accumulator (the 3xTF32 split
 //               reproduces fp32 products to ~2^-21 relative).
 //
@@ -469,7 +472,7 @@ __global__ void __launch_bounds__((4 * NTW + 4 * NDRAIN + 3) * 32, 1) lognorm_um
     // the chunk groups g with g % 2 == m: while one issuer is blocked on its barrier waits
     // and commits (~800 cycles per chunk, measured), the other keeps the tensor pipe fed.
     // The two never touch the same accumulator or operand stage, so no order between their
-    // MMAs is needed.  With a single accumulator only issuer 0 works.
+    // MMAs is needed.
     const int m = warp - kMmaWarp;
     if (lane == 0 && m < nAcc) {
       const uint32_t idesc = idesc_tf32(kTileM, p.nPad, 0, 0);
