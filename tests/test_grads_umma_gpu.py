@@ -42,6 +42,9 @@ def grads(E, P, labels, il, ll, deltas, path, passes=2, blank=0):
 SHAPES = [
     (2, 200, 33, 128, 1.0), (2, 150, 21, 260, 2.0), (3, 300, 101, 1000, 1.0), (1, 130, 1, 64, 1.0),
     (2, 100, 128, 160, 1.0), (2, 90, 64, 96, 1.0), (1, 64, 17, 32, 1.0), (2, 500, 101, 4000, 2.0),
+    # label axes of more than 128 positions: two launches over halves of the axis, the second
+    # adding to egrads (the lengths of the second utterance put it below / inside the second half)
+    (2, 260, 151, 512, 1.0), (3, 180, 201, 1000, 1.0), (2, 300, 256, 264, 1.0), (2, 150, 129, 128, 1.0),
 ]
 
 
@@ -80,6 +83,22 @@ def test_repeated_labels_and_nonzero_blank_against_oracle():
     want = O.loss_and_grads(n(E), n(P), n(labels), n(il), n(ll), blank=blank, deltas=n(deltas))
     assert abi.rel_to_max(n(eg), want["egrads"]) <= 3e-4
     assert abi.rel_to_max(n(pg), want["pgrads"]) <= 3e-4
+
+
+def test_wide_label_axis_against_oracle_with_repeats_and_blank():
+    """U' = 201, few distinct labels (so that more than 16 of them fall into one column block in
+    both halves of the label axis) and a blank that is not 0."""
+    B, T, U, V, blank = 2, 230, 201, 256, 70
+    E, P, labels, il, ll, deltas = make(B, T, U, V, seed=14, repeat_labels=True, blank=blank)
+    ll[1] = 140
+    fwd, eg, pg = grads(E, P, labels, il, ll, deltas, path=2, blank=blank)
+    abi.check(abi.lib.tb200_check_status())
+    n = lambda t: t.cpu().numpy()
+    want = O.loss_and_grads(n(E), n(P), n(labels), n(il), n(ll), blank=blank, deltas=n(deltas))
+    np.testing.assert_allclose(n(fwd["costs"]), want["costs"], rtol=1e-4)
+    assert abi.rel_to_max(n(eg), want["egrads"]) <= 1e-3
+    assert abi.rel_to_max(n(pg), want["pgrads"]) <= 1e-3
+    assert pg[1, 141:].abs().max().item() == 0.0
 
 
 def test_zero_length_utterances_give_zero_gradients():

@@ -457,13 +457,13 @@ int loss_backward_any(const void* E, const void* P, const int* labels, const int
     if (g_opt.grads_path == 2 && !can)
       throw std::invalid_argument(
           "tensor-core gradients need alphabetSize % 4 == 0, alphabetSize >= 32, "
-          "maxLabelLength <= 128 and 16-byte aligned emissions and egrads");
+          "maxLabelLength <= 256 and 16-byte aligned emissions and egrads");
     const bool tensorCore = can && g_opt.grads_path != 1;
     if (dtype != kDtypeF32 && !(tensorCore && lattice_warp_supported(d)))
       throw std::invalid_argument(
           "bf16 gradients need the tensor-core gradient kernel: alphabetSize % 8 == 0, "
           "maxLabelLength <= 128, grad_passes = 2, 16-byte aligned buffers");
-    if ((egrads == E || pgrads == P) && !(tensorCore && lattice_warp_supported(d)))
+    if ((egrads == E || pgrads == P) && !(tensorCore && lattice_warp_supported(d)))   // (one launch only)
       throw std::invalid_argument(
           "gradients in place (egrads == emissions / pgrads == predictions) need the "
           "tensor-core gradient kernel: alphabetSize % 4 == 0, maxLabelLength <= 128");
@@ -492,6 +492,16 @@ int loss_backward_any(const void* E, const void* P, const int* labels, const int
                         inLens, labLens, ws.Ws, ws.EMs, ws.eBlank, ws.pBlank, ws.pLabel, d,
                         g_stream);
       launch_lattice_unskew(ws.Ws, ws.EMs, ws.W, ldW, ws.em, inLens, labLens, g, d, g_stream);
+      if (tensorCore) {
+        // label axes of 129..256 positions: the block-wide sweep's outputs re-laid out as the
+        // tensor-core kernel's operands; the kernel runs once per half of the label axis
+        launch_tc_operands(ws.W, ws.em, ws.eBlank, st.rowRef, deltas, ws.emT, ws.nref, ws.ebl,
+                           inLens, d, g_stream);
+        launch_grads_umma(E, P, st.maxP, ws.W, ws.emT, ws.nref, ws.ebl, ws.pBlank, ws.pLabel,
+                          labels, deltas, egrads, pgrads, inLens, labLens, d, passes,
+                          device_status_word(), g_stream);
+        return;
+      }
     }
     launch_exp_rows(Pf, ws.expP, ws.maxPScratch, labLens, B, maxU, V, g_stream);
     launch_egrad_simt(Ef, st.rowRef, ws.W, ldW, ws.expP, ws.eBlank, ws.em, labels, deltas,

@@ -83,6 +83,12 @@ struct GradParams {
   void* pgrads;
   int* status;
   int maxT, maxU, V, blank;
+  // Label axes of 129..256 positions run as two launches over the position ranges
+  // [uOff, uOff + 128): each computes its rows of pgrads and its share of egrads (the sum over
+  // its positions and their label-arc terms); the first launch writes egrads (and carries the
+  // blank-arc terms and the zero padding), the second ADDS its tiles to it (accumulate: the
+  // stores become TMA reduce-adds).
+  int uOff, accumulate;
   int ldT;      // maxT rounded up to 4: row length of nref / eBlank / emT
   int ldW;      // columns of W (multiple of 32, <= 128)
   int N2;       // GEMM2 N: maxU rounded up to 16 (<= ldW)
@@ -120,17 +126,23 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   constexpr int TBH = TB / 2;  // frames per owner half
   static_assert(TBH % 8 == 0, "tile halves move through TMEM in 8-column pieces");
   const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
-  const int T = min(p.inLens[b], p.maxT), U = min(p.labLens[b] + 1, p.maxU);
+  const int T = min(p.inLens[b], p.maxT), Utot = min(p.labLens[b] + 1, p.maxU);
+  // my range of label positions: local u <-> position uOff + u; U of them belong to the utterance
+  const int U = max(0, min(Utot - p.uOff, 128));
+  const int rowsMine = min(128, p.maxU - p.uOff);   // rows of pgrads this launch owns
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float delta = p.deltas ? p.deltas[b] : 1.0f;
   TIO* eg = static_cast<TIO*>(p.egrads) + (i64)b * p.maxT * p.V;
-  TIO* pg = static_cast<TIO*>(p.pgrads) + (i64)b * p.maxU * p.V;
+  TIO* pg = static_cast<TIO*>(p.pgrads) + ((i64)b * p.maxU + p.uOff) * p.V;
 
-  if (T <= 0 || U <= 0) {  // nothing flows through this utterance: gradients are zero
+  if (T <= 0 || U <= 0) {
+    // nothing flows through (this range of) the utterance: its rows of pgrads are zero, and so
+    // is egrads if this is the launch that writes it (an accumulating launch adds nothing)
     const int v = v0 + threadIdx.x;
     if (threadIdx.x < kVBlock && v < p.V) {
-      for (int t = 0; t < p.maxT; ++t) from_f32(eg[(i64)t * p.V + v], 0.0f);
-      for (int u = 0; u < p.maxU; ++u) from_f32(pg[(i64)u * p.V + v], 0.0f);
+      if (!p.accumulate)
+        for (int t = 0; t < p.maxT; ++t) from_f32(eg[(i64)t * p.V + v], 0.0f);
+      for (int u = 0; u < rowsMine; ++u) from_f32(pg[(i64)u * p.V + v], 0.0f);
     }
     return;
   }
@@ -163,7 +175,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   __shared__ float sPb[128], sPl[128];
 
   const int nTiles = (T + TB - 1) / TB;
-  const bool blankHere = p.blank >= v0 && p.blank < v0 + kVBlock;
+  // (the blank-arc terms go with the launch that writes egrads)
+  const bool blankHere = !p.accumulate && p.blank >= v0 && p.blank < v0 + kVBlock;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SE; ++s) {
@@ -192,9 +205,9 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
   if (threadIdx.x < 128) {
     const int u = threadIdx.x;
     if (u < U) {
-      sPb[u] = p.pBlank[(i64)b * p.maxU + u];
-      sPl[u] = p.pLabel[(i64)b * p.maxU + u];
-      if (u < U - 1) myLab = p.labels[(i64)b * (p.maxU - 1) + u];
+      sPb[u] = p.pBlank[(i64)b * p.maxU + p.uOff + u];
+      sPl[u] = p.pLabel[(i64)b * p.maxU + p.uOff + u];
+      if (p.uOff + u < Utot - 1) myLab = p.labels[(i64)b * (p.maxU - 1) + p.uOff + u];
     }
     sLab[u] = myLab;
     inBlock = myLab >= v0 && myLab < v0 + kVBlock;
@@ -258,7 +271,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     } else if (lane == 5) {
       if (blankHere) { myMap = &tm.ebl; myDst = kEBytes + kRowStride; myX = b; myZ = 0; yIsT0 = false; }
     } else if (lane >= 6 && lane - 6 < nStaged) {
-      myMap = &tm.emT; myDst = kEBytes + (lane - 4) * kRowStride; myX = sListU[lane - 6]; myZ = b; yIsT0 = false;
+      myMap = &tm.emT; myDst = kEBytes + (lane - 4) * kRowStride; myX = p.uOff + sListU[lane - 6]; myZ = b; yIsT0 = false;
     }
     int fs = 0;  // stage of the next fill
     auto fill = [&](int i) {
@@ -280,7 +293,10 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       // lanes 0..3 store one 32-column box each (every lane has a bulk group of its own), and
       // wait until the store engine has read their box before the stage is refilled
       if (lane < kBoxes && v0 + kBoxCols * lane < p.V) {
-        tma_store_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + kBoxCols * lane, i * TB, b);
+        if (p.accumulate)
+          tma_reduce_add_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + kBoxCols * lane, i * TB, b);
+        else
+          tma_store_3d(&tm.G, smem + (size_t)ss * kEStage + lane * kBoxBytes, v0 + kBoxCols * lane, i * TB, b);
         tma_store_commit();
         if (issued < nTiles) tma_store_wait_read();
       }
@@ -321,8 +337,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
       __syncwarp();
       const int j = lane >> 1;
       if (lane < 8 && j < nUB) {
-        if (lane & 1) tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], 32 * j, t0, b);
-        else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], 32 * j, t0, b);
+        if (lane & 1) tma_load_3d(st + wBytes + j * kBoxBytes, &tm.Wmn, &barWFull[s], p.uOff + 32 * j, t0, b);
+        else tma_load_3d(st + j * kBoxBytes, &tm.Wk, &barWFull[s], p.uOff + 32 * j, t0, b);
       }
       issued = i + 1;
       if (++s == SW) { s = 0; wph ^= 1u; }
@@ -417,8 +433,8 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 
     // expP^T[v, u] = exp(P[u,v] - maxP[u]) for u < U, zero beyond: resident A operand of GEMM1
     {
-      const TIO* pp = static_cast<const TIO*>(p.P) + (i64)b * p.maxU * p.V;
-      const float* mp = p.maxP + (i64)b * p.maxU;
+      const TIO* pp = static_cast<const TIO*>(p.P) + ((i64)b * p.maxU + p.uOff) * p.V;
+      const float* mp = p.maxP + (i64)b * p.maxU + p.uOff;
       const int vc = min(v, p.V - 1);
       for (int u0 = 8 * part; u0 < p.Ku; u0 += 32) {
         // unconditional loads from clamped addresses: all eight are in flight together
@@ -553,7 +569,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
         uint8_t* stE = smem + (size_t)se * kEStage;
         uint8_t* col = stE + colOff;
         const float* rows = reinterpret_cast<const float*>(stE + kEBytes + kRowStride) + h * TBH;
-        if (v == p.blank) {
+        if (v == p.blank && !p.accumulate) {
 #pragma unroll
           for (int j = 0; j < TBH; ++j) d1[j] -= rows[j];
         }
@@ -578,7 +594,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     }
 
     // padded frames beyond the last tile: exact zeros
-    if (vOk)
+    if (vOk && !p.accumulate)
       for (int t = nTiles * TB + part; t < p.maxT; t += 4) from_f32(eg[(i64)t * p.V + v], 0.0f);
 
     // pgrads[u, v] = delta * (expP[u,v] * D2[v,u] - sparse)
@@ -595,7 +611,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int u = u0 + j;
-          if (u < p.maxU && vOk) {
+          if (u < rowsMine && vOk) {
             float val = 0.0f;
             if (u < U) {
               float xp = __uint_as_float(xh[j]);
@@ -622,7 +638,7 @@ __global__ void __launch_bounds__(kGradThreads, 1) grads_umma_kernel(
     const float bad = __int_as_float(0x7fc00000);
     const int v = v0 + threadIdx.x;
     for (int t = 0; t < p.maxT; ++t) from_f32(eg[(i64)t * p.V + v], bad);
-    for (int u = 0; u < p.maxU; ++u) from_f32(pg[(i64)u * p.V + v], bad);
+    for (int u = 0; u < rowsMine; ++u) from_f32(pg[(i64)u * p.V + v], bad);
   }
 }
 
@@ -751,16 +767,18 @@ template <typename TIO>
 __global__ void __launch_bounds__(256) label_overflow_kernel(
     const int* __restrict__ labels, const float* __restrict__ emT, TIO* __restrict__ egrads,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
-    int ldT) {
+    int ldT, int uOff) {
   __shared__ short sU[128];
   __shared__ short sV[128];
   __shared__ int sCount;
   const int b = blockIdx.y, v0 = blockIdx.x * kVBlock;
-  const int T = min(inLens[b], maxT), U = min(labLens[b] + 1, maxU);
+  const int T = min(inLens[b], maxT), Utot = min(labLens[b] + 1, maxU);
+  // the labelled positions of this launch's range: uOff + u, u < U - 1 in the code below
+  const int U = min(Utot - uOff, 129);
   if (T <= 0 || U <= 1) return;
   __shared__ int sLab[128];
   int mine = -1;
-  if ((int)threadIdx.x < U - 1 && threadIdx.x < 128) mine = labels[(i64)b * (maxU - 1) + threadIdx.x];
+  if ((int)threadIdx.x < U - 1 && threadIdx.x < 128) mine = labels[(i64)b * (maxU - 1) + uOff + threadIdx.x];
   if (threadIdx.x < 128) sLab[threadIdx.x] = mine;
   // the normal case, decided by all threads at once: the block holds no more labels than are staged
   if (__syncthreads_count(mine >= v0 && mine < v0 + kVBlock) <= kMaxStagedLabels) return;
@@ -785,7 +803,52 @@ __global__ void __launch_bounds__(256) label_overflow_kernel(
   for (int t = blockIdx.z * 1024 + threadIdx.x; t < min(T, (int)(blockIdx.z + 1) * 1024); t += 256) {
     TIO* row = egrads + ((i64)b * maxT + t) * V + v0;
     for (int k = 0; k < n; ++k)
-      from_f32(row[sV[k]], to_f32(row[sV[k]]) - emT[((i64)b * maxU + sU[k]) * ldT + t]);
+      from_f32(row[sV[k]], to_f32(row[sV[k]]) - emT[((i64)b * maxU + uOff + sU[k]) * ldT + t]);
+  }
+}
+
+// Operands of the gradient kernel from the outputs of the block-wide reverse sweep (label axes
+// of more than 128 positions): W [B,maxT,ldW] = occupancy * exp(ref + maxP - LN), unrounded,
+// becomes delta_b * W rounded to TF32, in place; the label-arc occupancies em [B,maxT,maxU]
+// become emT [B,maxU,ldT] = delta_b * em, frames contiguous; the blank-arc sums eBlank [B,maxT]
+// become ebl [B,ldT] = delta_b * eBlank; rowRef becomes nref = -rowRef * log2(e); all three zero
+// for frames at or beyond T_b.  One CTA per 32 frames x 32 positions.
+__global__ void __launch_bounds__(256) tc_operands_kernel(
+    float* __restrict__ W, const float* __restrict__ em, const float* __restrict__ eBlank,
+    const float* __restrict__ rowRef, const float* __restrict__ deltas, float* __restrict__ emT,
+    float* __restrict__ nref, float* __restrict__ ebl, const int* __restrict__ inLens, int maxT,
+    int maxU, int ldW, int ldT) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z, t0 = blockIdx.x * 32, u0 = blockIdx.y * 32;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int T = min(inLens[b], maxT);
+  const float delta = deltas ? deltas[b] : 1.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int tt = w * 4 + k, t = t0 + tt, u = u0 + lane;
+    float e = 0.0f;
+    if (t < maxT) {
+      if (u < ldW) {
+        float* x = W + ((i64)b * maxT + t) * ldW + u;
+        *x = t < T ? tf32_round(*x * delta) : 0.0f;
+      }
+      if (t < T && u < maxU) e = em[((i64)b * maxT + t) * maxU + u] * delta;
+    }
+    tile[tt][lane] = e;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int uu = u0 + w * 4 + k, t = t0 + lane;
+    if (uu < maxU && t < ldT) emT[((i64)b * maxU + uu) * ldT + t] = tile[lane][w * 4 + k];
+  }
+  if (blockIdx.y == 0 && threadIdx.x < 32) {
+    const int t = t0 + lane;
+    if (t < ldT) {
+      const bool ok = t < T;
+      nref[(i64)b * ldT + t] = ok ? -rowRef[(i64)b * maxT + t] * kLog2e : 0.0f;
+      ebl[(i64)b * ldT + t] = ok ? eBlank[(i64)b * maxT + t] * delta : 0.0f;
+    }
   }
 }
 
@@ -850,15 +913,19 @@ int grads_umma_ld_t(Dims d) { return (int)round_up64(d.maxT > 0 ? d.maxT : 1, 4)
 bool grads_umma_supported(const void* E, const void* P, const void* egrads,
                           const void* pgrads, Dims d, int passes) {
   const bool bf = d.dtype == kDtypeBf16;
-  if (d.V % (bf ? 8 : 4) != 0 || d.V < 32 || d.maxU < 1 || d.maxU > 128 || d.B > 65535) return false;
+  // (label axes of 129..256 positions: two launches, the second adding to egrads -- fp32 only,
+  // a bf16 sum would be rounded twice)
+  if (d.V % (bf ? 8 : 4) != 0 || d.V < 32 || d.maxU < 1 || d.maxU > (bf ? 128 : 256) || d.B > 65535)
+    return false;
   if (bf && passes != 2) return false;   // one operand precision is built for bf16 storage
   // E and egrads are TMA operands (16-byte base); the column owners read P and write pgrads
   // with plain 4-byte accesses, but a caller whose P / pgrads are offset by a few bytes gets
   // the same routing as for E: the SIMT kernels
   for (const void* ptr : {E, P, egrads, pgrads})
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return false;
-  const int Ku = (int)round_up64(d.maxU, 8);
-  return pick_tile(Ku, grads_umma_ld_w(d), (int)round_up64(d.maxU, 16), passes, kStaticSmemBound, bf).TB > 0;
+  const int n = std::min(d.maxU, 128);   // positions of the (first) launch
+  return pick_tile((int)round_up64(n, 8), (int)round_up64(n, 32), (int)round_up64(n, 16), passes,
+                   kStaticSmemBound, bf).TB > 0;
 }
 
 void launch_unskew_round(const float* stayS, const float* stepS, const float* LNs,
@@ -886,65 +953,82 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
   TB200_CHECK_LAUNCH();
 }
 
+void launch_tc_operands(float* W, const float* em, const float* eBlank, const float* rowRef,
+                        const float* deltas, float* emT, float* nref, float* ebl,
+                        const int* inLens, Dims d, cudaStream_t stream) {
+  if (d.B <= 0 || d.maxT <= 0 || d.maxU <= 0) return;
+  const int ldW = grads_umma_ld_w(d), ldT = grads_umma_ld_t(d);
+  ScopedKernel sk("lattice_tc_operands", stream);
+  tc_operands_kernel<<<dim3(div_up(ldT, 32), div_up(ldW, 32), d.B), 256, 0, stream>>>(
+      W, em, eBlank, rowRef, deltas, emT, nref, ebl, inLens, d.maxT, d.maxU, ldW, ldT);
+  TB200_CHECK_LAUNCH();
+}
+
 void launch_grads_umma(const void* E, const void* P, const float* maxP, const float* W,
                        const float* emT, const float* nref, const float* ebl, const float* pBlank,
                        const float* pLabel, const int* labels, const float* deltas, void* egrads,
                        void* pgrads, const int* inLens, const int* labLens, Dims d, int passes,
                        int* status, cudaStream_t stream) {
   if (d.B <= 0 || d.V <= 0) return;
+  const bool bf = d.dtype == kDtypeBf16;
+  if (bf && passes != 2) throw std::invalid_argument("bf16 gradients are built for grad_passes = 2 only");
   GradParams p;
   p.P = P; p.maxP = maxP; p.pBlank = pBlank; p.pLabel = pLabel; p.emT = emT; p.labels = labels;
   p.inLens = inLens; p.labLens = labLens; p.deltas = deltas; p.egrads = egrads; p.pgrads = pgrads;
   p.status = status;
   p.maxT = d.maxT; p.maxU = d.maxU; p.V = d.V; p.blank = d.blank;
   p.ldT = grads_umma_ld_t(d);
-  p.ldW = grads_umma_ld_w(d);
-  p.Ku = (int)round_up64(d.maxU, 8);
-  p.N2 = (int)round_up64(d.maxU, 16);
-  p.stagesE = p.stagesW = p.eBufs = p.dBufs = p.tmemCols = 0;
-  const bool bf = d.dtype == kDtypeBf16;
-  const TileCfg cfg = pick_tile(p.Ku, p.ldW, p.N2, passes, kStaticSmemBound, bf);
-  if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
-  const int TB = cfg.TB;
-  const uint64_t V = d.V, T = d.maxT, B = d.B, ldW = p.ldW, ldT = p.ldT, U = d.maxU;
-  GradMaps tm;
-  if (bf) {
-    tm.E = make_tmap_bf16_3d(E, V, T, B, V * 2, T * V * 2, 64, TB);
-    tm.G = make_tmap_bf16_3d(egrads, V, T, B, V * 2, T * V * 2, 64, TB);
-  } else {
-    tm.E = make_tmap_f32_3d(E, V, T, B, V * 4, T * V * 4, TB);
-    tm.G = make_tmap_f32_3d(egrads, V, T, B, V * 4, T * V * 4, TB);
-  }
-  tm.Wk = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB);
-  tm.Wmn = make_tmap_f32_3d(W, ldW, T, B, ldW * 4, T * ldW * 4, TB, /*atom32=*/true);
-  tm.nref = make_tmap_f32_rows(nref, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
-  tm.ebl = make_tmap_f32_rows(ebl, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
-  tm.emT = make_tmap_f32_rows(emT, ldT, U, B, ldT * 4, U * ldT * 4, TB);
+  const uint64_t V = d.V, T = d.maxT, B = d.B, ldWall = grads_umma_ld_w(d), ldT = p.ldT, U = d.maxU;
+  // one launch per range of 128 label positions (see GradParams::uOff)
+  for (int uOff = 0; uOff < d.maxU; uOff += 128) {
+    const int n = std::min(128, d.maxU - uOff);
+    p.uOff = uOff;
+    p.accumulate = uOff > 0 ? 1 : 0;
+    p.ldW = (int)round_up64(n, 32);
+    p.Ku = (int)round_up64(n, 8);
+    p.N2 = (int)round_up64(n, 16);
+    p.stagesE = p.stagesW = p.eBufs = p.dBufs = p.tmemCols = 0;
+    const TileCfg cfg = pick_tile(p.Ku, p.ldW, p.N2, passes, kStaticSmemBound, bf);
+    if (cfg.TB == 0) throw std::invalid_argument("label axis too long for the tensor-core gradient kernel");
+    const int TB = cfg.TB;
+    GradMaps tm;
+    if (bf) {
+      tm.E = make_tmap_bf16_3d(E, V, T, B, V * 2, T * V * 2, 64, TB);
+      tm.G = make_tmap_bf16_3d(egrads, V, T, B, V * 2, T * V * 2, 64, TB);
+    } else {
+      tm.E = make_tmap_f32_3d(E, V, T, B, V * 4, T * V * 4, TB);
+      tm.G = make_tmap_f32_3d(egrads, V, T, B, V * 4, T * V * 4, TB);
+    }
+    tm.Wk = make_tmap_f32_3d(W, ldWall, T, B, ldWall * 4, T * ldWall * 4, TB);
+    tm.Wmn = make_tmap_f32_3d(W, ldWall, T, B, ldWall * 4, T * ldWall * 4, TB, /*atom32=*/true);
+    tm.nref = make_tmap_f32_rows(nref, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
+    tm.ebl = make_tmap_f32_rows(ebl, ldT, B, 1, ldT * 4, B * ldT * 4, TB);
+    tm.emT = make_tmap_f32_rows(emT, ldT, U, B, ldT * 4, U * ldT * 4, TB);
 #define GO(TBV, EV, PV) launch_variant<TBV, EV, PV>(tm, p, cfg, d, stream)
 #define GO_TB(EV, PV) \
   do { if (TB == 64) GO(64, EV, PV); else if (TB == 48) GO(48, EV, PV); else GO(32, EV, PV); } while (0)
-  if (bf) {
-    if (passes != 2) throw std::invalid_argument("bf16 gradients are built for grad_passes = 2 only");
-    if (TB == 64) launch_variant<64, true, false, true>(tm, p, cfg, d, stream);
-    else if (TB == 48) launch_variant<48, true, false, true>(tm, p, cfg, d, stream);
-    else launch_variant<32, true, false, true>(tm, p, cfg, d, stream);
-  } else if (passes == 3) GO_TB(true, true);
-  else if (passes == 2) GO_TB(true, false);
-  else GO_TB(false, false);
+    if (bf) {
+      if (TB == 64) launch_variant<64, true, false, true>(tm, p, cfg, d, stream);
+      else if (TB == 48) launch_variant<48, true, false, true>(tm, p, cfg, d, stream);
+      else launch_variant<32, true, false, true>(tm, p, cfg, d, stream);
+    } else if (passes == 3) GO_TB(true, true);
+    else if (passes == 2) GO_TB(true, false);
+    else GO_TB(false, false);
 #undef GO_TB
 #undef GO
-  TB200_CHECK_LAUNCH();
-  // only a vocabulary block that can hold more labels than are staged needs the second kernel
-  if (d.maxU - 1 > kMaxStagedLabels) {
-    ScopedKernel sk("label_overflow", stream);
-    const dim3 grid(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024));
-    if (bf)
-      label_overflow_kernel<bf16><<<grid, 256, 0, stream>>>(
-          labels, emT, static_cast<bf16*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
-    else
-      label_overflow_kernel<float><<<grid, 256, 0, stream>>>(
-          labels, emT, static_cast<float*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT);
     TB200_CHECK_LAUNCH();
+    // only a vocabulary block that can hold more labels than are staged needs the second kernel
+    if (n - (uOff + n == d.maxU ? 1 : 0) > kMaxStagedLabels) {
+      ScopedKernel sk("label_overflow", stream);
+      const dim3 grid(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024));
+      if (bf)
+        label_overflow_kernel<bf16><<<grid, 256, 0, stream>>>(
+            labels, emT, static_cast<bf16*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff);
+      else
+        label_overflow_kernel<float><<<grid, 256, 0, stream>>>(
+            labels, emT, static_cast<float*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff);
+      TB200_CHECK_LAUNCH();
+    }
   }
 }
 

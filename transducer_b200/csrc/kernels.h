@@ -146,7 +146,15 @@ void launch_unskew_round(const float* stayS, const float* stepS, const float* LN
                          float* emT, float* nref, float* ebl, const int* inLens,
                          const int* labLens, SkewGeom g, Dims d, bool tensorCore,
                          cudaStream_t stream);
-// E, P, egrads and pgrads are of d.dtype (bf16: passes = 2 only).
+// Operands of launch_grads_umma from the outputs of the block-wide reverse sweep
+// (launch_gamma_skew + launch_lattice_unskew; label axes of more than 128 positions): W is
+// scaled by deltas[b] and rounded to TF32 in place, em [B,maxT,maxU] becomes emT, eBlank becomes
+// ebl, rowRef becomes nref (layouts as written by launch_unskew_round with tensorCore = true).
+void launch_tc_operands(float* W, const float* em, const float* eBlank, const float* rowRef,
+                        const float* deltas, float* emT, float* nref, float* ebl,
+                        const int* inLens, Dims d, cudaStream_t stream);
+// E, P, egrads and pgrads are of d.dtype (bf16: passes = 2 only, label axes up to 128; fp32:
+// label axes up to 256 positions, those above 128 as two launches over halves of the axis).
 void launch_grads_umma(const void* E, const void* P, const float* maxP, const float* W,
                        const float* emT, const float* nref, const float* ebl, const float* pBlank,
                        const float* pLabel, const int* labels, const float* deltas, void* egrads,

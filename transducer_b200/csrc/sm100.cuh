@@ -131,6 +131,14 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
       ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// The same tile ADDED to global memory (fp32 add done by the copy engine).
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* src, int x,
+                                                  int y, int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
