@@ -45,6 +45,10 @@ CONFIGS = {
     # Viterbi best path
     "c5": Workload("c5", B=64, T=1500, U=150, V=4096, t_range=(750, 1500),
                    u_range=(75, 150), blank_bias=4.0, task="viterbi"),
+    # not a benchmark configuration of the reference: the shape of c5 through the loss (forward +
+    # backward), i.e. a label axis of more than 128 positions in the gradient kernels
+    "c5_loss": Workload("c5_loss", B=64, T=1500, U=150, V=4096, t_range=(750, 1500),
+                        u_range=(75, 150), blank_bias=4.0, task="loss"),
 }
 
 
