@@ -758,8 +758,8 @@ __global__ void __launch_bounds__(1024, 2) unskew_round_kernel(
 // columns it subtracts the occupancies of the first kMaxStagedLabels label positions (in
 // position order) whose label falls into the block; with a vocabulary of ten thousand entries a
 // block sees one or two labels, but a vocabulary of 100 puts all of an utterance's labels into
-// one block.  The remaining positions are applied here, one CTA per (block, utterance, 1024
-// frames), in position order (so that repeated labels are combined in a fixed order):
+// one block.  The remaining positions are applied here, one CTA per (block, utterance,
+// framesPerCta frames), in position order (so that repeated labels are combined in a fixed order):
 //   egrads[b, t, label_u] -= emT[b, u, t]        (emT already carries delta_b)
 // The CTA rebuilds the block's list exactly as the gradient kernel does and returns at once if
 // it is short enough, which is the normal case.
@@ -767,7 +767,7 @@ template <typename TIO>
 __global__ void __launch_bounds__(256) label_overflow_kernel(
     const int* __restrict__ labels, const float* __restrict__ emT, TIO* __restrict__ egrads,
     const int* __restrict__ inLens, const int* __restrict__ labLens, int maxT, int maxU, int V,
-    int ldT, int uOff) {
+    int ldT, int uOff, int framesPerCta) {
   __shared__ short sU[128];
   __shared__ short sV[128];
   __shared__ int sCount;
@@ -797,10 +797,10 @@ __global__ void __launch_bounds__(256) label_overflow_kernel(
     sCount = max(0, n - kMaxStagedLabels);
   }
   __syncthreads();
-  // a thread owns frames t = blockIdx.z * 1024 + thread + 256 j and applies the positions one
+  // a thread owns frames t = blockIdx.z * framesPerCta + thread + 256 j and applies the positions one
   // after the other, so repeated labels are combined in position order
   const int n = sCount;
-  for (int t = blockIdx.z * 1024 + threadIdx.x; t < min(T, (int)(blockIdx.z + 1) * 1024); t += 256) {
+  for (int t = blockIdx.z * framesPerCta + threadIdx.x; t < min(T, (int)(blockIdx.z + 1) * framesPerCta); t += 256) {
     TIO* row = egrads + ((i64)b * maxT + t) * V + v0;
     for (int k = 0; k < n; ++k)
       from_f32(row[sV[k]], to_f32(row[sV[k]]) - emT[((i64)b * maxU + uOff + sU[k]) * ldT + t]);
@@ -1020,13 +1020,16 @@ void launch_grads_umma(const void* E, const void* P, const float* maxP, const fl
     // only a vocabulary block that can hold more labels than are staged needs the second kernel
     if (n - (uOff + n == d.maxU ? 1 : 0) > kMaxStagedLabels) {
       ScopedKernel sk("label_overflow", stream);
-      const dim3 grid(div_up(d.V, kVBlock), d.B, div_up(d.maxT, 1024));
+      // (few vocabulary blocks: the kernel will have work -- spread the frames over more CTAs;
+      // many blocks: almost every CTA returns at once -- keep them few)
+      const int framesPerCta = d.V <= 1024 ? 256 : 1024;
+      const dim3 grid(div_up(d.V, kVBlock), d.B, div_up(d.maxT, framesPerCta));
       if (bf)
         label_overflow_kernel<bf16><<<grid, 256, 0, stream>>>(
-            labels, emT, static_cast<bf16*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff);
+            labels, emT, static_cast<bf16*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff, framesPerCta);
       else
         label_overflow_kernel<float><<<grid, 256, 0, stream>>>(
-            labels, emT, static_cast<float*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff);
+            labels, emT, static_cast<float*>(egrads), inLens, labLens, d.maxT, d.maxU, d.V, p.ldT, uOff, framesPerCta);
       TB200_CHECK_LAUNCH();
     }
   }
