@@ -140,20 +140,60 @@ __device__ float pick_threshold(float* row, int V, int vp, int blank, int K, int
   return hi;
 }
 
-// Appends the entries above `th` to out (index, value bits; any order; at most K of them by
-// the choice of th) through the counter *cnt (shared memory, zero on entry); returns the
-// largest entry not appended.  Warp-wide.
+// Copies the entries above `th` to out (index, value bits; any order; at most K of them by the
+// choice of th), sets *cnt (shared memory) to their number and returns the largest entry not
+// copied.  Warp-wide.  Rows of up to 4096 words: one branch-free pass marks the entries in a
+// bit mask per lane, then every lane copies its own few (a branch per entry would be taken by
+// the whole warp ~100 times per row); longer rows: appended one by one through the counter.
 __device__ __forceinline__ float collect_above(const float* row, int vp, float th, int lane,
                                                int2* out, int* cnt) {
   float rest = neg_inf();
   const float4* r4 = reinterpret_cast<const float4*>(row);
-  for (int i = lane; i < (vp >> 2); i += 32) {
-    const float4 x4 = r4[i];
-    const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+  const int n4 = vp >> 2;
+  if (n4 <= 1024) {
+    unsigned mask[4] = {0u, 0u, 0u, 0u};   // bit 4q + k of word q / 8: entry k of float4 lane + 32q
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (x[k] > th) out[atomicAdd(cnt, 1)] = make_int2(4 * i + k, __float_as_int(x[k]));
-      else rest = fmaxf(rest, x[k]);   // (NaN entries are ignored, as by the reference's '>')
+    for (int q = 0; q < 32; ++q) {
+      const int i = lane + 32 * q;
+      if (i < n4) {
+        const float4 x4 = r4[i];
+        const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const bool sel = x[k] > th;
+          mask[q >> 3] |= sel ? 1u << ((4 * q + k) & 31) : 0u;
+          rest = sel ? rest : fmaxf(rest, x[k]);   // (NaN entries are ignored, as by the reference's '>')
+        }
+      }
+    }
+    const int mine = __popc(mask[0]) + __popc(mask[1]) + __popc(mask[2]) + __popc(mask[3]);
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int at = incl - mine;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      unsigned m = mask[w];
+      while (m) {
+        const int e = 32 * w + __ffs(m) - 1;   // entry (e & 3) of float4 lane + 32 * (e >> 2)
+        m &= m - 1;
+        const int v = 4 * (lane + 32 * (e >> 2)) + (e & 3);
+        out[at++] = make_int2(v, __float_as_int(row[v]));
+      }
+    }
+    if (lane == 31) *cnt = incl;
+  } else {
+    for (int i = lane; i < n4; i += 32) {
+      const float4 x4 = r4[i];
+      const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (x[k] > th) out[atomicAdd(cnt, 1)] = make_int2(4 * i + k, __float_as_int(x[k]));
+        else rest = fmaxf(rest, x[k]);
+      }
     }
   }
   __syncwarp();
